@@ -1,0 +1,450 @@
+// Variable-length causal GQA flash-attention prefill on tcgen05 / TMEM.
+//
+// Math of the reference's context_attention_fwd
+// (python/dlBLAS/dlblas/kernels/prefill_attention.py:28-181): per packed
+// sequence, softmax(q k^T * sm_scale + causal mask) v with fp32 softmax and
+// accumulation and P cast to the value dtype before P.V; optional LSE output
+// in the convention of python/dlBLAS/dlblas/kernels/flash_attention.py:152-155
+// (natural log, scale included).
+//
+// One CTA = one (sequence, q-head, 128-query tile); two CTAs are resident per
+// SM (256 TMEM columns and ~113 KiB of shared memory each), so one CTA's
+// softmax overlaps the other's MMAs.  Inside a CTA, 192 threads:
+//   warp 0     TMA producer: Q tile once, then K and V tiles of 64 keys into
+//              2-stage rings (3-D tensor maps over [token, head, d], 128-byte swizzle)
+//   warp 1     one lane issues tcgen05.mma: S_j = Q K_j^T (M128 N64 K16 x 8) into
+//              a double-buffered TMEM S, then O += P_{j-1} V_{j-1}
+//              (M128 N128 K16 x 4, V as an MN-major operand straight from the
+//              row-major tile), software-pipelined so S_j is computed while
+//              the softmax of block j-1 runs
+//   warps 2-5  softmax: one thread per query row reads its S row from TMEM
+//              (tcgen05.ld), online softmax in the base-2 domain, writes P
+//              (16-bit, swizzled K-major) to shared memory for the next MMA,
+//              rescales O in TMEM only when the row max grew by more than
+//              2^8 (lazy rescaling), and finally normalises and stores O
+// CTAs are ordered by decreasing causal work so the tail of the grid is short.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace dlb {
+
+namespace fp {
+constexpr int BM = 128;           // query rows per CTA
+constexpr int BN = 64;            // keys per block
+constexpr int D = 128;            // head size
+constexpr int THREADS = 192;
+constexpr int Q_BYTES = BM * D * 2;            // 32 KiB (two 64-wide boxes)
+constexpr int KV_BYTES = BN * D * 2;           // 16 KiB (two 64-wide boxes)
+constexpr int P_BYTES = BM * BN * 2;           // 16 KiB
+constexpr int KV_STAGES = 2;
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;
+constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
+constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
+constexpr int OFF_CTRL = OFF_P + P_BYTES;
+constexpr int SMEM_BYTES = OFF_CTRL + 128;   // two CTAs (plus 1 KiB system reserve each) fit one SM
+constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,256)
+constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
+}  // namespace fp
+
+static int make_tmap_tokens(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t tokens,
+                            int64_t stride_h, int64_t stride_t, int box_tokens) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  DLB_CHECK_ARG(enc != nullptr, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  DLB_CHECK_ARG(((uintptr_t)base & 15) == 0, DLB_ERR_ALIGNMENT, "attention tensor base is not 16-byte aligned");
+  DLB_CHECK_ARG((stride_h * 2) % 16 == 0 && (stride_t * 2) % 16 == 0, DLB_ERR_ALIGNMENT,
+                "attention tensor strides must be multiples of 16 bytes");
+  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)stride_h * 2, (cuuint64_t)stride_t * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)box_tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DLB_CHECK_ARG(r == CUDA_SUCCESS, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled(tokens) failed with CUresult %d", (int)r);
+  return DLB_OK;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct PrefillParams {
+  void* out;
+  float* lse;                     // [hq, total] or null
+  const int32_t* b_start_loc;
+  const int32_t* b_seq_len;
+  int64_t o_stride_t, o_stride_h;
+  int64_t total_tokens;
+  int batch, hq, hkv, group;
+  int max_tiles;
+  int causal;
+  float scale_log2;               // sm_scale * log2(e)
+  uint32_t idesc_qk, idesc_pv;
+  uint32_t v_lbo, v_sbo;          // MN-major descriptor strides of the V tile
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(fp::THREADS, 2)
+flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  using namespace fp;
+  // ---- which tile ----
+  const int head = blockIdx.x % p.hq;
+  const int t_lin = blockIdx.x / p.hq;
+  const int seq = t_lin % p.batch;
+  const int tile = p.max_tiles - 1 - t_lin / p.batch;     // heavy (late) tiles first
+  const int seq_len = p.b_seq_len[seq];
+  const int q0 = tile * BM;
+  if (q0 >= seq_len) return;
+  const int start = p.b_start_loc[seq];
+  const int kv_end = p.causal ? min(seq_len, q0 + BM) : seq_len;
+  const int nb = (kv_end + BN - 1) / BN;
+  const int kvh = head / p.group;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    // the 128-byte swizzle needs 1 KiB aligned tiles; report instead of computing garbage
+    if (threadIdx.x == 0 && p.status != nullptr && atomicCAS(p.status, 0, 2) == 0) p.status[1] = 20;
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_CTRL);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* k_empty = bars + 3;    // [2]
+  uint64_t* v_full = bars + 5;     // [2]
+  uint64_t* v_empty = bars + 7;    // [2]
+  uint64_t* s_full = bars + 9;     // [2]
+  uint64_t* s_empty = bars + 11;   // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* pv_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      mbar_arrive_expect_tx(q_full, Q_BYTES);
+      tma_load_3d(smem + OFF_Q, &tmap_q, q_full, 0, head, start + q0);
+      tma_load_3d(smem + OFF_Q + Q_BYTES / 2, &tmap_q, q_full, 64, head, start + q0);
+      for (int j = 0; j < nb; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int row = start + j * BN;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, 21, j)) break;
+        uint8_t* kd = smem + OFF_K + s * KV_BYTES;
+        mbar_arrive_expect_tx(&k_full[s], KV_BYTES);
+        tma_load_3d(kd, &tmap_k, &k_full[s], 0, kvh, row);
+        tma_load_3d(kd + KV_BYTES / 2, &tmap_k, &k_full[s], 64, kvh, row);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
+        uint8_t* vd = smem + OFF_V + s * KV_BYTES;
+        mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
+        tma_load_3d(vd, &tmap_v, &v_full[s], 0, kvh, row);
+        tma_load_3d(vd + KV_BYTES / 2, &tmap_v, &v_full[s], 64, kvh, row);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 23, 0);
+      const uint32_t q_addr = smem_u32(smem + OFF_Q);
+      const uint32_t p_addr = smem_u32(smem + OFF_P);
+      for (int j = 0; ok && j <= nb; ++j) {
+        if (j < nb) {
+          // S_j = Q K_j^T
+          const int s = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          if (!mbar_wait(&k_full[s], ph, abort_flag, p.status, 24, j)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[s], ph ^ 1, abort_flag, p.status, 25, j)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t k_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t a_desc = make_smem_desc(q_addr + (ks >> 2) * (Q_BYTES / 2) + (ks & 3) * 32, 16, 1024, 2);
+            const uint64_t b_desc = make_smem_desc(k_addr + (ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32, 16, 1024, 2);
+            umma_ss_f16(tmem_base + s * BN, a_desc, b_desc, p.idesc_qk, ks != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[s]);
+          umma_commit(&k_empty[s]);
+        }
+        if (j > 0) {
+          // O += P_{j-1} V_{j-1}
+          const int jj = j - 1;
+          const int s = jj & 1;
+          const uint32_t ph = (jj >> 1) & 1;
+          if (!mbar_wait(p_full, jj & 1, abort_flag, p.status, 26, jj)) { ok = false; break; }
+          if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, 27, jj)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t v_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < BN / 16; ++ks) {
+            const uint64_t a_desc = make_smem_desc(p_addr + ks * 32, 16, 1024, 2);
+            const uint64_t b_desc = make_smem_desc(v_addr + ks * 16 * 128, p.v_lbo, p.v_sbo, 2);
+            umma_ss_f16(tmem_o, a_desc, b_desc, p.idesc_pv, (jj | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(pv_done);
+          umma_commit(&v_empty[s]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax / correction / epilogue ------------------------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;              // query row inside the tile == TMEM lane
+    const int q_pos = q0 + row;                    // position inside the sequence
+    const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+    float m_ref = -CUDART_INF_F;                   // reference max used for exponentiation (scaled, log2 domain)
+    float l_sum = 0.f;
+    uint8_t* p_row = smem + OFF_P + row * 128;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(&s_full[s], ph, abort_flag, p.status, 28, j);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t sr[2][32];
+      tmem_ld_32x32b_x32(tmem_base + lane_field + s * BN, sr[0]);
+      tmem_ld_32x32b_x32(tmem_base + lane_field + s * BN + 32, sr[1]);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+
+      // scale + mask
+      const int key0 = j * BN;
+      const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0);
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float v = __uint_as_float(sr[h][c]) * p.scale_log2;
+          if (need_mask) {
+            const int key = key0 + h * 32 + c;
+            const bool visible = key < kv_end && (!p.causal || key <= q_pos);
+            v = visible ? v : -CUDART_INF_F;
+          }
+          sr[h][c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      }
+      // lazy rescale decision
+      float alpha = 1.f;
+      bool rescale = false;
+      if (m_ref == -CUDART_INF_F) {
+        m_ref = mx;                                 // first visible block: nothing accumulated yet
+      } else if (mx - m_ref > RESCALE_THRESHOLD) {
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+        rescale = true;
+      }
+      // exponentiate, pack to 16 bit
+      uint32_t pk[32];
+      float psum = 0.f;
+      const float mref_safe = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float e0 = fast_exp2(__uint_as_float(sr[h][c]) - mref_safe);
+          const float e1 = fast_exp2(__uint_as_float(sr[h][c + 1]) - mref_safe);
+          psum += e0 + e1;
+          if constexpr (sizeof(T) == 2) {
+            typename Elem<T>::T2 v2 = Elem<T>::from_f2(e0, e1);
+            pk[h * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+        }
+      }
+      l_sum = l_sum * alpha + psum;
+
+      // P buffer and O are free once P_{j-1} V_{j-1} has retired
+      if (j > 0) {
+        ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 29, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_o + lane_field + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_o + lane_field + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // write P row (64 x 16 bit = 128 B) in the swizzled K-major layout
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) =
+            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok) {
+      ok = mbar_wait(pv_done, (nb - 1) & 1, abort_flag, p.status, 30, nb);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l_sum;
+      const bool row_ok = q_pos < seq_len;
+      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(start + q_pos) * p.o_stride_t + (int64_t)head * p.o_stride_h;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_field + c * 32, o);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              typename Elem<T>::T2 v2 = Elem<T>::from_f2(__uint_as_float(o[v * 8 + 2 * i]) * inv_l,
+                                                         __uint_as_float(o[v * 8 + 2 * i + 1]) * inv_l);
+              w[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr) {
+        p.lse[(int64_t)head * p.total_tokens + start + q_pos] = m_ref * 0.6931471805599453f + __logf(l_sum);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace dlb
+
+extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
+                                        const int32_t* b_start_loc, const int32_t* b_seq_len, int64_t batch,
+                                        int64_t total_tokens, int64_t max_seq_len, int64_t hq, int64_t hkv,
+                                        int64_t head_dim, int64_t q_stride_t, int64_t q_stride_h,
+                                        int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
+                                        int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h, float sm_scale,
+                                        int causal, int dtype, int32_t* status, void* stream) {
+  using namespace dlb;
+  using namespace dlb::fp;
+  DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
+                "flash_prefill: dtype %d (need fp16 or bf16)", dtype);
+  DLB_CHECK_ARG(head_dim == D, DLB_ERR_UNSUPPORTED, "flash_prefill: head_dim %lld not supported (128)",
+                (long long)head_dim);
+  DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "flash_prefill: bad head counts");
+  DLB_CHECK_ARG(total_tokens >= 0 && max_seq_len >= 0, DLB_ERR_BAD_ARG, "flash_prefill: negative size");
+  if (batch == 0 || total_tokens == 0 || max_seq_len == 0) return DLB_OK;
+  DLB_CHECK_ARG(q && k && v && out && b_start_loc && b_seq_len, DLB_ERR_BAD_ARG, "flash_prefill: null pointer");
+  DLB_CHECK_ARG(((uintptr_t)out & 15) == 0 && o_stride_t % 8 == 0 && o_stride_h % 8 == 0, DLB_ERR_ALIGNMENT,
+                "flash_prefill: output must be 16-byte aligned with strides that are multiples of 8");
+  const int64_t max_tiles = (max_seq_len + BM - 1) / BM;
+  const int64_t grid = max_tiles * batch * hq;
+  DLB_CHECK_ARG(grid <= 0x7fffffffLL && total_tokens < (1LL << 31), DLB_ERR_TOO_LARGE, "flash_prefill: grid too large");
+
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_tokens(&tq, q, D, hq, total_tokens, q_stride_h, q_stride_t, BM);
+  if (rc != DLB_OK) return rc;
+  rc = make_tmap_tokens(&tk, k, D, hkv, total_tokens, k_stride_h, k_stride_t, BN);
+  if (rc != DLB_OK) return rc;
+  rc = make_tmap_tokens(&tv, v, D, hkv, total_tokens, v_stride_h, v_stride_t, BN);
+  if (rc != DLB_OK) return rc;
+
+  const uint32_t fmt = dtype == DLB_DTYPE_BF16 ? 1u : 0u;
+  PrefillParams p;
+  p.out = out;
+  p.lse = lse;
+  p.b_start_loc = b_start_loc;
+  p.b_seq_len = b_seq_len;
+  p.o_stride_t = o_stride_t;
+  p.o_stride_h = o_stride_h;
+  p.total_tokens = total_tokens;
+  p.batch = (int)batch;
+  p.hq = (int)hq;
+  p.hkv = (int)hkv;
+  p.group = (int)(hq / hkv);
+  p.max_tiles = (int)max_tiles;
+  p.causal = causal;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.idesc_qk = make_idesc_f16(BM, BN, fmt, 0u, 0u);
+  p.idesc_pv = make_idesc_f16(BM, D, fmt, 0u, 1u);
+  // V tile in shared memory: two 64-wide (128 B) column boxes of BN key rows each.
+  // MN-major canonical layout: 64 d contiguous, next 64-d atom at LBO; 8 key rows at
+  // 128 B pitch, next group of 8 keys at SBO.
+  p.v_lbo = KV_BYTES / 2;
+  p.v_sbo = 1024;
+  p.status = status;
+
+  cudaError_t e;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DLB_DTYPE_BF16) {
+    auto kern = flash_prefill_kernel<__nv_bfloat16>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) { set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e)); return (int)e; }
+    kern<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(tq, tk, tv, p);
+  } else {
+    auto kern = flash_prefill_kernel<__half>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) { set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e)); return (int)e; }
+    kern<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(tq, tk, tv, p);
+  }
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}

@@ -1,0 +1,407 @@
+// Grouped (per-expert) GEMM for fused_moe on the 5th-generation tensor cores.
+//
+// Computes, for every 128-row block b of the expert-sorted, block-padded row
+// list produced by moe_align_block_size,
+//     C[rows of b, :] = A[rows of b, :] @ B[expert_ids[b]]^T        (fp32 accumulate)
+// which is what the reference's Triton `fused_moe_kernel` does per expert
+// (python/dlBLAS/dlblas/kernels/fused_moe.py:77-175; B is [E, N, K] with K
+// contiguous).  Two epilogues cover the two GEMMs of fused_moe():
+//   FUSE_SILU   : B holds [gate; up] halves (fused_moe.py:351-352).  A tile
+//                 accumulates 128 gate and the matching 128 up columns in one
+//                 256-wide MMA and stores silu(gate) * up, rounding at the
+//                 same three points as the reference (GEMM output -> bf16,
+//                 silu -> bf16, product -> bf16).
+//   WEIGHT/SCATTER: rows are scaled by the routing weight in fp32 before the
+//                 cast (fused_moe.py:162-166) and written to row `slot` of the
+//                 [tokens * top_k, N] buffer (reindex_c, fused_moe.py:168-169).
+//
+// Kernel structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128B-swizzled A (128 x 64) and B (256 x 64)
+//               tiles into a 4-stage shared-memory ring, mbarrier expect_tx
+//   warp 1      allocates TMEM, one lane issues tcgen05.mma (M128 N256 K16),
+//               tcgen05.commit releases ring stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (one TMEM lane =
+//               one output row per thread), fused math, 16-byte global stores
+// The 512 TMEM columns hold two 256-column accumulators, so the epilogue of
+// tile i overlaps the main loop of tile i+1.  Tiles are ordered expert-major,
+// then by N tile, then by M block, so the CTAs running concurrently share one
+// expert's weight tiles through L2 and each weight tile leaves HBM once.
+#include "common.cuh"
+
+namespace dlb {
+
+namespace gg {
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 x 16-bit = one 128-byte swizzle row
+constexpr int UMMA_N = 256;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
+constexpr int B_BYTES = UMMA_N * BK * 2;    // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int MAX_EXPERTS = 1024;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+// dynamic shared memory: ring + 1 KiB alignment slack + control block
+constexpr int CTRL_BYTES = 256 + (MAX_EXPERTS + 1) * 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + CTRL_BYTES;
+
+constexpr int FLAG_FUSE_SILU = 1;
+constexpr int FLAG_WEIGHT = 2;
+constexpr int FLAG_SCATTER = 4;
+}  // namespace gg
+
+struct GroupedGemmParams {
+  const int32_t* sorted_token_ids;   // [padded rows]
+  const int32_t* block_start;        // [E + 1] first 128-row block of each expert
+  const float* topk_weights;         // [numel] routing weight per slot (FLAG_WEIGHT)
+  void* out;
+  int64_t out_row_stride;            // elements
+  int num_experts;
+  int n_out;                         // output columns
+  int k;                             // reduction length
+  int numel;                         // tokens * top_k (sentinel value of sorted_token_ids)
+  int rows_per_expert;               // rows of B per expert
+  int up_row_offset;                 // FUSE_SILU: row offset of the `up` half inside an expert
+  int max_m_blocks;                  // rows of A / 128
+  int idesc;
+  int* status;
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename T> __device__ __forceinline__ float round_to(float a) { return Elem<T>::to_f(Elem<T>::from_f(a)); }
+
+// silu(gate) * up with the reference's rounding points.
+template <typename T> __device__ __forceinline__ float silu_mul_rounded(float gate_acc, float up_acc) {
+  const float g = round_to<T>(gate_acc);
+  const float u = round_to<T>(up_acc);
+  const float s = round_to<T>(g / (1.0f + __expf(-g)));
+  return s * u;  // rounded by the caller's pack
+}
+
+struct TileCursor {
+  int e = 0;
+  // maps a linear tile index to (expert, n tile, m block); tiles must be visited in increasing order
+  __device__ __forceinline__ void locate(const int32_t* bs, int num_experts, int n_tiles, int tile, int& m_blk,
+                                         int& n_blk) {
+    while (e + 1 < num_experts && tile >= bs[e + 1] * n_tiles) ++e;
+    const int first = bs[e];
+    const int mb = bs[e + 1] - first;
+    const int local = tile - first * n_tiles;
+    n_blk = local / mb;
+    m_blk = first + (local - n_blk * mb);
+  }
+};
+
+template <typename T, int FLAGS>
+__global__ void __launch_bounds__(gg::THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GroupedGemmParams p) {
+  using namespace gg;
+  constexpr bool kSilu = (FLAGS & FLAG_FUSE_SILU) != 0;
+  constexpr bool kWeight = (FLAGS & FLAG_WEIGHT) != 0;
+  constexpr bool kScatter = (FLAGS & FLAG_SCATTER) != 0;
+  constexpr int BN_OUT = kSilu ? 128 : 256;   // output columns per tile
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* ctrl = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);            // [STAGES]
+  uint64_t* empty_bar = full_bar + STAGES;                           // [STAGES]
+  uint64_t* tmem_full_bar = empty_bar + STAGES;                      // [2]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;                      // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  int32_t* bs = reinterpret_cast<int32_t*>(ctrl + 256);              // [E + 1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i <= p.num_experts; i += THREADS) {
+    int v = p.block_start[i];
+    bs[i] = v < p.max_m_blocks ? v : p.max_m_blocks;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full_bar[i], 1);
+      mbar_init(&tmem_empty_bar[i], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int n_tiles = (p.n_out + BN_OUT - 1) / BN_OUT;
+  const int total_tiles = bs[p.num_experts] * n_tiles;
+  const int k_blocks = (p.k + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      TileCursor cur;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        int m_blk, n_blk;
+        cur.locate(bs, p.num_experts, n_tiles, tile, m_blk, n_blk);
+        const int b_row = cur.e * p.rows_per_expert + n_blk * BN_OUT;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 1, tile)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * BK, m_blk * BM);
+          if constexpr (kSilu) {
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * BK, b_row);
+            tma_load_2d(b_dst + B_BYTES / 2, &tmap_b, &full_bar[s], kb * BK, b_row + p.up_row_offset);
+          } else {
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * BK, b_row);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_ph ^ 1, abort_flag, p.status, 2, tile)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * UMMA_N;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3, tile)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, 2);
+          const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024, 2);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // advance 32 bytes (16 elements) along K inside the 128-byte swizzle row
+            umma_ss_f16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), (uint32_t)p.idesc,
+                        (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);   // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    TileCursor cur;
+    uint32_t tile_iter = 0;
+    T* out = reinterpret_cast<T*>(p.out);
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+      int m_blk, n_blk;
+      cur.locate(bs, p.num_experts, n_tiles, tile, m_blk, n_blk);
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      bool ok = mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag, p.status, 4, tile);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * UMMA_N;
+      const int sorted_row = m_blk * BM + row_in_tile;
+      const int col0 = n_blk * BN_OUT;
+
+      int64_t out_row = sorted_row;
+      bool row_valid = true;
+      float w = 1.0f;
+      if constexpr (kWeight || kScatter) {
+        const int sid = p.sorted_token_ids[sorted_row];
+        row_valid = sid < p.numel;
+        if constexpr (kScatter) out_row = row_valid ? sid : 0;
+        if constexpr (kWeight) w = row_valid ? p.topk_weights[sid] : 0.f;
+      }
+      T* orow = out + out_row * p.out_row_stride + col0;
+
+      if constexpr (kSilu) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, g);
+          tmem_ld_32x32b_x32(t_row + 128 + c * 32, u);
+          tmem_wait_ld();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float r0 = silu_mul_rounded<T>(__uint_as_float(g[2 * j]), __uint_as_float(u[2 * j]));
+            const float r1 = silu_mul_rounded<T>(__uint_as_float(g[2 * j + 1]), __uint_as_float(u[2 * j + 1]));
+            o[j] = pack2<T>(r0, r1);
+          }
+          if (row_valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = col0 + c * 32 + v * 8;
+              if (col + 8 <= p.n_out)
+                *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t a[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, a);
+          tmem_wait_ld();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            o[j] = pack2<T>(__uint_as_float(a[2 * j]) * w, __uint_as_float(a[2 * j + 1]) * w);
+          if (row_valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = col0 + c * 32 + v * 8;
+              if (col + 8 <= p.n_out)
+                *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <typename T, int FLAGS>
+static int launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, const GroupedGemmParams& p, int grid,
+                          cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<T, FLAGS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gg::SMEM_BYTES);
+  if (e != cudaSuccess) {
+    set_last_error("grouped_gemm: cannot raise dynamic shared memory to %d B: %s", gg::SMEM_BYTES,
+                   cudaGetErrorString(e));
+    return (int)e;
+  }
+  kern<<<grid, gg::THREADS, gg::SMEM_BYTES, stream>>>(ta, tb, p);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
+                                    int num_experts, int64_t rows_per_expert, int64_t k, int64_t b_row_stride,
+                                    void* out, int64_t out_row_stride, int64_t n_out,
+                                    const int32_t* sorted_token_ids, const int32_t* block_start,
+                                    const float* topk_weights, int64_t numel, int flags, int dtype,
+                                    int32_t* status, void* stream) {
+  using namespace dlb;
+  using namespace dlb::gg;
+  DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
+                "grouped_gemm: dtype %d (need fp16 or bf16)", dtype);
+  DLB_CHECK_ARG(a && b && out && sorted_token_ids && block_start, DLB_ERR_BAD_ARG, "grouped_gemm: null pointer");
+  DLB_CHECK_ARG(num_experts >= 1 && num_experts <= MAX_EXPERTS, DLB_ERR_UNSUPPORTED, "grouped_gemm: experts=%d",
+                num_experts);
+  DLB_CHECK_ARG(a_rows >= 0 && a_rows % BM == 0, DLB_ERR_BAD_ARG,
+                "grouped_gemm: A must hold a whole number of 128-row blocks (rows=%lld)", (long long)a_rows);
+  DLB_CHECK_ARG(k >= 8 && k % 8 == 0, DLB_ERR_ALIGNMENT, "grouped_gemm: K=%lld must be a positive multiple of 8",
+                (long long)k);
+  DLB_CHECK_ARG(n_out >= 8 && n_out % 8 == 0 && out_row_stride % 8 == 0, DLB_ERR_ALIGNMENT,
+                "grouped_gemm: N=%lld and the output row stride must be multiples of 8", (long long)n_out);
+  DLB_CHECK_ARG((((uintptr_t)out) & 15) == 0, DLB_ERR_ALIGNMENT, "grouped_gemm: output not 16-byte aligned");
+  DLB_CHECK_ARG(a_row_stride >= k && b_row_stride >= k, DLB_ERR_BAD_ARG, "grouped_gemm: row stride < K");
+  DLB_CHECK_ARG(k < (1LL << 31) && n_out < (1LL << 31) && a_rows < (1LL << 31) && numel < (1LL << 31) &&
+                    (int64_t)num_experts * rows_per_expert < (1LL << 31),
+                DLB_ERR_TOO_LARGE, "grouped_gemm: a dimension exceeds int32");
+  const bool silu = (flags & FLAG_FUSE_SILU) != 0;
+  if (silu) {
+    DLB_CHECK_ARG(flags == FLAG_FUSE_SILU, DLB_ERR_UNSUPPORTED, "grouped_gemm: silu fusion excludes weight/scatter");
+    DLB_CHECK_ARG(rows_per_expert == 2 * n_out, DLB_ERR_BAD_ARG,
+                  "grouped_gemm: fused silu needs rows_per_expert == 2 * n_out");
+  } else {
+    DLB_CHECK_ARG(rows_per_expert >= n_out, DLB_ERR_BAD_ARG, "grouped_gemm: rows_per_expert < n_out");
+    if (flags & FLAG_WEIGHT) DLB_CHECK_ARG(topk_weights != nullptr, DLB_ERR_BAD_ARG, "grouped_gemm: null weights");
+  }
+  if (a_rows == 0) return DLB_OK;
+
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_16b(&ta, a, (uint64_t)k, (uint64_t)a_rows, (uint64_t)a_row_stride * 2, BK, BM);
+  if (rc != DLB_OK) return rc;
+  rc = make_tmap_2d_16b(&tb, b, (uint64_t)k, (uint64_t)num_experts * rows_per_expert, (uint64_t)b_row_stride * 2,
+                        BK, silu ? 128 : 256);
+  if (rc != DLB_OK) return rc;
+
+  GroupedGemmParams p;
+  p.sorted_token_ids = sorted_token_ids;
+  p.block_start = block_start;
+  p.topk_weights = topk_weights;
+  p.out = out;
+  p.out_row_stride = out_row_stride;
+  p.num_experts = num_experts;
+  p.n_out = (int)n_out;
+  p.k = (int)k;
+  p.numel = (int)numel;
+  p.rows_per_expert = (int)rows_per_expert;
+  p.up_row_offset = (int)n_out;
+  p.max_m_blocks = (int)(a_rows / BM);
+  p.idesc = (int)make_idesc_f16(BM, UMMA_N, dtype == DLB_DTYPE_BF16 ? 1u : 0u, 0u, 0u);
+  p.status = status;
+
+  const int grid = sm_count(current_device());
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool bf = dtype == DLB_DTYPE_BF16;
+  switch (flags) {
+    case FLAG_FUSE_SILU:
+      return bf ? launch_grouped<__nv_bfloat16, FLAG_FUSE_SILU>(ta, tb, p, grid, s)
+                : launch_grouped<__half, FLAG_FUSE_SILU>(ta, tb, p, grid, s);
+    case 0:
+      return bf ? launch_grouped<__nv_bfloat16, 0>(ta, tb, p, grid, s) : launch_grouped<__half, 0>(ta, tb, p, grid, s);
+    case FLAG_WEIGHT:
+      return bf ? launch_grouped<__nv_bfloat16, FLAG_WEIGHT>(ta, tb, p, grid, s)
+                : launch_grouped<__half, FLAG_WEIGHT>(ta, tb, p, grid, s);
+    case FLAG_SCATTER:
+      return bf ? launch_grouped<__nv_bfloat16, FLAG_SCATTER>(ta, tb, p, grid, s)
+                : launch_grouped<__half, FLAG_SCATTER>(ta, tb, p, grid, s);
+    case FLAG_WEIGHT | FLAG_SCATTER:
+      return bf ? launch_grouped<__nv_bfloat16, FLAG_WEIGHT | FLAG_SCATTER>(ta, tb, p, grid, s)
+                : launch_grouped<__half, FLAG_WEIGHT | FLAG_SCATTER>(ta, tb, p, grid, s);
+    default:
+      set_last_error("grouped_gemm: unsupported flag combination %d", flags);
+      return DLB_ERR_UNSUPPORTED;
+  }
+}

@@ -1,0 +1,234 @@
+// MoE router: grouped top-k gating (DeepSeek-V3 style) and plain softmax top-k.
+//
+// One warp per token.  Lane l owns the VPL consecutive experts
+// [l*VPL, (l+1)*VPL), loaded as 128-bit vectors; every reduction (softmax
+// max/sum, per-group top-2 sums, group ranking, k rounds of arg-max) is a
+// warp-shuffle tree, so no shared memory and no atomics are used and the
+// result is deterministic.
+//
+// Algorithm (scoring = sigmoid, grouped):
+//   s[e]   = sigmoid(logits[e])                       (weights come from s)
+//   c[e]   = s[e] + bias[e]                            (selection score)
+//   g[j]   = sum of the two largest c in group j
+//   keep the topk_group groups with the largest g (ties: lower group index)
+//   pick the top_k experts with the largest c among kept groups
+//     (ties: lower expert index), output in descending order of c
+//   w[i]   = s[id_i]; if renormalize: w /= sum(w) (+eps); w *= scale
+// With scoring = softmax and n_group = topk_group = 1 this is the
+// softmax -> top-k router the fused_moe tests build with torch
+// (python/dlBLAS/tests/kernels/test_fused_moe.py:207-218).
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace dlb {
+
+#define DLB_SCORE_SIGMOID 0
+#define DLB_SCORE_SOFTMAX 1
+
+struct GatingParams {
+  const float* logits;   // [T, E] row stride = ld
+  const float* bias;     // [E] or null
+  int32_t* ids;          // [T, K]
+  float* weights;        // [T, K]
+  int64_t tokens;
+  int64_t ld;
+  int experts;
+  int n_group;
+  int topk_group;
+  int top_k;
+  int scoring;
+  int renormalize;
+  float scale;
+};
+
+__device__ __forceinline__ void merge_top2(float& a1, float& a2, float b1, float b2) {
+  // (a1 >= a2), (b1 >= b2) -> two largest of the four
+  const float hi = fmaxf(a1, b1);
+  const float lo = fmaxf(fminf(a1, b1), fmaxf(a2, b2));
+  a1 = hi;
+  a2 = lo;
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t token = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (token >= p.tokens) return;  // whole warp leaves together
+
+  const int E = p.experts;
+  const int e0 = lane * VPL;
+  const float* row = p.logits + token * p.ld;
+
+  float s[VPL];  // un-biased score (sigmoid or softmax probability)
+  float c[VPL];  // selection score
+  // ---- load ----
+  if constexpr (VPL >= 4) {
+#pragma unroll
+    for (int v = 0; v < VPL; v += 4) {
+      if (e0 + v + 3 < E) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(row + e0 + v));
+        s[v] = x.x; s[v + 1] = x.y; s[v + 2] = x.z; s[v + 3] = x.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[v + j] = (e0 + v + j < E) ? __ldg(row + e0 + v + j) : -CUDART_INF_F;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? __ldg(row + e0 + v) : -CUDART_INF_F;
+  }
+
+  // ---- scoring ----
+  if (p.scoring == DLB_SCORE_SIGMOID) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? 1.0f / (1.0f + expf(-s[v])) : -CUDART_INF_F;
+  } else {
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) m = fmaxf(m, s[v]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      s[v] = (e0 + v < E) ? expf(s[v] - m) : 0.f;
+      sum += s[v];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? s[v] / sum : -CUDART_INF_F;
+  }
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const bool valid = e0 + v < E;
+    c[v] = valid ? (p.bias != nullptr ? s[v] + __ldg(p.bias + e0 + v) : s[v]) : -CUDART_INF_F;
+  }
+
+  // ---- group selection ----
+  if (p.n_group > 1) {
+    const int lanes_per_group = (E / p.n_group) / VPL;  // power of two, checked on the host
+    float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) merge_top2(t1, t2, c[v], -CUDART_INF_F);
+    for (int o = 1; o < lanes_per_group; o <<= 1) {
+      const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
+      const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
+      merge_top2(t1, t2, o1, o2);
+    }
+    const int my_group = lane / lanes_per_group;
+    const float my_score = (my_group < p.n_group) ? t1 + t2 : -CUDART_INF_F;
+    int rank = 0;
+    for (int g = 0; g < p.n_group; ++g) {
+      const float gs = __shfl_sync(0xffffffffu, my_score, g * lanes_per_group);
+      rank += (gs > my_score) || (gs == my_score && g < my_group);
+    }
+    const bool keep = (my_group < p.n_group) && (rank < p.topk_group);
+    if (!keep) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) c[v] = -CUDART_INF_F;
+    }
+  }
+
+  // ---- top-k: k rounds of warp arg-max (ties -> lower expert index) ----
+  float wsum = 0.f;
+  float my_w = 0.f;   // lane i < K keeps weight i
+  int my_id = 0;
+  for (int k = 0; k < p.top_k; ++k) {
+    float best = -CUDART_INF_F;
+    int best_e = 0x7fffffff;
+    float best_s = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      if (c[v] > best) {  // strict: the lower index wins a tie inside the lane
+        best = c[v];
+        best_e = e0 + v;
+        best_s = s[v];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+        best_s = os;
+      }
+    }
+    // every lane now agrees on (best, best_e, best_s)
+    if (best_e >= e0 && best_e < e0 + VPL) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v)
+        if (e0 + v == best_e) c[v] = -CUDART_INF_F;
+    }
+    wsum += best_s;
+    if (lane == k) {
+      my_w = best_s;
+      my_id = best_e;
+    }
+  }
+  if (lane < p.top_k) {
+    float w = my_w;
+    if (p.renormalize) w = w / (wsum + 1e-20f);
+    w *= p.scale;
+    p.ids[token * p.top_k + lane] = my_id;
+    p.weights[token * p.top_k + lane] = w;
+  }
+}
+
+}  // namespace dlb
+
+extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, int32_t* ids, float* weights,
+                                       int64_t tokens, int experts, int64_t logits_row_stride, int n_group,
+                                       int topk_group, int top_k, int scoring, int renormalize, float scale,
+                                       void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0, DLB_ERR_BAD_ARG, "gating: negative token count");
+  DLB_CHECK_ARG(experts >= 1 && experts <= 512, DLB_ERR_UNSUPPORTED, "gating: experts=%d not in [1, 512]", experts);
+  DLB_CHECK_ARG(top_k >= 1 && top_k <= 32 && top_k <= experts, DLB_ERR_BAD_ARG, "gating: top_k=%d invalid", top_k);
+  DLB_CHECK_ARG(scoring == DLB_SCORE_SIGMOID || scoring == DLB_SCORE_SOFTMAX, DLB_ERR_BAD_ARG,
+                "gating: scoring=%d invalid", scoring);
+  DLB_CHECK_ARG(n_group >= 1 && topk_group >= 1 && topk_group <= n_group, DLB_ERR_BAD_ARG,
+                "gating: n_group=%d topk_group=%d invalid", n_group, topk_group);
+  DLB_CHECK_ARG(logits_row_stride >= experts, DLB_ERR_BAD_ARG, "gating: row stride smaller than experts");
+  if (tokens == 0) return DLB_OK;
+  DLB_CHECK_ARG(logits && ids && weights, DLB_ERR_BAD_ARG, "gating: null pointer");
+
+  int vpl = 1;
+  while (vpl * 32 < experts) vpl <<= 1;
+  if (n_group > 1) {
+    DLB_CHECK_ARG(experts % n_group == 0, DLB_ERR_BAD_ARG, "gating: experts %% n_group != 0");
+    const int gs = experts / n_group;
+    DLB_CHECK_ARG(gs % vpl == 0, DLB_ERR_UNSUPPORTED, "gating: group size %d not a multiple of %d lanes-worth", gs,
+                  vpl);
+    const int lpg = gs / vpl;
+    DLB_CHECK_ARG((lpg & (lpg - 1)) == 0 && lpg <= 32, DLB_ERR_UNSUPPORTED,
+                  "gating: group must span a power-of-two number of lanes (got %d)", lpg);
+    DLB_CHECK_ARG(top_k <= topk_group * gs, DLB_ERR_BAD_ARG, "gating: top_k exceeds experts in kept groups");
+    DLB_CHECK_ARG(gs >= 2, DLB_ERR_BAD_ARG, "gating: groups need at least two experts");
+  }
+  // 128-bit loads need 16-byte aligned rows
+  if (vpl >= 4) {
+    DLB_CHECK_ARG(((uintptr_t)logits & 15) == 0 && (logits_row_stride % 4) == 0, DLB_ERR_ALIGNMENT,
+                  "gating: logits rows must be 16-byte aligned");
+  }
+  GatingParams p{logits, bias, ids, weights, tokens, logits_row_stride, experts, n_group,
+                 topk_group, top_k, scoring, renormalize, scale};
+  const int warps = 8;
+  const int64_t blocks = (tokens + warps - 1) / warps;
+  DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gating: too many tokens");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (vpl) {
+    case 1: grouped_topk_kernel<1><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 2: grouped_topk_kernel<2><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 4: grouped_topk_kernel<4><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 8: grouped_topk_kernel<8><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    default: grouped_topk_kernel<16><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+  }
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}

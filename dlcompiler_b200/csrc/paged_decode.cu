@@ -1,0 +1,559 @@
+// Paged flash-decode: one query token per sequence against a paged KV cache,
+// split over the KV length, with a log-sum-exp merge.
+//
+// Same math as the reference's split-K decode path
+// (python/dlBLAS/dlblas/kernels/paged_attention.py:40-285): scores
+// q.k * sm_scale (optional tanh soft-cap, optional sliding window), online
+// softmax in fp32, P cast to the cache dtype before P.V, per-split partial
+// (acc, m, l) merged by rescaling with exp(m_s - m_max).  Differences are
+// structural only: the number of splits adapts to each sequence's length
+// (fixed `chunk` tokens per split instead of a fixed 4 splits), so a batch that
+// mixes 1k and 32k contexts keeps every SM busy.
+//
+// HBM-bound (about 4 FLOP per byte of KV), so the kernel is built around the
+// memory system: a producer lane walks the block table and issues TMA tile
+// loads (4-D tensor map over [page, slot, kv-head, d], 128-byte swizzle) into a
+// multi-stage shared-memory ring guarded by mbarriers; four consumer warps each
+// own 16 of the 64 keys of a tile and run mma.sync m16n8k16 with the
+// sequence's q-heads of one kv-head as the (zero-padded) M=16 rows, fed by
+// swizzle-aware ldmatrix.  Each KV byte is read from HBM exactly once.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace dlb {
+
+namespace pd {
+constexpr int TILE_KEYS = 64;
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
+constexpr int STAGES = 3;
+}  // namespace pd
+
+// Encode a 4-D tensor map over a paged cache [pages, slots, heads, d] (element
+// strides given), box = 64 x 1 x box_slots x 1, 128-byte swizzle.
+static int make_tmap_cache(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t slots,
+                           int64_t pages, int64_t stride_page, int64_t stride_slot, int64_t stride_head,
+                           int box_slots) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  DLB_CHECK_ARG(enc != nullptr, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  DLB_CHECK_ARG(((uintptr_t)base & 15) == 0, DLB_ERR_ALIGNMENT, "cache base is not 16-byte aligned");
+  DLB_CHECK_ARG((stride_page * 2) % 16 == 0 && (stride_slot * 2) % 16 == 0 && (stride_head * 2) % 16 == 0,
+                DLB_ERR_ALIGNMENT, "cache strides must be multiples of 16 bytes");
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)slots, (cuuint64_t)pages};
+  cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_slot * 2, (cuuint64_t)stride_page * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_slots, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DLB_CHECK_ARG(r == CUDA_SUCCESS, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled(cache) failed with CUresult %d", (int)r);
+  return DLB_OK;
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct DecodeParams {
+  const void* q;             // [B, Hq, D]
+  void* out;                 // [B, Hq, D]
+  float* partial;            // [B, Hq, max_splits, D + 2] fp32 (acc, m, l); unused when max_splits == 1
+  const void* block_table;   // [B, max_pages] int32 or int64
+  const void* kv_seqlens;    // [B] int32 or int64
+  int64_t q_stride_b, q_stride_h;
+  int64_t o_stride_b, o_stride_h;
+  int64_t bt_stride;
+  int batch, hq, hkv, group;
+  int page_size, max_pages, num_pages;
+  int chunk;                 // tokens per split (multiple of 64 and of the page size when page_size > 64)
+  int max_splits;
+  int window;                // <= 0: none
+  int table_is_int64, lens_is_int64;
+  float sm_scale, softcap;   // softcap <= 0: none
+  int* status;
+};
+
+__device__ __forceinline__ int load_index(const void* p, int64_t i, int is64) {
+  return is64 ? (int)reinterpret_cast<const int64_t*>(p)[i] : reinterpret_cast<const int32_t*>(p)[i];
+}
+
+// Token range [lo, hi) of split `s`; returns false if the split is empty.
+__device__ __forceinline__ bool split_range(int ctx, int window, int chunk, int s, int& lo, int& hi, int& kv_lo) {
+  kv_lo = (window > 0 && ctx > window) ? ctx - window : 0;
+  const int base = (kv_lo / pd::TILE_KEYS) * pd::TILE_KEYS;
+  lo = base + s * chunk;
+  hi = min(ctx, lo + chunk);
+  return lo < hi;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(pd::THREADS, 2)
+paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                          const DecodeParams p) {
+  using namespace pd;
+  constexpr int HALF_BYTES = TILE_KEYS * 128;         // one 64-key x 64-d swizzled box
+  constexpr int BOXES = D / 64;
+  constexpr int KV_BYTES = BOXES * HALF_BYTES;        // K (or V) tile
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + STAGES);
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y % p.hkv;
+  const int hblk = blockIdx.y / p.hkv;          // block of 16 q-heads inside the group
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int ctx = load_index(p.kv_seqlens, b, p.lens_is_int64);
+  int lo, hi, kv_lo;
+  if (!split_range(ctx, p.window, p.chunk, split, lo, hi, kv_lo)) {
+    // empty split: nothing to do, except that without a merge pass an empty context still owes zeros
+    if (p.max_splits == 1) {
+      const int rows = min(16, p.group - hblk * 16);
+      T* o = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b;
+      for (int idx = threadIdx.x; idx < rows * D; idx += pd::THREADS)
+        o[(int64_t)(kvh * p.group + hblk * 16 + idx / D) * p.o_stride_h + idx % D] = Elem<T>::from_f(0.f);
+    }
+    return;   // whole CTA leaves
+  }
+  const int n_tiles = (hi - lo + TILE_KEYS - 1) / TILE_KEYS;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], CONSUMER_WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int rows_valid = min(16, p.group - hblk * 16);   // q-heads handled by this CTA
+  const int head0 = kvh * p.group + hblk * 16;
+
+  // per-warp running state (consumer warps only)
+  float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
+  float l_run[2] = {0.f, 0.f};
+  float oacc[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oacc[t][j] = 0.f;
+
+  if (warp == CONSUMER_WARPS) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      const int keys_per_box = min(p.page_size, TILE_KEYS);
+      const int boxes_per_tile = TILE_KEYS / keys_per_box;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 11, t)) break;
+        uint8_t* kdst = smem + s * STAGE_BYTES;
+        uint8_t* vdst = kdst + KV_BYTES;
+        mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int tok0 = lo + t * TILE_KEYS;
+        for (int bx = 0; bx < boxes_per_tile; ++bx) {
+          const int tok = tok0 + bx * keys_per_box;
+          int page_slot = tok / p.page_size;
+          if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // tail boxes past the table: any valid page
+          int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
+          if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
+          const int slot0 = tok % p.page_size;
+#pragma unroll
+          for (int h = 0; h < BOXES; ++h) {
+            tma_load_4d(kdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_k, &full_bar[s], h * 64, kvh, slot0,
+                        page);
+            tma_load_4d(vdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_v, &full_bar[s], h * 64, kvh, slot0,
+                        page);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ consumers ------------------------------
+    const int r0 = lane >> 2;        // fragment row (q-head) 0..7, second row is r0 + 8
+    const int cq = (lane & 3) * 2;   // fragment column pair
+    // Q fragments straight from global memory (rows beyond the group are zero)
+    uint32_t qf[KSTEPS][4];
+    {
+      const T* qb = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = r0 + (j & 1) * 8;
+          const int col = ks * 16 + cq + (j >> 1) * 8;
+          uint32_t v = 0;
+          if (row < rows_valid) v = *reinterpret_cast<const uint32_t*>(qb + (int64_t)(head0 + row) * p.q_stride_h + col);
+          qf[ks][j] = v;
+        }
+      }
+    }
+    const float scale2 = p.sm_scale * 1.4426950408889634f;
+    const bool use_cap = p.softcap > 0.f;
+    const int mat = lane >> 3;      // ldmatrix: which 8x8 matrix this lane addresses
+    const int mrow = lane & 7;
+
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % STAGES;
+      const uint32_t ph = (t / STAGES) & 1;
+      bool ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, 12, t);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t kbase = smem_u32(smem + s * STAGE_BYTES);
+      const uint32_t vbase = kbase + KV_BYTES;
+      const int tok0 = lo + t * TILE_KEYS + warp * 16;   // first key of this warp's slice
+
+      // zero V rows past the context so that stale cache bits cannot poison P.V
+      if (tok0 + 16 > ctx) {
+        for (int i = lane; i < 16 * (D / 8); i += 32) {
+          const int key = i / (D / 8);
+          if (tok0 + key >= ctx) {
+            const int chunk16 = i % (D / 8);
+            const int krow = warp * 16 + key;
+            uint8_t* dst = smem + s * STAGE_BYTES + KV_BYTES + (chunk16 >> 3) * HALF_BYTES + krow * 128 +
+                           (((chunk16 & 7) ^ (krow & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T for this warp's 16 keys ----
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sacc[j][i] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int key = warp * 16 + (mat >> 1) * 8 + mrow;
+        const int ch = ks * 2 + (mat & 1);
+        const uint32_t addr = kbase + (ch >> 3) * HALF_BYTES + key * 128 + (((ch & 7) ^ (key & 7)) << 4);
+        uint32_t b00, b01, b10, b11;
+        ldmatrix_x4(addr, b00, b01, b10, b11);
+        mma_16816<T>(sacc[0], qf[ks], b00, b01);
+        mma_16816<T>(sacc[1], qf[ks], b10, b11);
+      }
+
+      // ---- scale, soft-cap, mask, online softmax (base-2 domain) ----
+      float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = tok0 + j * 8 + cq + (i & 1);
+          float v = sacc[j][i];
+          if (use_cap) v = p.softcap * tanhf(v * p.sm_scale / p.softcap) * 1.4426950408889634f;
+          else v *= scale2;
+          v = (key < ctx && key >= kv_lo) ? v : -CUDART_INF_F;
+          sacc[j][i] = v;
+          mx[i >> 1] = fmaxf(mx[i >> 1], v);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      }
+      float alpha[2];
+      bool grew = false;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        alpha[r] = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_run[r] - m_new);
+        grew |= (m_new > m_run[r]) && (m_run[r] != -CUDART_INF_F);
+        m_run[r] = m_new;
+      }
+      float psum[2] = {0.f, 0.f};
+      uint32_t pf[4];
+      {
+        float pv[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float mref = m_run[i >> 1];
+            const float e = (mref == -CUDART_INF_F) ? 0.f : exp2f(sacc[j][i] - mref);
+            pv[j][i] = e;
+            psum[i >> 1] += e;
+          }
+        pf[0] = pack_pair<T>(pv[0][0], pv[0][1]);
+        pf[1] = pack_pair<T>(pv[0][2], pv[0][3]);
+        pf[2] = pack_pair<T>(pv[1][0], pv[1][1]);
+        pf[3] = pack_pair<T>(pv[1][2], pv[1][3]);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) l_run[r] = l_run[r] * alpha[r] + psum[r];
+      if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt) {
+          oacc[tt][0] *= alpha[0];
+          oacc[tt][1] *= alpha[0];
+          oacc[tt][2] *= alpha[1];
+          oacc[tt][3] *= alpha[1];
+        }
+      }
+
+      // ---- O += P V ----
+#pragma unroll
+      for (int n = 0; n < D / 16; ++n) {
+        const int key = warp * 16 + (mat & 1) * 8 + mrow;
+        const int ch = n * 2 + (mat >> 1);
+        const uint32_t addr = vbase + (ch >> 3) * HALF_BYTES + key * 128 + (((ch & 7) ^ (key & 7)) << 4);
+        uint32_t v00, v01, v10, v11;
+        ldmatrix_x4_trans(addr, v00, v01, v10, v11);
+        mma_16816<T>(oacc[2 * n], pf, v00, v01);
+        mma_16816<T>(oacc[2 * n + 1], pf, v10, v11);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    // quad-reduce the row sums (each lane summed its own 4 keys per row)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+  }
+
+  // ------------------------------ cross-warp merge ------------------------------
+  __syncthreads();   // every TMA write has been consumed; the ring can be reused
+  float* red_o = reinterpret_cast<float*>(smem);                       // [warps][16][D]
+  float* red_m = red_o + CONSUMER_WARPS * 16 * D;                      // [warps][16]
+  float* red_l = red_m + CONSUMER_WARPS * 16;                          // [warps][16]
+  if (warp < CONSUMER_WARPS) {
+    const int r0 = lane >> 2;
+    const int cq = (lane & 3) * 2;
+#pragma unroll
+    for (int tt = 0; tt < NT; ++tt) {
+      float* o0 = red_o + (warp * 16 + r0) * D + tt * 8 + cq;
+      float* o1 = red_o + (warp * 16 + r0 + 8) * D + tt * 8 + cq;
+      o0[0] = oacc[tt][0];
+      o0[1] = oacc[tt][1];
+      o1[0] = oacc[tt][2];
+      o1[1] = oacc[tt][3];
+    }
+    if ((lane & 3) == 0) {
+      red_m[warp * 16 + r0] = m_run[0];
+      red_m[warp * 16 + r0 + 8] = m_run[1];
+      red_l[warp * 16 + r0] = l_run[0];
+      red_l[warp * 16 + r0 + 8] = l_run[1];
+    }
+  }
+  __syncthreads();
+  T* out = reinterpret_cast<T*>(p.out);
+  for (int idx = threadIdx.x; idx < rows_valid * D; idx += THREADS) {
+    const int row = idx / D;
+    const int d = idx - row * D;
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, red_m[w * 16 + row]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < CONSUMER_WARPS; ++w) {
+      const float mw = red_m[w * 16 + row];
+      const float sc = (mw == -CUDART_INF_F) ? 0.f : exp2f(mw - m);
+      acc += red_o[(w * 16 + row) * D + d] * sc;
+      l += red_l[w * 16 + row] * sc;
+    }
+    const int head = head0 + row;
+    if (p.max_splits == 1) {
+      out[(int64_t)b * p.o_stride_b + (int64_t)head * p.o_stride_h + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
+    } else {
+      float* dst = p.partial + (((int64_t)b * p.hq + head) * p.max_splits + split) * (D + 2);
+      dst[d] = acc;
+      if (d == 0) {
+        dst[D] = m;
+        dst[D + 1] = l;
+      }
+    }
+  }
+}
+
+// Merge the per-split partials of one (sequence, q-head): D threads.
+template <typename T, int D>
+__global__ void __launch_bounds__(D) paged_decode_merge_kernel(const DecodeParams p) {
+  const int head = blockIdx.x;
+  const int b = blockIdx.y;
+  const int d = threadIdx.x;
+  const int ctx = load_index(p.kv_seqlens, b, p.lens_is_int64);
+  T* out = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b + (int64_t)head * p.o_stride_h;
+  int lo, hi, kv_lo;
+  if (!split_range(ctx, p.window, p.chunk, 0, lo, hi, kv_lo)) {
+    out[d] = Elem<T>::from_f(0.f);
+    return;
+  }
+  const int n_splits = min(p.max_splits, (ctx - lo + p.chunk - 1) / p.chunk);
+  const float* src = p.partial + ((int64_t)b * p.hq + head) * p.max_splits * (D + 2);
+  float m = -CUDART_INF_F;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[s * (D + 2) + D]);
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = src[s * (D + 2) + D];
+    const float sc = (ms == -CUDART_INF_F) ? 0.f : exp2f(ms - m);
+    acc += src[s * (D + 2) + d] * sc;
+    l += src[s * (D + 2) + D + 1] * sc;
+  }
+  out[d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
+}
+
+template <typename T, int D>
+static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeParams& p, cudaStream_t stream) {
+  using namespace pd;
+  constexpr int STAGE_BYTES = 2 * (D / 64) * TILE_KEYS * 128;
+  constexpr int RED_BYTES = CONSUMER_WARPS * 16 * (D + 2) * 4;
+  constexpr int RING = STAGES * STAGE_BYTES;
+  constexpr int SMEM = (RING > RED_BYTES ? RING : RED_BYTES) + 1024 + 128;
+  auto kern = paged_decode_split_kernel<T, D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) {
+    set_last_error("paged_decode: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  const int hblocks = (p.group + 15) / 16;
+  dim3 grid(p.max_splits, p.hkv * hblocks, p.batch);
+  kern<<<grid, THREADS, SMEM, stream>>>(tk, tv, p);
+  DLB_CUDA_LAUNCH_CHECK();
+  if (p.max_splits > 1) {
+    paged_decode_merge_kernel<T, D><<<dim3(p.hq, p.batch), D, 0, stream>>>(p);
+    DLB_CUDA_LAUNCH_CHECK();
+  }
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+extern "C" int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t head_dim,
+                                                     int64_t max_splits) {
+  return max_splits <= 1 ? 0 : batch * hq * max_splits * (head_dim + 2);
+}
+
+extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                const void* block_table, const void* kv_seqlens, float* partial, int64_t batch,
+                                int64_t hq, int64_t hkv, int64_t head_dim, int64_t page_size, int64_t num_pages,
+                                int64_t max_pages, int64_t q_stride_b, int64_t q_stride_h, int64_t o_stride_b,
+                                int64_t o_stride_h, int64_t k_stride_page, int64_t k_stride_slot,
+                                int64_t k_stride_head, int64_t v_stride_page, int64_t v_stride_slot,
+                                int64_t v_stride_head, int64_t bt_stride, int table_is_int64, int lens_is_int64,
+                                int64_t chunk, int64_t max_splits, int64_t window, float sm_scale, float softcap,
+                                int dtype, int32_t* status, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
+                "paged_decode: dtype %d (need fp16 or bf16)", dtype);
+  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
+                "paged_decode: head_dim %lld not supported (64 or 128)", (long long)head_dim);
+  DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "paged_decode: bad head counts");
+  DLB_CHECK_ARG(page_size >= 16 && (page_size & (page_size - 1)) == 0, DLB_ERR_UNSUPPORTED,
+                "paged_decode: page size %lld must be a power of two >= 16", (long long)page_size);
+  DLB_CHECK_ARG(chunk >= 64 && chunk % 64 == 0 && chunk % page_size == 0, DLB_ERR_BAD_ARG,
+                "paged_decode: chunk %lld must be a multiple of 64 and of the page size", (long long)chunk);
+  DLB_CHECK_ARG(max_splits >= 1 && max_splits <= 65535, DLB_ERR_BAD_ARG, "paged_decode: max_splits out of range");
+  DLB_CHECK_ARG(max_splits == 1 || partial != nullptr, DLB_ERR_BAD_ARG, "paged_decode: workspace missing");
+  DLB_CHECK_ARG(max_pages >= 1 && num_pages >= 1, DLB_ERR_BAD_ARG, "paged_decode: empty block table or cache");
+  DLB_CHECK_ARG(batch <= 65535 && hkv * ((hq / hkv + 15) / 16) <= 65535, DLB_ERR_TOO_LARGE,
+                "paged_decode: grid too large");
+  if (batch == 0) return DLB_OK;
+  DLB_CHECK_ARG(q && k_cache && v_cache && out && block_table && kv_seqlens, DLB_ERR_BAD_ARG,
+                "paged_decode: null pointer");
+  DLB_CHECK_ARG(q_stride_h % 2 == 0 && q_stride_b % 2 == 0 && ((uintptr_t)q & 3) == 0, DLB_ERR_ALIGNMENT,
+                "paged_decode: q must be 4-byte aligned with even strides");
+  const int box_slots = (int)(page_size < 64 ? page_size : 64);
+  CUtensorMap tk, tv;
+  int rc = make_tmap_cache(&tk, k_cache, head_dim, hkv, page_size, num_pages, k_stride_page, k_stride_slot,
+                           k_stride_head, box_slots);
+  if (rc != DLB_OK) return rc;
+  rc = make_tmap_cache(&tv, v_cache, head_dim, hkv, page_size, num_pages, v_stride_page, v_stride_slot,
+                       v_stride_head, box_slots);
+  if (rc != DLB_OK) return rc;
+
+  DecodeParams p;
+  p.q = q;
+  p.out = out;
+  p.partial = partial;
+  p.block_table = block_table;
+  p.kv_seqlens = kv_seqlens;
+  p.q_stride_b = q_stride_b;
+  p.q_stride_h = q_stride_h;
+  p.o_stride_b = o_stride_b;
+  p.o_stride_h = o_stride_h;
+  p.bt_stride = bt_stride;
+  p.batch = (int)batch;
+  p.hq = (int)hq;
+  p.hkv = (int)hkv;
+  p.group = (int)(hq / hkv);
+  p.page_size = (int)page_size;
+  p.max_pages = (int)max_pages;
+  p.num_pages = (int)num_pages;
+  p.chunk = (int)chunk;
+  p.max_splits = (int)max_splits;
+  p.window = (int)window;
+  p.table_is_int64 = table_is_int64;
+  p.lens_is_int64 = lens_is_int64;
+  p.sm_scale = sm_scale;
+  p.softcap = softcap;
+  p.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DLB_DTYPE_BF16) {
+    return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(tk, tv, p, s)
+                           : launch_decode<__nv_bfloat16, 64>(tk, tv, p, s);
+  }
+  return head_dim == 128 ? launch_decode<__half, 128>(tk, tv, p, s) : launch_decode<__half, 64>(tk, tv, p, s);
+}

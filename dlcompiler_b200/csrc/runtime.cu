@@ -1,0 +1,82 @@
+// Host-side runtime shared by all entry points of libdlblas_b200:
+// error message storage, cached device properties, tensor-map encoding.
+// The library never allocates or frees device memory.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace dlb {
+
+static thread_local char g_last_error[512] = {0};
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev;
+}
+
+int sm_count(int device) {
+  static int cache[64];
+  static std::once_flag once[64];
+  if (device < 0 || device >= 64) return 148;
+  std::call_once(once[device], [device]() {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cache[device] = n;
+  });
+  return cache[device];
+}
+
+PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = (PFN_encodeTiled)p;
+    }
+  });
+  return fn;
+}
+
+int make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                     uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  DLB_CHECK_ARG(enc != nullptr, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  DLB_CHECK_ARG(((uintptr_t)base & 15) == 0, DLB_ERR_ALIGNMENT, "tensor base %p is not 16-byte aligned", base);
+  DLB_CHECK_ARG((row_stride_bytes & 15) == 0, DLB_ERR_ALIGNMENT, "row stride %llu B is not a multiple of 16",
+                (unsigned long long)row_stride_bytes);
+  DLB_CHECK_ARG(box_inner * 2 == 128, DLB_ERR_BAD_ARG, "128-byte swizzle needs a 128-byte inner box");
+  DLB_CHECK_ARG(box_outer >= 1 && box_outer <= 256, DLB_ERR_BAD_ARG, "box_outer %u out of range", box_outer);
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DLB_CHECK_ARG(r == CUDA_SUCCESS, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+extern "C" {
+
+int dlb_version(void) { return 100; }
+
+const char* dlb_last_error(void) { return dlb::g_last_error; }
+
+}  // extern "C"

@@ -1,0 +1,133 @@
+// silu_and_mul: out[t, i] = silu(x[t, i]) * x[t, N + i]
+//
+// Mirrors dlblas/kernels/activation.py:17-85 (reference Triton kernels): the
+// gate is the first half of each row, the math runs in fp32
+// (g / (1 + exp(-g)) * u) and the result is rounded once on store.
+//
+// HBM-bound streaming kernel: 3 * N * elemsize bytes per row.  Each thread
+// moves 128-bit vectors (8 x 16-bit elements) with streaming cache hints; a
+// thread owns UNROLL vectors spaced one block apart so that a warp's accesses
+// stay fully coalesced and several loads are in flight per thread.
+#include "common.cuh"
+
+namespace dlb {
+
+template <typename T> __device__ __forceinline__ float silu_mul_f32(float g, float u) {
+  return g / (1.0f + __expf(-g)) * u;
+}
+
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                               int64_t rows, int nvec /* N / 8 */,
+                                                               int64_t x_row_stride, int64_t out_row_stride,
+                                                               int n) {
+  using T2 = typename Elem<T>::T2;
+  const int64_t total = rows * (int64_t)nvec;
+  const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
+
+  uint4 g[UNROLL], u[UNROLL];
+  int64_t orow[UNROLL];
+  int ocol[UNROLL];
+#pragma unroll
+  for (int i = 0; i < UNROLL; ++i) {
+    const int64_t v = base + (int64_t)i * blockDim.x;
+    if (v < total) {
+      const int64_t r = v / nvec;
+      const int c = (int)(v - r * nvec);
+      orow[i] = r;
+      ocol[i] = c;
+      const uint4* gp = reinterpret_cast<const uint4*>(x + r * x_row_stride) + c;
+      const uint4* up = reinterpret_cast<const uint4*>(x + r * x_row_stride + n) + c;
+      g[i] = __ldcs(gp);
+      u[i] = __ldcs(up);
+    } else {
+      orow[i] = -1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < UNROLL; ++i) {
+    if (orow[i] < 0) continue;
+    uint4 o;
+    const T2* g2 = reinterpret_cast<const T2*>(&g[i]);
+    const T2* u2 = reinterpret_cast<const T2*>(&u[i]);
+    T2* o2 = reinterpret_cast<T2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 gf = Elem<T>::to_f2(g2[j]);
+      const float2 uf = Elem<T>::to_f2(u2[j]);
+      o2[j] = Elem<T>::from_f2(silu_mul_f32<T>(gf.x, uf.x), silu_mul_f32<T>(gf.y, uf.y));
+    }
+    __stcs(reinterpret_cast<uint4*>(out + orow[i] * out_row_stride) + ocol[i], o);
+  }
+}
+
+// Generic fallback for shapes/strides that do not allow 128-bit accesses
+// (N not a multiple of the vector width, unaligned rows, fp32 data).
+template <typename T>
+__global__ void __launch_bounds__(256) silu_and_mul_scalar_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                                  int64_t rows, int n, int64_t x_row_stride,
+                                                                  int64_t out_row_stride) {
+  const int64_t total = rows * (int64_t)n;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / n;
+    const int c = (int)(idx - r * n);
+    const float g = Elem<T>::to_f(x[r * x_row_stride + c]);
+    const float u = Elem<T>::to_f(x[r * x_row_stride + n + c]);
+    out[r * out_row_stride + c] = Elem<T>::from_f(silu_mul_f32<T>(g, u));
+  }
+}
+
+template <typename T>
+static int launch_silu(const void* x, void* out, int64_t rows, int n, int64_t xs, int64_t os, cudaStream_t stream) {
+  constexpr int VEC = 16 / sizeof(T);
+  const bool vec_ok = (sizeof(T) == 2) && (n % VEC == 0) && (xs % VEC == 0) && (os % VEC == 0) &&
+                      (((uintptr_t)x & 15) == 0) && (((uintptr_t)out & 15) == 0);
+  if (vec_ok) {
+    if constexpr (sizeof(T) == 2) {
+      constexpr int UNROLL = 4;
+      const int nvec = n / VEC;
+      const int64_t total = rows * (int64_t)nvec;
+      const int64_t per_block = 256 * UNROLL;
+      const int64_t blocks = (total + per_block - 1) / per_block;
+      DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "silu_and_mul: too many blocks");
+      silu_and_mul_vec_kernel<T, UNROLL><<<(unsigned)blocks, 256, 0, stream>>>(
+          (const T*)x, (T*)out, rows, nvec, xs, os, n);
+    }
+  } else {
+    const int64_t total = rows * (int64_t)n;
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count(current_device()) * 32;
+    if (blocks > cap) blocks = cap;
+    silu_and_mul_scalar_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, (T*)out, rows, n, xs, os);
+  }
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+extern "C" int dlb_silu_and_mul(const void* gate_up, void* out, int64_t rows, int64_t n,
+                                int64_t gate_up_row_stride, int64_t out_row_stride, int dtype,
+                                void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(rows >= 0 && n >= 0, DLB_ERR_BAD_ARG, "silu_and_mul: negative size");
+  DLB_CHECK_ARG(n <= 0x3fffffff, DLB_ERR_TOO_LARGE, "silu_and_mul: N=%lld too large", (long long)n);
+  if (rows == 0 || n == 0) return DLB_OK;
+  DLB_CHECK_ARG(gate_up != nullptr && out != nullptr, DLB_ERR_BAD_ARG, "silu_and_mul: null pointer");
+  DLB_CHECK_ARG(gate_up_row_stride >= 2 * n && out_row_stride >= n, DLB_ERR_BAD_ARG,
+                "silu_and_mul: row strides (%lld, %lld) smaller than the row", (long long)gate_up_row_stride,
+                (long long)out_row_stride);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dtype) {
+    case DLB_DTYPE_BF16:
+      return launch_silu<__nv_bfloat16>(gate_up, out, rows, (int)n, gate_up_row_stride, out_row_stride, s);
+    case DLB_DTYPE_F16:
+      return launch_silu<__half>(gate_up, out, rows, (int)n, gate_up_row_stride, out_row_stride, s);
+    case DLB_DTYPE_F32:
+      return launch_silu<float>(gate_up, out, rows, (int)n, gate_up_row_stride, out_row_stride, s);
+    default:
+      set_last_error("silu_and_mul: unsupported dtype %d", dtype);
+      return DLB_ERR_UNSUPPORTED;
+  }
+}

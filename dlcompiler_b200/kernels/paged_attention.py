@@ -1,0 +1,90 @@
+"""paged_attention_fwd with the signature of python/dlBLAS/dlblas/kernels/paged_attention.py:492."""
+from __future__ import annotations
+
+import logging
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+
+logger = logging.getLogger("dlblas")
+
+_TARGET_CTAS = 148 * 2 * 16  # split work items aimed at per launch (16 waves of 2 CTAs per SM)
+
+
+def _pick_chunk(batch: int, kv_heads: int, max_ctx: int, page_size: int) -> int:
+    """Tokens per KV split: a power of two, at least one 64-key tile and one page."""
+    want = max(1, batch * kv_heads * max_ctx // _TARGET_CTAS)
+    chunk = 1 << (want.bit_length() - 1)
+    lo = max(256, page_size)
+    return max(lo, min(chunk, 4096))
+
+
+def paged_attention_fwd(
+    q: Tensor,
+    k: Tensor,
+    v: Tensor,
+    o: Tensor,
+    block_offsets: Tensor,
+    q_start_loc: Tensor,
+    q_seqlens: Tensor,
+    kv_seqlens: Tensor,
+    max_seqlen: int,
+    window_size: int = None,
+    sm_scale: float = None,
+    logit_softcapping: float = None,
+):
+    """Paged attention forward, decode case (one query token per sequence).
+
+    Args follow the reference (paged_attention.py:492-519): `q` [batch, Hq, D], caches
+    `k`/`v` [num_pages, page_size, Hkv, D], `o` written in place, `block_offsets`
+    [batch, max_pages] page ids (int32 or int64), `kv_seqlens` [batch].  The KV length is
+    split in fixed-size chunks (count adapts to each sequence) and merged by log-sum-exp.
+    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power
+    of two >= 16, decode only (q_seqlens all 1).
+    """
+    dev = _lib.require_cuda(q, k, v, o, block_offsets, kv_seqlens)
+    if window_size is None:
+        window_size = -1
+    if logit_softcapping is None:
+        logit_softcapping = -1.0
+    Lq, Lk, Lv = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert Lq == Lk, Lv == o.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / (Lq**0.5)
+    batch, head = q_seqlens.shape[0], q.shape[-2]
+    BLOCK = k.size(1)
+    assert BLOCK >= 16
+    is_decoding = q.shape[-3] == q_seqlens.size(0)
+    if not is_decoding:
+        raise NotImplementedError("paged prefill with history is outside this implementation (decode only)")
+    assert Lk == Lv, "decode kernel needs equal K and V head sizes"
+    assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert q.stride(-1) == 1 and o.stride(-1) == 1
+    assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
+    assert block_offsets.dtype in (torch.int32, torch.int64) and kv_seqlens.dtype in (torch.int32, torch.int64)
+    kv_seqlens = kv_seqlens.contiguous()
+    hkv = k.shape[-2]
+    max_pages = block_offsets.size(1)
+    max_ctx = max_pages * BLOCK
+    chunk = _pick_chunk(batch, hkv, max_ctx, BLOCK)
+    max_splits = (max_ctx + chunk - 1) // chunk
+    if window_size > 0:
+        # a window touches at most window + one tile of alignment slack
+        max_splits = min(max_splits, (window_size + 64 + chunk - 1) // chunk + 1)
+    lib = _lib.load()
+    nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, Lq, max_splits)
+    partial = torch.empty(max(nfloats, 1), dtype=torch.float32, device=dev)
+    status = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        rc = lib.dlb_paged_decode(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), block_offsets.data_ptr(), kv_seqlens.data_ptr(),
+            partial.data_ptr(), batch, head, hkv, Lq, BLOCK, k.size(0), max_pages,
+            q.stride(-3), q.stride(-2), o.stride(-3), o.stride(-2),
+            k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
+            block_offsets.stride(0), int(block_offsets.dtype == torch.int64), int(kv_seqlens.dtype == torch.int64),
+            chunk, max_splits, window_size, float(sm_scale), float(logit_softcapping), _lib.dtype_code(q),
+            status.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "paged_attention_fwd(decode)")
+    return o

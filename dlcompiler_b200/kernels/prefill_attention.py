@@ -1,0 +1,42 @@
+"""context_attention_fwd with the signature of python/dlBLAS/dlblas/kernels/prefill_attention.py:155."""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+
+
+def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse=None, causal=True,
+                          sm_scale=None):
+    """Variable-length causal GQA attention over packed sequences, written to `o` in place.
+
+    q [total, Hq, D], k/v [total, Hkv, D]; sequence i occupies rows
+    [b_start_loc[i], b_start_loc[i] + b_seq_len[i]).  sm_scale defaults to D**-0.5 as in the
+    reference (prefill_attention.py:157).  Extension over the reference: if `lse` (fp32
+    [Hq, total]) is given it receives m * sm_scale + log(sum), the natural-log convention of
+    python/dlBLAS/dlblas/kernels/flash_attention.py:152-155.
+    """
+    dev = _lib.require_cuda(q, k, v, o, b_start_loc, b_seq_len, lse)
+    assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3 and o.shape == q.shape
+    Lq, Lk, Lv = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert Lq == Lk == Lv
+    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and o.stride(-1) == 1
+    if sm_scale is None:
+        sm_scale = 1.0 / (Lq**0.5)
+    batch, head = b_seq_len.shape[0], q.shape[1]
+    assert head % k.shape[1] == 0
+    b_start_loc = b_start_loc.to(torch.int32).contiguous()
+    b_seq_len = b_seq_len.to(torch.int32).contiguous()
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.shape == (head, q.shape[0]) and lse.is_contiguous()
+    lib = _lib.load()
+    status = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        rc = lib.dlb_flash_prefill_varlen(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), _lib.ptr(lse), b_start_loc.data_ptr(),
+            b_seq_len.data_ptr(), batch, q.shape[0], int(max_input_len), head, k.shape[1], Lq,
+            q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), o.stride(0), o.stride(1),
+            float(sm_scale), int(causal), _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "context_attention_fwd")
+    return o

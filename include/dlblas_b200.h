@@ -1,0 +1,125 @@
+/*
+ * libdlblas_b200 -- C ABI of the B200 (sm_100a) kernels behind the dlBLAS hot-path ops.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer unless stated,
+ *     owned by the caller; the library never allocates, frees or retains device memory;
+ *   - strides are in ELEMENTS; the innermost dimension is contiguous;
+ *   - `stream` is a cudaStream_t passed as void*; the call only enqueues work;
+ *   - return value: 0 ok, < 0 argument/support error (text in dlb_last_error()),
+ *     > 0 a cudaError_t from the launch;
+ *   - `status` (optional, may be NULL) is a device int32[4] the tensor-core kernels
+ *     write if one of their bounded waits gives up:
+ *     {code (0 = none, 1 = wait timed out), wait site, block index, tile}.
+ *
+ * Paths below are relative to the reference project root (DeepLink-org/DLCompiler).
+ */
+#ifndef DLBLAS_B200_H
+#define DLBLAS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DLB_DTYPE_F16 0
+#define DLB_DTYPE_BF16 1
+#define DLB_DTYPE_F32 2
+
+#define DLB_SCORE_SIGMOID 0
+#define DLB_SCORE_SOFTMAX 1
+
+#define DLB_GEMM_FUSE_SILU 1 /* B = [gate; up] halves, store silu(gate) * up */
+#define DLB_GEMM_WEIGHT 2    /* scale each row by its routing weight (fp32) before the cast */
+#define DLB_GEMM_SCATTER 4   /* write row p to row sorted_token_ids[p] of the output */
+
+/* Library version (major * 100 + minor). */
+int dlb_version(void);
+/* Text of the last error raised on the calling thread. */
+const char* dlb_last_error(void);
+
+/* silu_and_mul: out[t, i] = silu(x[t, i]) * x[t, n + i], fp32 math, one rounding.
+ * Replaces python/dlBLAS/dlblas/kernels/activation.py:88-130 (wrapper) and :17-85 (kernels). */
+int dlb_silu_and_mul(const void* gate_up, void* out, int64_t rows, int64_t n, int64_t gate_up_row_stride,
+                     int64_t out_row_stride, int dtype, void* stream);
+
+/* Router.  scoring = sigmoid/softmax over `experts` fp32 logits per token; optional per-expert
+ * selection bias; optional group-limited selection (n_group groups, score = sum of the group's two
+ * largest biased scores, keep topk_group groups); top_k experts by biased score (ties: lower index,
+ * output in descending order); weights = un-biased scores, optionally renormalised, times `scale`.
+ * The reference computes its routers in torch (python/dlBLAS/tests/kernels/test_fused_moe.py:207-218,
+ * softmax -> topk) or with the capacity-based topk_gating family
+ * (python/dlBLAS/dlblas/kernels/topk_gating.py:259-290); the group-limited sigmoid form has no
+ * counterpart in the reference. */
+int dlb_grouped_topk_gating(const float* logits, const float* bias, int32_t* ids, float* weights, int64_t tokens,
+                            int experts, int64_t logits_row_stride, int n_group, int topk_group, int top_k,
+                            int scoring, int renormalize, float scale, void* stream);
+
+/* moe_align_block_size: stable counting sort of the numel (token, k) slots by expert id, each expert
+ * segment padded to a multiple of `block` with the sentinel `numel`.  Block-padded form of the
+ * reference's argsort + [start, end) ranges
+ * (python/dlBLAS/dlblas/kernels/fused_moe.py:314-320, :267-293, kernel :238-264).
+ *   sorted_token_ids  int32[sorted_capacity],  sorted_capacity  >= numel + experts * (block - 1)
+ *   expert_ids        int32[expert_ids_capacity], >= ceil(sorted_capacity / block); unused = -1
+ *   num_tokens_post_padded int32[1]
+ *   block_start       int32[experts + 1], first block of each expert (prefix sum of blocks) */
+int dlb_moe_align_block_size(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts, int block,
+                             int32_t* sorted_token_ids, int64_t sorted_capacity, int32_t* expert_ids,
+                             int64_t expert_ids_capacity, int32_t* num_tokens_post_padded, int32_t* block_start,
+                             void* stream);
+
+/* dst[p, :] = src[sorted_token_ids[p] / top_k, :] for p < num_tokens_post_padded (zeros for sentinel
+ * rows).  The gather the reference does inside its GEMM by pointer arithmetic (reindex_a,
+ * python/dlBLAS/dlblas/kernels/fused_moe.py:136-140), as a separate pass so the GEMM can use TMA. */
+int dlb_moe_permute_rows(const void* src, void* dst, const int32_t* sorted_token_ids,
+                         const int32_t* num_tokens_post_padded, int64_t numel, int top_k, int64_t hidden,
+                         int64_t src_row_stride, int64_t sorted_capacity, int elem_size, void* stream);
+
+/* Grouped GEMM over the block-padded row list: for every 128-row block b,
+ * out[rows of b] = A[rows of b] @ B[expert of b]^T (fp32 accumulate), with the epilogue chosen by
+ * `flags` (DLB_GEMM_*).  A is [a_rows, k] with a_rows a multiple of 128, B is
+ * [num_experts * rows_per_expert, k].  Replaces fused_moe_kernel and its launcher,
+ * python/dlBLAS/dlblas/kernels/fused_moe.py:77-175 and :178-235. */
+int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b, int num_experts,
+                         int64_t rows_per_expert, int64_t k, int64_t b_row_stride, void* out,
+                         int64_t out_row_stride, int64_t n_out, const int32_t* sorted_token_ids,
+                         const int32_t* block_start, const float* topk_weights, int64_t numel, int flags,
+                         int dtype, int32_t* status, void* stream);
+
+/* out[t, :] = sum over k of partial[t * top_k + k, :] (fp32 accumulate, one rounding): the
+ * `intermediate_cache2.sum(dim=1)` of python/dlBLAS/dlblas/kernels/fused_moe.py:375. */
+int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
+                    int64_t out_row_stride, int dtype, void* stream);
+
+/* Varlen causal GQA flash-attention prefill.  q [total, hq, d], k/v [total, hkv, d], out like q,
+ * lse (optional, may be NULL) fp32 [hq, total] = m * sm_scale + log(sum) in natural log.
+ * Replaces context_attention_fwd, python/dlBLAS/dlblas/kernels/prefill_attention.py:155-181
+ * (kernel :28-152); LSE convention of python/dlBLAS/dlblas/kernels/flash_attention.py:152-155. */
+int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
+                             const int32_t* b_start_loc, const int32_t* b_seq_len, int64_t batch,
+                             int64_t total_tokens, int64_t max_seq_len, int64_t hq, int64_t hkv, int64_t head_dim,
+                             int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
+                             int64_t v_stride_t, int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h,
+                             float sm_scale, int causal, int dtype, int32_t* status, void* stream);
+
+/* Number of fp32 elements of the split-KV workspace dlb_paged_decode needs (0 when max_splits == 1). */
+int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t head_dim, int64_t max_splits);
+
+/* Paged flash-decode (one query token per sequence), split over the KV length in `chunk`-token
+ * pieces with a log-sum-exp merge.  Caches are [num_pages, page_size, hkv, d]; block_table is
+ * [batch, max_pages] (int32 or int64).  Replaces the decode branch of paged_attention_fwd,
+ * python/dlBLAS/dlblas/kernels/paged_attention.py:492-671 (kernels :40-285). */
+int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* block_table,
+                     const void* kv_seqlens, float* partial, int64_t batch, int64_t hq, int64_t hkv,
+                     int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages, int64_t q_stride_b,
+                     int64_t q_stride_h, int64_t o_stride_b, int64_t o_stride_h, int64_t k_stride_page,
+                     int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page, int64_t v_stride_slot,
+                     int64_t v_stride_head, int64_t bt_stride, int table_is_int64, int lens_is_int64, int64_t chunk,
+                     int64_t max_splits, int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLBLAS_B200_H */

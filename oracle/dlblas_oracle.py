@@ -1,0 +1,329 @@
+"""CPU oracle for the dlBLAS hot-path operators.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain torch on the CPU, the ground-truth code that the
+reference's own tests use for each operator (citations below are paths inside
+the reference project, DeepLink-org/DLCompiler).  It is the checker for the
+CUDA kernels and the timed CPU baseline of the benchmark; nothing in the
+shipped package imports it and it must never be used as a compute path.
+
+Parity status
+  pinned   silu_and_mul, fused_moe (launcher and end-to-end), varlen prefill
+           attention, paged decode attention: checked against fixtures produced
+           by executing the reference tests' own ground-truth functions
+           (tests/golden/make_golden.py, tests/golden/*.pt).
+  UNPINNED grouped_topk_gating (group-limited sigmoid routing) and
+           moe_align_block_size: the reference contains neither, so these two
+           restate the definitions written in this file; "parity unpinned".
+           The LSE output of prefill is pinned only through its formula
+           (python/dlBLAS/dlblas/kernels/flash_attention.py:152-155).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------------------------
+# silu_and_mul
+# --------------------------------------------------------------------------------------
+def silu_and_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """Test ground truth, python/dlBLAS/tests/kernels/test_activation.py:22-25:
+    silu on the first half times the second half, evaluated in the input dtype."""
+    n = gate_up.size(-1) // 2
+    gate, up = gate_up[..., :n], gate_up[..., n:]
+    return F.silu(gate) * up
+
+
+def silu_and_mul_fp32(gate_up: torch.Tensor) -> torch.Tensor:
+    """Kernel-faithful form: fp32 math, one rounding on store
+    (python/dlBLAS/dlblas/kernels/activation.py:73-85; same as the swiglu ground truth of
+    test/ascend/passed_tests/test_swiglu.py:31-35)."""
+    n = gate_up.size(-1) // 2
+    g = gate_up[..., :n].float()
+    u = gate_up[..., n:].float()
+    return (g / (1.0 + torch.exp(-g)) * u).to(gate_up.dtype)
+
+
+# --------------------------------------------------------------------------------------
+# routers
+# --------------------------------------------------------------------------------------
+def _stable_topk(scores: torch.Tensor, k: int):
+    """Largest k along the last dim, ties to the LOWER index, descending order.
+    (torch.topk on CPU does not guarantee the tie order, a stable descending sort does.)"""
+    vals, idx = torch.sort(scores, dim=-1, descending=True, stable=True)
+    return vals[..., :k], idx[..., :k]
+
+
+def grouped_topk_gating(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, n_group: int = 1,
+                        topk_group: int = 1, routed_scaling_factor: float = 1.0, renormalize: bool = True,
+                        scoring_func: str = "sigmoid"):
+    """Group-limited top-k routing (UNPINNED: no reference implementation exists).
+
+    Definition: scores = sigmoid(logits) or softmax(logits) in fp32; choice = scores + bias;
+    group score = sum of the 2 largest `choice` in each of the n_group equal groups; keep the
+    topk_group best groups (ties: lower group index); experts of other groups get -inf;
+    select top_k experts by `choice` (ties: lower expert index, output sorted by descending
+    `choice`); weights = scores[ids], / (sum + 1e-20) if renormalize, * routed_scaling_factor.
+    Returns (ids int32 [T, k], weights fp32 [T, k]).
+    """
+    logits = logits.float()
+    T, E = logits.shape
+    scores = torch.sigmoid(logits) if scoring_func == "sigmoid" else torch.softmax(logits, dim=-1)
+    choice = scores + bias.float().unsqueeze(0) if bias is not None else scores.clone()
+    if n_group > 1:
+        grp = choice.view(T, n_group, E // n_group)
+        g_scores = _stable_topk(grp, 2)[0].sum(dim=-1)                      # [T, n_group]
+        _, g_idx = _stable_topk(g_scores, topk_group)
+        g_mask = torch.zeros_like(g_scores, dtype=torch.bool)
+        g_mask.scatter_(1, g_idx, True)
+        e_mask = g_mask.unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E)
+        choice = choice.masked_fill(~e_mask, float("-inf"))
+    _, ids = _stable_topk(choice, top_k)
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    w = w * routed_scaling_factor
+    return ids.to(torch.int32), w
+
+
+def gating_margins(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, n_group: int, topk_group: int):
+    """float64 decision margins of grouped sigmoid routing, per token.
+
+    Returns the smallest gap, over the three decision layers (which groups are kept, which
+    experts are selected, and the order of the selected experts), between two quantities
+    whose comparison decides an output id.  If the minimum over all tokens is far above
+    fp32 rounding noise (~1e-7), every correct implementation must return the same ids.
+    """
+    x = logits.double()
+    T, E = x.shape
+    s = torch.sigmoid(x)
+    c = s + (bias.double().unsqueeze(0) if bias is not None else 0.0)
+    margins = []
+    if n_group > 1:
+        grp = c.view(T, n_group, E // n_group)
+        gs = torch.sort(grp, dim=-1, descending=True)[0][..., :2].sum(-1)
+        gsort = torch.sort(gs, dim=-1, descending=True)[0]
+        if topk_group < n_group:
+            margins.append(gsort[:, topk_group - 1] - gsort[:, topk_group])
+        gidx = torch.sort(gs, dim=-1, descending=True, stable=True)[1][:, :topk_group]
+        gm = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, gidx, True)
+        em = gm.unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E)
+        c = c.masked_fill(~em, float("-inf"))
+    cs = torch.sort(c, dim=-1, descending=True)[0]
+    gaps = cs[:, :top_k] - cs[:, 1:top_k + 1]
+    gaps = torch.where(torch.isfinite(gaps), gaps, torch.full_like(gaps, float("inf")))
+    margins.append(gaps.min(dim=-1)[0])
+    return torch.stack(margins, 0).min(dim=0)[0]
+
+
+def softmax_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = False):
+    """Router of python/dlBLAS/tests/kernels/test_fused_moe.py:207-218: softmax in fp32, then top-k."""
+    ids, w = grouped_topk_gating(router_logits, None, top_k, 1, 1, 1.0, renormalize, "softmax")
+    return w, ids
+
+
+# --------------------------------------------------------------------------------------
+# moe_align_block_size
+# --------------------------------------------------------------------------------------
+def moe_align_block_size(topk_ids: torch.Tensor, block: int, num_experts: int):
+    """Block-padded counting sort of the slots by expert (UNPINNED: absent from the reference).
+
+    Conventions fixed here: sorted_token_ids has numel + num_experts*(block-1) entries rounded
+    up to a multiple of `block`, filled with the sentinel `numel`; within an expert the slots
+    are in ascending index order; expert_ids has capacity/block entries, -1 when unused; ids
+    outside [0, num_experts) are dropped.  The reference's equivalent is argsort plus
+    per-expert [start, end) ranges (python/dlBLAS/dlblas/kernels/fused_moe.py:314-320,
+    267-293); `start_end_from_align` converts to that form.
+    Returns (sorted_token_ids, expert_ids, num_tokens_post_padded, block_start) as int32.
+    """
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    numel = flat.numel()
+    cap = numel + num_experts * (block - 1)
+    cap = (cap + block - 1) // block * block
+    sorted_ids = torch.full((cap,), numel, dtype=torch.int32)
+    expert_ids = torch.full((max(cap // block, 1),), -1, dtype=torch.int32)
+    block_start = torch.zeros(num_experts + 1, dtype=torch.int32)
+    pos = 0
+    blk = 0
+    for e in range(num_experts):
+        block_start[e] = blk
+        slots = torch.nonzero(flat == e).flatten()
+        n = slots.numel()
+        sorted_ids[pos:pos + n] = slots.to(torch.int32)
+        nb = (n + block - 1) // block
+        expert_ids[blk:blk + nb] = e
+        blk += nb
+        pos += nb * block
+    block_start[num_experts] = blk
+    return sorted_ids, expert_ids, torch.tensor([pos], dtype=torch.int32), block_start
+
+
+def start_end_from_counts(topk_ids: torch.Tensor, num_experts: int):
+    """exp_start / exp_end of python/dlBLAS/dlblas/kernels/fused_moe.py:267-293 (docstring formula)."""
+    cnt = F.one_hot(topk_ids.flatten().to(torch.int64), num_classes=num_experts).sum(0)
+    end = cnt.cumsum(0)
+    return end - cnt, end
+
+
+# --------------------------------------------------------------------------------------
+# fused_moe
+# --------------------------------------------------------------------------------------
+def fused_moe_launcher_gt(A, B, top_k, topk_idx, weights=None):
+    """Launcher ground truth, python/dlBLAS/tests/kernels/test_fused_moe.py:98-112."""
+    M, N, E = A.size(0), B.size(1), B.size(0)
+    C = B.new_zeros(M, top_k, N)
+    for eid in range(E):
+        token_idx, k_idx = torch.where(topk_idx == eid)
+        if len(token_idx) == 0:
+            continue
+        C[token_idx, k_idx] = A[token_idx] @ B[eid].t()
+    if weights is not None:
+        C = C * weights[..., None]
+    return C.flatten(0, 1)
+
+
+def fused_moe(hidden_states, w1, w2, topk_weights, topk_ids, renormalize=False):
+    """End-to-end ground truth, python/dlBLAS/tests/kernels/test_fused_moe.py:148-151, 227-244:
+    per expert, down(silu(gate(x)) * up(x)) * weight, index_add into the output."""
+    if renormalize:
+        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+    output = hidden_states.new_zeros(hidden_states.size(0), w2.size(1))
+    for eid in range(w1.size(0)):
+        token_idx, k_idx = torch.where(topk_ids == eid)
+        if token_idx.numel() == 0:
+            continue
+        gate_proj, up_proj = w1[eid].chunk(2, dim=0)
+        x = hidden_states[token_idx]
+        tmp = F.linear(F.silu(F.linear(x, gate_proj)) * F.linear(x, up_proj), w2[eid])
+        tmp = tmp * topk_weights[token_idx, k_idx, None]
+        output.index_add_(0, token_idx, tmp.to(output.dtype))
+    return output
+
+
+def fused_moe_rounding_faithful(hidden_states, w1, w2, topk_weights, topk_ids, renormalize=False):
+    """Same result as the reference *kernel path* including its rounding points
+    (python/dlBLAS/dlblas/kernels/fused_moe.py:351-352, 162-166, 375): GEMM outputs rounded to
+    the activation dtype, silu and product rounded separately, weight applied to the fp32
+    accumulator before the cast, top-k sum accumulated in fp32 and rounded once."""
+    dt = hidden_states.dtype
+    if renormalize:
+        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+    M, topk = topk_ids.shape
+    partial = torch.zeros(M, topk, w2.size(1), dtype=dt)
+    for eid in range(w1.size(0)):
+        token_idx, k_idx = torch.where(topk_ids == eid)
+        if token_idx.numel() == 0:
+            continue
+        x = hidden_states[token_idx].float()
+        gu = (x @ w1[eid].float().t()).to(dt)
+        gate, up = gu.chunk(2, dim=-1)
+        act = F.silu(gate) * up
+        y = act.float() @ w2[eid].float().t()
+        y = (y * topk_weights[token_idx, k_idx, None].float()).to(dt)
+        partial[token_idx, k_idx] = y
+    return partial.float().sum(dim=1).to(dt)
+
+
+# --------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------
+def _torch_att(xq, xk, xv, seqlen, num_head, head_dim):
+    """Single-sequence causal attention, python/dlBLAS/tests/kernels/test_prefill_attention.py:11-36
+    (same-count heads; additive -1e8 mask, softmax in fp32, P cast back before P.V)."""
+    xq = xq.view(1, seqlen, num_head, head_dim).transpose(1, 2)
+    keys = xk.view(1, seqlen, num_head, head_dim).transpose(1, 2)
+    values = xv.view(1, seqlen, num_head, head_dim).transpose(1, 2)
+    mask = torch.tril(torch.ones(seqlen, seqlen), diagonal=0).unsqueeze(0).unsqueeze(0)
+    mask[mask == 0.0] = -100000000.0
+    scores = torch.matmul(xq, keys.transpose(2, 3)) / math.sqrt(head_dim)
+    scores = F.softmax(scores.float() + mask, dim=-1).type_as(xq)
+    return torch.matmul(scores, values).transpose(1, 2).contiguous().reshape(-1, num_head, head_dim)
+
+
+def context_attention(q, k, v, b_start_loc, b_seq_len, causal=True, sm_scale=None, return_lse=False,
+                      block_rows=1024):
+    """Varlen causal GQA prefill: the per-sequence loop of test_prefill_attention.py:68-77 with the
+    kv heads repeated for grouped queries (prefill_attention.py:159), evaluated in query-row
+    blocks to bound memory.  Scores are formed in fp32 from the 16-bit inputs (as the kernels
+    do); P is cast to the value dtype before P.V.  LSE = max*scale + log(sum) in natural log
+    (flash_attention.py:152-155), shape [Hq, total]."""
+    total, hq, d = q.shape
+    hkv = k.shape[1]
+    group = hq // hkv
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    out = torch.zeros_like(q)
+    lse = torch.full((hq, total), float("-inf"), dtype=torch.float32)
+    for s0, n in zip(b_start_loc.tolist(), b_seq_len.tolist()):
+        if n == 0:
+            continue
+        qs = q[s0:s0 + n].transpose(0, 1).float()                    # [hq, n, d]
+        ks = k[s0:s0 + n].transpose(0, 1).repeat_interleave(group, 0).float()
+        vs = v[s0:s0 + n].transpose(0, 1).repeat_interleave(group, 0)
+        for r0 in range(0, n, block_rows):
+            r1 = min(n, r0 + block_rows)
+            kend = r1 if causal else n
+            sc = torch.matmul(qs[:, r0:r1], ks[:, :kend].transpose(1, 2)) * sm_scale
+            if causal:
+                qi = torch.arange(r0, r1).unsqueeze(1)
+                kj = torch.arange(0, kend).unsqueeze(0)
+                sc = sc.masked_fill((kj > qi).unsqueeze(0), float("-inf"))
+            m = sc.max(dim=-1, keepdim=True)[0]
+            p = torch.exp(sc - m)
+            l = p.sum(dim=-1, keepdim=True)
+            pn = (p / l).to(v.dtype)
+            o = torch.matmul(pn.float(), vs[:, :kend].float())
+            out[s0 + r0:s0 + r1] = o.transpose(0, 1).to(q.dtype)
+            lse[:, s0 + r0:s0 + r1] = (m + torch.log(l)).squeeze(-1)
+    return (out, lse) if return_lse else out
+
+
+def make_blocked_cache(batched_k, batched_v, kv_lens, block_offsets, block_size):
+    """Scatter dense [B, L, H, D] keys/values into a paged cache [pages, block, H, D]
+    (python/dlBLAS/tests/kernels/test_paged_attention.py:28-58)."""
+    num_pages = int(block_offsets.max().item()) + 1
+    hk, d, dv = batched_k.shape[2], batched_k.shape[3], batched_v.shape[3]
+    blocked_k = batched_k.new_zeros(num_pages, block_size, hk, d)
+    blocked_v = batched_v.new_zeros(num_pages, block_size, hk, dv)
+    for b, offs in enumerate(block_offsets):
+        n = int(kv_lens[b])
+        for i, st in enumerate(range(0, n, block_size)):
+            size = min(block_size, n - st)
+            blocked_k[offs[i], :size] = batched_k[b, st:st + size]
+            blocked_v[offs[i], :size] = batched_v[b, st:st + size]
+    return blocked_k, blocked_v
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_scale=None, window_size=None,
+                           logit_softcapping=None):
+    """Decode ground truth: `_naive_attention` of test_paged_attention.py:61-84 specialised to one
+    query token per sequence, reading K/V through the block table.  q [B, Hq, D]; scores in
+    fp32, softmax in fp32, P cast to the value dtype before P.V; optional sliding window
+    (keys in [ctx - window, ctx)) and tanh soft-cap as in paged_attention.py:175-200."""
+    B, hq, d = q.shape
+    page = k_cache.shape[1]
+    hkv = k_cache.shape[2]
+    group = hq // hkv
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(B, hq, v_cache.shape[-1], dtype=q.dtype)
+    for b in range(B):
+        n = int(kv_seqlens[b])
+        if n == 0:
+            continue
+        npg = (n + page - 1) // page
+        pages = block_offsets[b, :npg].to(torch.int64)
+        ks = k_cache[pages].reshape(npg * page, hkv, -1)[:n]
+        vs = v_cache[pages].reshape(npg * page, hkv, -1)[:n]
+        lo = max(0, n - window_size) if (window_size is not None and window_size > 0) else 0
+        ks, vs = ks[lo:], vs[lo:]
+        kf = ks.transpose(0, 1).repeat_interleave(group, 0).float()      # [hq, n, d]
+        vf = vs.transpose(0, 1).repeat_interleave(group, 0)
+        sc = torch.matmul(q[b].float().unsqueeze(1), kf.transpose(1, 2)) * sm_scale   # [hq, 1, n]
+        if logit_softcapping is not None and logit_softcapping > 0:
+            sc = logit_softcapping * torch.tanh(sc / logit_softcapping)
+        p = torch.softmax(sc, dim=-1, dtype=torch.float32).to(vf.dtype)
+        out[b] = torch.matmul(p.float(), vf.float()).squeeze(1).to(q.dtype)
+    return out

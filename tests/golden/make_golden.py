@@ -1,0 +1,174 @@
+"""Generate golden fixtures by EXECUTING the reference tests' own ground-truth functions on the CPU.
+
+Run once where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/DLCompiler
+
+Nothing is copied from the reference: the ground-truth functions are located in the
+reference's test files with `ast`, compiled in memory (decorators dropped, `.cuda()` calls
+removed so they run on the CPU) and called on seeded inputs.  Inputs and outputs are stored
+as small `.pt` files next to this script; the test-suite loads them without needing the
+reference checkout.
+"""
+from __future__ import annotations
+
+import argparse
+import ast
+import math
+import os
+
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class _StripCuda(ast.NodeTransformer):
+    """x.cuda() -> x ; device="cuda" keyword -> device="cpu"."""
+
+    def visit_Call(self, node):
+        self.generic_visit(node)
+        if isinstance(node.func, ast.Attribute) and node.func.attr == "cuda" and not node.args:
+            return node.func.value
+        for kw in node.keywords:
+            if kw.arg == "device" and isinstance(kw.value, ast.Constant) and kw.value.value == "cuda":
+                kw.value = ast.Constant("cpu")
+        return node
+
+
+def load_functions(path: str, names: list[str]) -> dict:
+    """Compile the named functions (`func` or `Class.method`) of a reference file in memory."""
+    tree = ast.parse(open(path).read())
+    found = {}
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            found[node.name] = node
+        elif isinstance(node, ast.ClassDef):
+            for sub in node.body:
+                key = f"{node.name}.{sub.name}" if isinstance(sub, ast.FunctionDef) else None
+                if key in names:
+                    found[key] = sub
+    missing = [n for n in names if n not in found]
+    if missing:
+        raise RuntimeError(f"{path}: cannot find {missing}")
+    ns = {"torch": torch, "math": math, "F": F}
+    out = {}
+    for key, node in found.items():
+        node.decorator_list = []
+        node = _StripCuda().visit(node)
+        mod = ast.Module(body=[node], type_ignores=[])
+        ast.fix_missing_locations(mod)
+        exec(compile(mod, path, "exec"), ns)
+        out[key] = ns[node.name]
+    return out
+
+
+def _fixture_value(gen_fn, *args):
+    """The reference ground truths are pytest fixtures (generators): take the yielded value."""
+    return next(gen_fn(None, *args))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    tests = os.path.join(args.reference, "python/dlBLAS/tests/kernels")
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+    # ---------------------------------------------------------------- silu_and_mul
+    fns = load_functions(os.path.join(tests, "test_activation.py"), ["TestSiluAndMul.gt"])
+    cases = []
+    for i, (rows, feat, dtype) in enumerate([(16, 4096, torch.float16), (16, 768, torch.float16),
+                                             (16, 2 * 1376, torch.bfloat16)]):
+        g = torch.Generator().manual_seed(1000 + i)
+        x = torch.rand(rows, feat, generator=g).to(dtype)
+        cases.append({"x": x, "gt": _fixture_value(fns["TestSiluAndMul.gt"], x)})
+    torch.save(cases, os.path.join(HERE, "silu_and_mul.pt"))
+
+    # ---------------------------------------------------------------- fused_moe (launcher + end to end)
+    fns = load_functions(os.path.join(tests, "test_fused_moe.py"),
+                         ["TestFusedMoEKernelLauncher.gt", "_mlp_forward", "TestFusedMoe.gt"])
+    g = torch.Generator().manual_seed(2000)
+    M, K, N, E, top_k = 256, 64, 128, 4, 2
+    A = ((torch.rand(M, K, generator=g) - 0.5) / 2).to(torch.float16)
+    B = ((torch.rand(E, N, K, generator=g) - 0.5) / 2).to(torch.float16)
+    router = torch.rand(M, E, generator=g).to(torch.float16)
+    weights, topk_idx = router.topk(top_k, dim=-1)
+    launcher = {"A": A, "B": B, "weights": weights, "topk_idx": topk_idx, "top_k": top_k,
+                "gt": _fixture_value(fns["TestFusedMoEKernelLauncher.gt"], A, B, top_k, topk_idx, True, weights)}
+    e2e = []
+    for i, dtype in enumerate([torch.float16, torch.bfloat16]):
+        g = torch.Generator().manual_seed(2100 + i)
+        seq, in_size, hidden, out_size = 128, 128, 256, 128
+        hs = ((torch.rand(seq, in_size, generator=g) - 0.5) / 2).to(dtype)
+        w1 = ((torch.rand(E, hidden, in_size, generator=g) - 0.5) / 2).to(dtype)
+        w2 = ((torch.rand(E, out_size, hidden // 2, generator=g) - 0.5) / 2).to(dtype)
+        logits = torch.rand(seq, E, generator=g).to(dtype)
+        tw, ti = torch.topk(torch.softmax(logits, dim=-1, dtype=torch.float32), top_k, dim=-1)
+        e2e.append({"hidden_states": hs, "w1": w1, "w2": w2, "topk_weights": tw, "topk_idx": ti,
+                    "renormalize": True,
+                    "gt": _fixture_value(fns["TestFusedMoe.gt"], hs, w1, w2, tw, ti, True)})
+    torch.save({"launcher": launcher, "e2e": e2e}, os.path.join(HERE, "fused_moe.pt"))
+
+    # ---------------------------------------------------------------- varlen prefill attention
+    fns = load_functions(os.path.join(tests, "test_prefill_attention.py"), ["TestPrefillAttention._torch_att"])
+    att = fns["TestPrefillAttention._torch_att"]
+    cases = []
+    for i, (lens, hq, hkv, dtype) in enumerate([([96, 200, 128, 70], 2, 2, torch.float16),
+                                                ([130, 64, 257], 4, 1, torch.bfloat16)]):
+        g = torch.Generator().manual_seed(3000 + i)
+        total, d = sum(lens), 128
+        q = (torch.randn(total, hq, d, generator=g) * 0.2 + 0.1).to(dtype)
+        k = (torch.randn(total, hkv, d, generator=g) * 0.2 + 0.4).to(dtype)
+        v = (torch.randn(total, hkv, d, generator=g) * 0.2 + 0.3).to(dtype)
+        outs, st = [], 0
+        for n in lens:
+            # the reference function is multi-head only: grouped queries = kv heads repeated
+            kk = k[st:st + n].repeat_interleave(hq // hkv, 1)
+            vv = v[st:st + n].repeat_interleave(hq // hkv, 1)
+            outs.append(att(None, q[st:st + n], kk, vv, 1, n, hq, d))
+            st += n
+        cases.append({"q": q, "k": k, "v": v, "lens": lens, "gt": torch.cat(outs, 0)})
+    torch.save(cases, os.path.join(HERE, "prefill_attention.pt"))
+
+    # fp32 flash-attention CPU reference used by the reference's compiler tests
+    fa = load_functions(os.path.join(args.reference, "test/ascend/cpu_verify/test_fa.py"), ["flash_attention_cpu"])
+    g = torch.Generator().manual_seed(20)
+    q = (torch.randn(1, 2, 192, 128, generator=g) * 0.5).to(torch.float16)
+    k = (torch.randn(1, 2, 192, 128, generator=g) * 0.5).to(torch.float16)
+    v = (torch.randn(1, 2, 192, 128, generator=g) * 0.5).to(torch.float16)
+    torch.save({"q": q, "k": k, "v": v, "sm_scale": 0.5,
+                "gt": fa["flash_attention_cpu"](q, k, v, 0.5, causal=True)}, os.path.join(HERE, "fa_cpu.pt"))
+
+    # ---------------------------------------------------------------- paged decode attention
+    fns = load_functions(os.path.join(tests, "test_paged_attention.py"),
+                         ["_conti_input", "_make_bias", "_make_blocked_cache", "_naive_attention"])
+    cases = []
+    for i, (d, hq, hkv, page, hist, dtype) in enumerate([(64, 8, 2, 16, [50, 40, 30, 20], torch.float16),
+                                                         (128, 8, 2, 16, [150, 77, 200, 16], torch.bfloat16),
+                                                         (128, 4, 4, 64, [64, 65, 1, 200], torch.float16)]):
+        torch.manual_seed(123 + i)
+        seq_lens = torch.tensor([1, 1, 1, 1])
+        history = torch.tensor(hist)
+        full = seq_lens + history
+        bq = torch.rand(4, 1, hq, d).to(dtype)
+        bk = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        bv = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        nblk = (full + page - 1) // page
+        offs = [torch.arange(int(n)) * 4 + idx for idx, n in enumerate(nblk)]
+        table = torch.zeros(4, max(len(o) for o in offs), dtype=torch.int64)
+        for o, row in zip(offs, table):
+            row[:len(o)] = o
+        mask = fns["_make_bias"](seq_lens, history, -1e30)
+        gt = fns["_naive_attention"](bq, (bk, bv), mask)
+        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, d)
+        cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
+                      "block_offsets": table, "kv_seqlens": full, "gt": fns["_conti_input"](gt, seq_lens)})
+    torch.save(cases, os.path.join(HERE, "paged_decode.pt"))
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".pt"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,52 @@
+"""The C-ABI library: it loads, exports every symbol the header declares, and rejects bad
+arguments before touching the device (no GPU needed)."""
+import os
+import re
+
+import pytest
+
+from dlcompiler_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "dlblas_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dlb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/dlblas_b200.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes prototypes and header declarations differ"
+    assert lib.dlb_version() >= 100
+
+
+def test_argument_errors_are_reported_without_a_device():
+    lib = _lib.load()
+    rc = lib.dlb_silu_and_mul(None, None, -1, 8, 16, 8, _lib.DTYPE_BF16, None)
+    assert rc < 0 and b"negative" in lib.dlb_last_error()
+    rc = lib.dlb_grouped_topk_gating(None, None, None, None, 4, 1000, 1000, 1, 1, 2, 0, 1, 1.0, None)
+    assert rc < 0 and b"experts" in lib.dlb_last_error()
+    with pytest.raises(AssertionError):
+        _lib.check(rc, "gating")
+    rc = lib.dlb_paged_decode(None, None, None, None, None, None, None, 1, 32, 8, 96, 64, 1, 1, 0, 0, 0, 0, 0, 0, 0,
+                              0, 0, 0, 0, 0, 0, 256, 1, -1, 1.0, -1.0, _lib.DTYPE_BF16, None, None)
+    assert rc < 0 and b"head_dim" in lib.dlb_last_error()
+    rc = lib.dlb_moe_grouped_gemm(1, 100, 64, 1, 4, 128, 64, 64, 1, 128, 128, 1, 1, None, 10, 0, _lib.DTYPE_BF16,
+                                  None, None)
+    assert rc < 0 and b"128-row" in lib.dlb_last_error()
+    assert lib.dlb_paged_decode_workspace_floats(64, 32, 128, 8) == 64 * 32 * 8 * 130
+
+
+def test_wrappers_refuse_cpu_tensors():
+    import torch
+
+    from dlcompiler_b200 import silu_and_mul
+
+    with pytest.raises(AssertionError):
+        silu_and_mul(torch.zeros(4, 8, dtype=torch.bfloat16))

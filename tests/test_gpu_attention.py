@@ -1,0 +1,172 @@
+"""GPU parity: varlen prefill attention (tcgen05) and paged flash-decode against the CPU oracle."""
+import os
+
+import pytest
+import torch
+
+from dlcompiler_b200 import context_attention_fwd, paged_attention_fwd
+from dlcompiler_b200 import workloads as W
+from oracle import dlblas_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+# stated bound for bf16 attention outputs
+RTOL = ATOL = 2e-2
+
+
+def _run_prefill(dev, d, lse=False, causal=True):
+    q, k, v = d["q"].to(dev), d["k"].to(dev), d["v"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    l = torch.full((q.shape[1], q.shape[0]), float("nan"), device=dev) if lse else None
+    context_attention_fwd(q, k, v, o, d["b_start_loc"].to(dev), d["b_seq_len"].to(dev), d["max_input_len"], lse=l,
+                          causal=causal)
+    return o.cpu(), (l.cpu() if lse else None)
+
+
+def test_prefill_golden(cuda_device, golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "prefill_attention.pt"), weights_only=True):
+        lens = c["lens"]
+        start = [0]
+        for n in lens[:-1]:
+            start.append(start[-1] + n)
+        d = {"q": c["q"], "k": c["k"], "v": c["v"], "b_start_loc": torch.tensor(start, dtype=torch.int32),
+             "b_seq_len": torch.tensor(lens, dtype=torch.int32), "max_input_len": max(lens)}
+        out, _ = _run_prefill(cuda_device, d)
+        # reference test: atol=1e-2, rtol=0 for fp16 (test_prefill_attention.py:83)
+        torch.testing.assert_close(out, c["gt"], atol=1e-2 if out.dtype == torch.float16 else 2e-2, rtol=0)
+
+
+@pytest.mark.parametrize("lens,hq,hkv,dtype", [
+    ([1], 4, 4, torch.bfloat16),
+    ([63, 64, 65], 4, 2, torch.bfloat16),
+    ([127, 128, 129, 1], 8, 2, torch.float16),
+    ([512, 1024, 512, 1024], 6, 6, torch.float16),      # the reference test's lengths
+    ([300, 0, 700], 8, 1, torch.bfloat16),               # an empty sequence in the batch
+    ([2048], 32, 8, torch.bfloat16),
+])
+def test_prefill_shapes_with_lse(cuda_device, lens, hq, hkv, dtype):
+    wl = W.PrefillWorkload(seq_lens=lens, hq=hq, hkv=hkv, dtype=dtype)
+    d = wl.make()
+    out, lse = _run_prefill(cuda_device, d, lse=True)
+    ref, rlse = oracle.context_attention(d["q"], d["k"], d["v"], d["b_start_loc"], d["b_seq_len"], return_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(lse, rlse, rtol=1e-3, atol=1e-3)
+
+
+def test_prefill_non_causal(cuda_device):
+    wl = W.PrefillWorkload(seq_lens=[200, 77], hq=4, hkv=2)
+    d = wl.make()
+    out, _ = _run_prefill(cuda_device, d, causal=False)
+    ref = oracle.context_attention(d["q"], d["k"], d["v"], d["b_start_loc"], d["b_seq_len"], causal=False)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_prefill_config_sample_and_properties(cuda_device):
+    """Full benchmark shape: one (sequence, kv-head group) against the oracle, plus properties
+    that hold at any size (causality, determinism)."""
+    wl = W.PrefillWorkload()
+    d = wl.make()
+    out, lse = _run_prefill(cuda_device, d, lse=True)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    # oracle on sequence 2, q heads 8..11 (kv head 2), first 2048 rows (causal: needs only those keys)
+    s0, n = int(d["b_start_loc"][2]), 2048
+    ref, rlse = oracle.context_attention(d["q"][s0:s0 + n, 8:12], d["k"][s0:s0 + n, 2:3], d["v"][s0:s0 + n, 2:3],
+                                         torch.tensor([0]), torch.tensor([n]), return_lse=True)
+    torch.testing.assert_close(out[s0:s0 + n, 8:12].float(), ref.float(), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(lse[8:12, s0:s0 + n], rlse, rtol=1e-3, atol=1e-3)
+    # last rows of the last sequence
+    s0, n = int(d["b_start_loc"][3]), 8192
+    ref = oracle.context_attention(d["q"][s0:s0 + n, 31:32], d["k"][s0:s0 + n, 7:8], d["v"][s0:s0 + n, 7:8],
+                                   torch.tensor([0]), torch.tensor([n]))
+    torch.testing.assert_close(out[s0 + 8000:s0 + n, 31:32].float(), ref[8000:].float(), rtol=RTOL, atol=ATOL)
+    # causality: changing the last 100 keys/values of a sequence leaves earlier rows bit-identical
+    d2 = dict(d)
+    d2["k"] = d["k"].clone()
+    d2["v"] = d["v"].clone()
+    d2["k"][8192 - 100:8192] = 0
+    d2["v"][8192 - 100:8192] = 1
+    out2, _ = _run_prefill(cuda_device, d2)
+    assert torch.equal(out2[:8192 - 100], out[:8192 - 100])
+    assert torch.equal(out2[8192:], out[8192:])
+
+
+def _run_decode(dev, d, **kw):
+    q = d["q"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    B = q.shape[0]
+    paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["block_table"].to(dev),
+                        torch.arange(B, device=dev), torch.ones(B, dtype=torch.int64, device=dev),
+                        d["kv_seqlens"].to(dev), 1, **kw)
+    return o.cpu()
+
+
+def test_decode_golden(cuda_device, golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "paged_decode.pt"), weights_only=True):
+        d = {"q": c["q"], "k_cache": c["k_cache"], "v_cache": c["v_cache"], "block_table": c["block_offsets"],
+             "kv_seqlens": c["kv_seqlens"]}
+        out = _run_decode(cuda_device, d)
+        # reference test: atol=1e-3, rtol=1e-5 for fp16 (test_paged_attention.py:286)
+        tol = 1e-3 if out.dtype == torch.float16 else 8e-3
+        torch.testing.assert_close(out, c["gt"], atol=tol, rtol=1e-5)
+
+
+@pytest.mark.parametrize("batch,lo,hi,page,hq,hkv,D,dtype", [
+    (1, 1, 1, 16, 4, 4, 64, torch.float16),
+    (5, 1, 300, 16, 8, 2, 128, torch.bfloat16),
+    (7, 50, 1500, 32, 32, 8, 128, torch.bfloat16),
+    (4, 1000, 5000, 64, 32, 8, 128, torch.bfloat16),
+    (3, 100, 900, 128, 16, 1, 64, torch.float16),        # 16 q heads on one kv head
+    (2, 64, 640, 64, 40, 2, 128, torch.bfloat16),        # group of 20 > 16 rows: two head blocks
+    (6, 0, 100, 16, 8, 8, 128, torch.bfloat16),          # may contain empty contexts
+])
+def test_decode_shapes(cuda_device, batch, lo, hi, page, hq, hkv, D, dtype):
+    wl = W.DecodeWorkload(batch=batch, ctx_lo=lo, ctx_hi=hi, page=page, hq=hq, hkv=hkv, head_dim=D, dtype=dtype)
+    d = wl.make()
+    out = _run_decode(cuda_device, d)
+    ref = oracle.paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["block_table"], d["kv_seqlens"])
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_decode_window_softcap_int64_and_stale_cache(cuda_device):
+    wl = W.DecodeWorkload(batch=6, ctx_lo=10, ctx_hi=3000, page=64, hq=8, hkv=2, head_dim=128)
+    d = wl.make()
+    d["block_table"] = d["block_table"].to(torch.int64)
+    d["kv_seqlens"] = d["kv_seqlens"].to(torch.int64)
+    for kw in ({"window_size": 333}, {"logit_softcapping": 5.0}, {"sm_scale": 0.03},
+               {"window_size": 100, "logit_softcapping": 30.0}):
+        out = _run_decode(cuda_device, d, **kw)
+        ref = oracle.paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["block_table"], d["kv_seqlens"],
+                                            **kw)
+        torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+    # slots past the context length may hold anything, including NaN bit patterns
+    base = _run_decode(cuda_device, d)
+    dirty = dict(d)
+    kc, vc = d["k_cache"].clone(), d["v_cache"].clone()
+    for b in range(6):
+        n = int(d["kv_seqlens"][b])
+        pg = int(d["block_table"][b, (n - 1) // 64]) if n > 0 else None
+        if pg is not None and n % 64:
+            kc[pg, n % 64:] = float("nan")
+            vc[pg, n % 64:] = float("nan")
+    dirty["k_cache"], dirty["v_cache"] = kc, vc
+    assert torch.equal(_run_decode(cuda_device, dirty), base)
+
+
+def test_decode_config_sample_and_properties(cuda_device):
+    """Full benchmark shape (caches generated on the device): sampled sequences against the oracle."""
+    wl = W.DecodeWorkload()
+    d = wl.make(device=cuda_device)
+    out = _run_decode(cuda_device, d)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, _run_decode(cuda_device, d))             # deterministic
+    ctx = d["kv_seqlens"]
+    picks = [int(ctx.argmin()), int(ctx.argmax()), 17]
+    for b in picks:
+        n = int(ctx[b])
+        npg = (n + wl.page - 1) // wl.page
+        pages = d["block_table"][b, :npg].long()
+        kc = d["k_cache"][pages.to(cuda_device)].cpu()
+        vc = d["v_cache"][pages.to(cuda_device)].cpu()
+        table = torch.arange(npg, dtype=torch.int32).unsqueeze(0)
+        ref = oracle.paged_decode_attention(d["q"][b:b + 1], kc, vc, table, ctx[b:b + 1])
+        torch.testing.assert_close(out[b:b + 1].float(), ref.float(), rtol=RTOL, atol=ATOL)
