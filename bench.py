@@ -1,0 +1,459 @@
+"""Benchmark of the dlBLAS hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ops all|none]
+
+Headline (one JSON line on stdout): fused_moe on the Mixtral-like configuration
+(T=4096, H=4096, I=14336, E=8, top_k=2, bf16) in TFLOP/s, whole job.  N > 1 runs the
+same total workload expert-parallel (tokens and experts sharded over the ranks, all-to-all
+dispatch/combine), so scaling is strong.  The line also carries, under "ops", the other
+four configurations (silu_and_mul, grouped gating, varlen prefill, paged decode) with
+their own roofline fractions, measured at N=1.
+
+`--impl reference` times the CPU checker (the torch restatement of the reference's own
+test ground truth, oracle/dlblas_oracle.py) on the host cores on a bounded token sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch of the grouped GEMM kernel from the committed ncu capture
+# (profiles/grouped_gemm_*.md); None until a capture exists for the benchmark shape.
+NCU_TRAFFIC = {"grouped_gemm": None, "silu_and_mul": None, "paged_decode": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["basis"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["basis"] = "fallback"
+    return d
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows = []
+        self.proc = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            ident = str(device_index)
+        self.cmd = ["nvidia-smi", "-i", ident, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                    "-lms", "100"]
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- helpers
+def time_steps(fn, steps, warmup, barrier=None):
+    """W untimed steps, then K steps between CUDA events on the current stream; returns ms per step."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if barrier is not None:
+        barrier()
+    return start.elapsed_time(end) / steps
+
+
+def flush_l2(buf):
+    buf.zero_()
+
+
+# --------------------------------------------------------------------------- per-op benches (N = 1)
+def bench_silu(dev, peaks, steps, warmup):
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    wl = W.SiluWorkload()
+    x = wl.make()["gate_up"].to(dev)
+    out = torch.empty(wl.tokens, wl.hidden, dtype=x.dtype, device=dev)
+    ms = time_steps(lambda: dl.silu_and_mul(x, out), steps, warmup)   # 270 MB per pass > 126 MB L2
+    gbs = wl.bytes() / ms / 1e6
+    return {"workload": "C1 silu_and_mul bf16 [4096, 2x11008]", "ms": ms, "value": gbs, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["silu_and_mul"],
+                         "basis": peaks["basis"]},
+            "l2": "working set 270 MB > L2", "gpu_launches": steps}
+
+
+def bench_gating(dev, peaks, steps, warmup):
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    wl = W.GatingWorkload()
+    d = wl.make()
+    nbuf = 16                                    # 16 x 17.8 MB rotating sets > 126 MB L2
+    logits = [d["logits"].to(dev).clone() for _ in range(nbuf)]
+    bias = d["bias"].to(dev)
+    state = {"i": 0}
+
+    def step():
+        dl.grouped_topk_gating(logits[state["i"] % nbuf], bias, wl.top_k, wl.n_group, wl.topk_group,
+                               wl.scale_factor)
+        state["i"] += 1
+
+    ms = time_steps(step, max(steps, 64), max(warmup, 16))
+    gbs = wl.bytes() / ms / 1e6
+    return {"workload": "C2 grouped sigmoid gating fp32 [16384, 256] top-8", "ms": ms, "value": gbs, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "basis": peaks["basis"]},
+            "l2": "16 rotating input sets (285 MB) > L2; includes launch latency", "gpu_launches": max(steps, 64)}
+
+
+def bench_prefill(dev, peaks, steps, warmup):
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    wl = W.PrefillWorkload()
+    d = wl.make()
+    q, k, v = d["q"].to(dev), d["k"].to(dev), d["v"].to(dev)
+    o = torch.empty_like(q)
+    lse = torch.empty(wl.hq, q.shape[0], dtype=torch.float32, device=dev)
+    st, ln = d["b_start_loc"].to(dev), d["b_seq_len"].to(dev)
+    ms = time_steps(lambda: dl.context_attention_fwd(q, k, v, o, st, ln, d["max_input_len"], lse=lse), steps, warmup)
+    tf = wl.flops() / ms / 1e9
+    return {"workload": "C4 varlen causal GQA prefill bf16 B=4 S=8192 Hq=32 Hkv=8 D=128", "ms": ms, "value": tf,
+            "unit": "TFLOP/s",
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": tf / peaks["bf16_tflops_sustained"], "traffic": None, "basis": peaks["basis"]},
+            "l2": "q/k/v/o 670 MB > L2", "gpu_launches": steps}
+
+
+def bench_decode(dev, peaks, steps, warmup):
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    wl = W.DecodeWorkload()
+    d = wl.make(device=dev)
+    q = d["q"].to(dev)
+    o = torch.empty_like(q)
+    table, lens = d["block_table"].to(dev), d["kv_seqlens"].to(dev)
+    qs = torch.arange(wl.batch, device=dev)
+    ql = torch.ones(wl.batch, dtype=torch.int64, device=dev)
+    ms = time_steps(lambda: dl.paged_attention_fwd(q, d["k_cache"], d["v_cache"], o, table, qs, ql, lens, 1), steps,
+                    warmup)
+    nbytes = wl.bytes(d["kv_seqlens"])
+    gbs = nbytes / ms / 1e6
+    return {"workload": f"C5 paged decode bf16 B=64 ctx U[1024,32768] page 64 (ctx_sum={int(d['kv_seqlens'].sum())})",
+            "ms": ms, "value": gbs, "unit": "GB/s", "tflops": wl.flops(d["kv_seqlens"]) / ms / 1e9,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["paged_decode"],
+                         "basis": peaks["basis"]},
+            "l2": "KV cache 4.4 GB > L2", "gpu_launches": 2 * steps}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_fused_moe(sample_tokens, threads=None, repeats=1):
+    """Times the CPU checker's fused_moe (reference test ground truth) on a token sample of C3."""
+    from dlcompiler_b200 import workloads as W
+    from oracle import dlblas_oracle as oracle
+
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    wl = W.MoeWorkload()
+    d = wl.make()
+    hs = d["hidden_states"][:sample_tokens]
+    tw, ti = oracle.softmax_topk(d["router_logits"][:sample_tokens], wl.top_k)
+    ti = ti.long()
+    oracle.fused_moe(hs[:32], d["w1"], d["w2"], tw[:32], ti[:32])          # warm-up
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.fused_moe(hs, d["w1"], d["w2"], tw, ti)
+        best = min(best, time.perf_counter() - t0)
+    tf = wl.flops(sample_tokens) / best / 1e12
+    return tf, best, threads
+
+
+def run_reference(args):
+    """The reference arm: CPU implementation on the host cores, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from dlcompiler_b200 import workloads as W
+    from oracle import dlblas_oracle as oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    wl = W.MoeWorkload()
+    d = wl.make()
+    sample = 256
+    hs = d["hidden_states"][:sample]
+    tw, ti = oracle.softmax_topk(d["router_logits"][:sample], wl.top_k)
+    ti = ti.long()
+    for _ in range(min(args.warmup, 2)):
+        oracle.fused_moe(hs, d["w1"], d["w2"], tw, ti)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.fused_moe(hs, d["w1"], d["w2"], tw, ti)
+    dt = (time.perf_counter() - t0) / args.steps
+    tf = wl.flops(sample) / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "fused_moe_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16",
+                   "sample": f"first {sample} tokens per step"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} of 4096 tokens per step, torch CPU restatement of the reference "
+                                   "test ground truth (the reference's Triton kernels cannot run on CPU)"},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- headline: fused_moe
+def run_ours(args):
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import _lib
+    from dlcompiler_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    _lib.load()
+    peaks = load_peaks()
+    wl = W.MoeWorkload()
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    d = wl.make(weights=False)
+    # routing inputs of the step: softmax -> top-2 of the seeded router logits (our router kernel)
+    tw_dev, ti_dev = dl.softmax_topk(d["router_logits"].to(dev), wl.top_k)
+    tw_cpu, ti_cpu = tw_dev.cpu(), ti_dev.cpu()
+
+    if world == 1:
+        wts = wl.make()
+        w1, w2 = wts["w1"].to(dev), wts["w2"].to(dev)
+        del wts
+        hs, tw, ti = d["hidden_states"].to(dev), tw_cpu.to(dev), ti_cpu.to(dev)
+        events = []
+
+        def step():
+            return dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k, _events=events)
+
+        launches_per_step = 5
+        with ClockSampler(local_rank) as clk:
+            ms = time_steps(step, args.steps, args.warmup)
+        torch.cuda.synchronize()
+        timed = events[-2 * args.steps:]
+        gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
+        clocks = clk.summary()
+
+        # end to end: pinned host inputs -> device -> fused_moe -> host result, every step
+        hs_h = d["hidden_states"].pin_memory()
+        tw_h, ti_h = tw_cpu.pin_memory(), ti_cpu.pin_memory()
+        out_h = torch.empty(wl.tokens, wl.hidden, dtype=torch.bfloat16).pin_memory()
+        hs_d, tw_d, ti_d = torch.empty_like(hs), torch.empty_like(tw), torch.empty_like(ti)
+
+        def step_e2e():
+            hs_d.copy_(hs_h, non_blocking=True)
+            tw_d.copy_(tw_h, non_blocking=True)
+            ti_d.copy_(ti_h, non_blocking=True)
+            out = dl.fused_moe(hs_d, w1, w2, tw_d, ti_d, wl.top_k)
+            out_h.copy_(out, non_blocking=True)
+
+        ms_e2e = time_steps(step_e2e, args.steps, args.warmup)
+        h2d = hs_h.numel() * 2 + tw_h.numel() * 4 + ti_h.numel() * 4
+        d2h = out_h.numel() * 2
+        dl.check_device_status()
+        parallelism = "single GPU"
+        flops = wl.flops()
+    else:
+        from dlcompiler_b200.distributed import ep_moe
+
+        ctx = ep_moe.EpMoeContext(dist.group.WORLD, wl.experts, dev)
+        e_local = wl.experts // world
+        wts = wl.make()
+        w1 = wts["w1"][rank * e_local:(rank + 1) * e_local].to(dev)
+        w2 = wts["w2"][rank * e_local:(rank + 1) * e_local].to(dev)
+        del wts
+        t_local = wl.tokens // world
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        hs, tw, ti = d["hidden_states"][sl].to(dev), tw_cpu[sl].to(dev), ti_cpu[sl].to(dev)
+        events = []
+
+        def step():
+            return ep_moe.ep_fused_moe(ctx, hs, w1, w2, tw, ti, wl.top_k, _events=events)
+
+        launches_per_step = ep_moe.KERNELS_PER_STEP
+        with ClockSampler(local_rank) as clk:
+            ms = time_steps(step, args.steps, args.warmup, barrier)
+        torch.cuda.synchronize()
+        timed = events[-2 * args.steps:]
+        gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
+        clocks = clk.summary()
+
+        hs_h = d["hidden_states"][sl].contiguous().pin_memory()
+        tw_h, ti_h = tw_cpu[sl].contiguous().pin_memory(), ti_cpu[sl].contiguous().pin_memory()
+        out_h = torch.empty(t_local, wl.hidden, dtype=torch.bfloat16).pin_memory()
+        hs_d, tw_d, ti_d = torch.empty_like(hs), torch.empty_like(tw), torch.empty_like(ti)
+
+        def step_e2e():
+            hs_d.copy_(hs_h, non_blocking=True)
+            tw_d.copy_(tw_h, non_blocking=True)
+            ti_d.copy_(ti_h, non_blocking=True)
+            out = ep_moe.ep_fused_moe(ctx, hs_d, w1, w2, tw_d, ti_d, wl.top_k)
+            out_h.copy_(out, non_blocking=True)
+
+        ms_e2e = time_steps(step_e2e, args.steps, args.warmup, barrier)
+        h2d = (hs_h.numel() * 2 + tw_h.numel() * 4 + ti_h.numel() * 4) * world
+        d2h = out_h.numel() * 2 * world
+        dl.check_device_status()
+        # max over ranks of the device-timed step
+        t = torch.tensor([ms, ms_e2e, gemm_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e, gemm_ms = t.tolist()
+        parallelism = f"ep{world}: tokens and experts sharded over {world} ranks, NCCL all-to-all dispatch/combine"
+        flops = wl.flops()
+
+    tflops = flops / ms / 1e9
+    e2e_tflops = flops / ms_e2e / 1e9
+    # dominant kernel: the grouped GEMM (two launches per step, both timed with events inside the steps)
+    gemm_flops_per_rank = flops / world
+    gemm_tf = gemm_flops_per_rank / gemm_ms / 1e9
+    peak = peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": "fused_moe_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16 (moe_align block 128 -> "
+                               "gate/up GEMM+silu -> down GEMM x weight -> combine)",
+                   "parallelism": parallelism, "l2": "expert weights 2.8 GB per pass > 126 MB L2"},
+        "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (2 launches per step)", "achieved": gemm_tf,
+                     "peak": peak, "unit": "TFLOP/s", "frac": gemm_tf / peak, "traffic": NCU_TRAFFIC["grouped_gemm"],
+                     "basis": f"{peaks['basis']} sustained cuBLAS bf16", "ms_per_step_in_kernel": gemm_ms},
+        "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1:
+        if args.ops != "none":
+            ops = {}
+            for name, fn in (("silu_and_mul", bench_silu), ("grouped_gating", bench_gating),
+                             ("flash_prefill", bench_prefill), ("paged_decode", bench_decode)):
+                torch.cuda.empty_cache()
+                ops[name] = fn(dev, peaks, max(args.steps, 10), max(args.warmup, 3))
+            dl.check_device_status()
+            line["ops"] = ops
+        if args.cpu_baseline:
+            del w1, w2
+            torch.cuda.empty_cache()
+            tf, secs, cores = cpu_fused_moe(args.cpu_sample)
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"first {args.cpu_sample} of 4096 tokens, one pass ({secs:.1f} s); torch "
+                                              "CPU restatement of the reference test ground truth"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ops", default="all", choices=["all", "none"])
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--cpu-sample", type=int, default=1024)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -42,6 +42,30 @@ struct GatingParams {
   float scale;
 };
 
+// sigmoid evaluated by a FIXED sequence of correctly-rounded fp32 operations
+// (no fused multiply-add, no approximate transcendental), so that the CPU checker,
+// which performs the same sequence with IEEE fp32 tensor ops, gets bit-identical
+// scores and therefore bit-identical expert ids even for near-ties:
+//   t = clamp(-x, -87, 88); n = rint(t * log2e); r = (t - n*LN2_HI) - n*LN2_LO
+//   e = (((((r/720 + 1/120) r + 1/24) r + 1/6) r + 1/2) r + 1) r + 1   [Horner]
+//   sigmoid = 1 / (1 + e * 2^n)
+__device__ __forceinline__ float sigmoid_spec(float x) {
+  const float t = fminf(fmaxf(-x, -87.0f), 88.0f);
+  const float n = rintf(__fmul_rn(t, 1.44269502162933349609375f));
+  float r = __fsub_rn(t, __fmul_rn(n, 0.693145751953125f));
+  r = __fsub_rn(r, __fmul_rn(n, 1.428606765330187045037746429443359375e-06f));
+  float p = 1.38888892251998186111450195312e-03f;                 // 1/720
+  p = __fadd_rn(__fmul_rn(p, r), 8.33333376795053482055664062500e-03f);   // 1/120
+  p = __fadd_rn(__fmul_rn(p, r), 4.16666679084300994873046875000e-02f);   // 1/24
+  p = __fadd_rn(__fmul_rn(p, r), 1.66666671633720397949218750000e-01f);   // 1/6
+  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  const float two_n = __int_as_float(((int)n + 127) << 23);
+  const float e = __fmul_rn(p, two_n);
+  return __frcp_rn(__fadd_rn(1.0f, e));
+}
+
 __device__ __forceinline__ void merge_top2(float& a1, float& a2, float b1, float b2) {
   // (a1 >= a2), (b1 >= b2) -> two largest of the four
   const float hi = fmaxf(a1, b1);
@@ -83,8 +107,14 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   // ---- scoring ----
   if (p.scoring == DLB_SCORE_SIGMOID) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? 1.0f / (1.0f + expf(-s[v])) : -CUDART_INF_F;
+    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? sigmoid_spec(s[v]) : -CUDART_INF_F;
   } else {
+    // softmax is monotone in the logit: without a bias the selection runs on the raw logits,
+    // which keeps the chosen ids independent of how exp() rounds
+    if (p.bias == nullptr) {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) c[v] = s[v];
+    }
     float m = -CUDART_INF_F;
 #pragma unroll
     for (int v = 0; v < VPL; ++v) m = fmaxf(m, s[v]);
@@ -101,10 +131,12 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? s[v] / sum : -CUDART_INF_F;
   }
+  if (p.scoring == DLB_SCORE_SIGMOID || p.bias != nullptr) {
 #pragma unroll
-  for (int v = 0; v < VPL; ++v) {
-    const bool valid = e0 + v < E;
-    c[v] = valid ? (p.bias != nullptr ? s[v] + __ldg(p.bias + e0 + v) : s[v]) : -CUDART_INF_F;
+    for (int v = 0; v < VPL; ++v) {
+      const bool valid = e0 + v < E;
+      c[v] = valid ? (p.bias != nullptr ? __fadd_rn(s[v], __ldg(p.bias + e0 + v)) : s[v]) : -CUDART_INF_F;
+    }
   }
 
   // ---- group selection ----
@@ -119,7 +151,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
       merge_top2(t1, t2, o1, o2);
     }
     const int my_group = lane / lanes_per_group;
-    const float my_score = (my_group < p.n_group) ? t1 + t2 : -CUDART_INF_F;
+    const float my_score = (my_group < p.n_group) ? __fadd_rn(t1, t2) : -CUDART_INF_F;
     int rank = 0;
     for (int g = 0; g < p.n_group; ++g) {
       const float gs = __shfl_sync(0xffffffffu, my_score, g * lanes_per_group);

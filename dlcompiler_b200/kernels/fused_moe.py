@@ -81,6 +81,22 @@ def _grouped_gemm(a, b, out, n_out, row_map, block_start, weights, numel, flags)
     _lib.check(rc, "moe_grouped_gemm")
 
 
+class _EventPair:
+    """Optional CUDA-event bracket around one launch on the current stream."""
+
+    def __init__(self, sink, name):
+        self.sink, self.name = sink, name
+        if sink is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+    def stop(self):
+        if self.sink is not None:
+            self.end.record()
+            self.sink.append((self.name, self.start, self.end))
+
+
 def fused_moe(hidden_states: torch.Tensor,
               w1: torch.Tensor,
               w2: torch.Tensor,
@@ -89,7 +105,8 @@ def fused_moe(hidden_states: torch.Tensor,
               topk: int,
               expert_offset: int = 0,
               num_experts: int = None,
-              renormalize: bool = False) -> torch.Tensor:
+              renormalize: bool = False,
+              _events: list = None) -> torch.Tensor:
     """Mixture-of-experts MLP: out[t] = sum_k w[t,k] * down_e(silu(gate_e(x_t)) * up_e(x_t)), e = ids[t,k].
 
     Arguments as in the reference (fused_moe.py:296-304): `w1` is [E, 2*I, H] with the gate
@@ -99,6 +116,9 @@ def fused_moe(hidden_states: torch.Tensor,
     Rounding points match the reference: GEMM outputs are rounded to the activation dtype,
     silu and the product are rounded separately, routing weights are applied in fp32 before the
     cast, and the top-k sum accumulates in fp32.
+
+    `_events`, when a list, receives (kernel name, start event, end event) for the two grouped
+    GEMM launches (used by the benchmark to time the dominant kernel inside a step).
     """
     dev = _lib.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids)
     assert hidden_states.dim() == 2 and w1.dim() == 3 and w2.dim() == 3
@@ -133,13 +153,17 @@ def fused_moe(hidden_states: torch.Tensor,
 
     a_sorted = _permute_rows(hidden_states, sorted_ids, num_post, numel, topk, cap)
     act = torch.empty((cap, inter), dtype=hidden_states.dtype, device=dev)
+    ev = _EventPair(_events, "grouped_gemm_gate_up_silu")
     _grouped_gemm(a_sorted, w1, act, inter, sorted_ids, block_start, None, numel, _lib.GEMM_FUSE_SILU)
+    ev.stop()
     if full_exp:
         partial = torch.empty((numel, H_out), dtype=hidden_states.dtype, device=dev)
     else:
         partial = torch.zeros((numel, H_out), dtype=hidden_states.dtype, device=dev)
+    ev = _EventPair(_events, "grouped_gemm_down_scatter")
     _grouped_gemm(act, w2, partial, H_out, sorted_ids, block_start, topk_weights, numel,
                   _lib.GEMM_WEIGHT | _lib.GEMM_SCATTER)
+    ev.stop()
     lib = _lib.load()
     with torch.cuda.device(dev):
         rc = lib.dlb_moe_combine(partial.data_ptr(), out.data_ptr(), M, topk, H_out, out.stride(0),

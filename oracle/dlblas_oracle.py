@@ -56,12 +56,37 @@ def _stable_topk(scores: torch.Tensor, k: int):
     return vals[..., :k], idx[..., :k]
 
 
+def sigmoid_spec(x: torch.Tensor) -> torch.Tensor:
+    """sigmoid as a fixed sequence of correctly-rounded fp32 operations (mul, add, sub, rint,
+    reciprocal; no fused multiply-add).  The CUDA router evaluates exactly this sequence, so both
+    sides produce bit-identical scores and near-ties cannot flip an expert id.  Accurate to
+    about 2 ulp of the true sigmoid:
+        t = clamp(-x, -87, 88); n = rint(t*log2e); r = (t - n*LN2_HI) - n*LN2_LO
+        e = Horner(1, 1, 1/2, 1/6, 1/24, 1/120, 1/720)(r) * 2^n;  sigmoid = 1 / (1 + e)
+    """
+    f = torch.float32
+    x = x.to(f)
+    c = lambda v: torch.tensor(v, dtype=torch.float64).to(f)          # nearest fp32 constant
+    t = torch.clamp(-x, -87.0, 88.0)
+    n = torch.round(t * c(1.44269502162933349609375))
+    r = t - n * c(0.693145751953125)
+    r = r - n * c(1.428606765330187045037746429443359375e-06)
+    p = c(1.38888892251998186111450195312e-03).expand_as(r)
+    for coef in (8.33333376795053482055664062500e-03, 4.16666679084300994873046875000e-02,
+                 1.66666671633720397949218750000e-01, 0.5, 1.0, 1.0):
+        p = p * r + c(coef)          # two roundings: fp32 mul, then fp32 add
+    two_n = ((n.to(torch.int32) + 127) << 23).view(f)
+    e = p * two_n
+    return torch.reciprocal(1.0 + e)
+
+
 def grouped_topk_gating(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, n_group: int = 1,
                         topk_group: int = 1, routed_scaling_factor: float = 1.0, renormalize: bool = True,
                         scoring_func: str = "sigmoid"):
     """Group-limited top-k routing (UNPINNED: no reference implementation exists).
 
-    Definition: scores = sigmoid(logits) or softmax(logits) in fp32; choice = scores + bias;
+    Definition: scores = sigmoid_spec(logits) or softmax(logits) in fp32; choice = scores + bias
+    (for softmax without bias the selection runs on the logits, which order identically);
     group score = sum of the 2 largest `choice` in each of the n_group equal groups; keep the
     topk_group best groups (ties: lower group index); experts of other groups get -inf;
     select top_k experts by `choice` (ties: lower expert index, output sorted by descending
@@ -70,8 +95,13 @@ def grouped_topk_gating(logits: torch.Tensor, bias: torch.Tensor | None, top_k: 
     """
     logits = logits.float()
     T, E = logits.shape
-    scores = torch.sigmoid(logits) if scoring_func == "sigmoid" else torch.softmax(logits, dim=-1)
-    choice = scores + bias.float().unsqueeze(0) if bias is not None else scores.clone()
+    scores = sigmoid_spec(logits) if scoring_func == "sigmoid" else torch.softmax(logits, dim=-1)
+    if bias is not None:
+        choice = scores + bias.float().unsqueeze(0)
+    elif scoring_func == "softmax":
+        choice = logits.clone()      # softmax is monotone: select on the logits, free of exp() rounding
+    else:
+        choice = scores.clone()
     if n_group > 1:
         grp = choice.view(T, n_group, E // n_group)
         g_scores = _stable_topk(grp, 2)[0].sum(dim=-1)                      # [T, n_group]

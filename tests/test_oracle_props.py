@@ -53,12 +53,21 @@ def test_grouped_gating_oracle_structure_and_margins():
     assert all(len(set(r.tolist())) <= wl.topk_group for r in groups)       # at most 4 groups used
     assert all(len(set(r.tolist())) == wl.top_k for r in ids)               # distinct experts
     torch.testing.assert_close(w.sum(-1), torch.full((2048,), wl.scale_factor), rtol=1e-5, atol=1e-5)
-    choice = torch.sigmoid(d["logits"]) + d["bias"]
+    choice = oracle.sigmoid_spec(d["logits"]) + d["bias"]
     picked = choice.gather(1, ids.long())
     assert torch.all(picked[:, 1:] <= picked[:, :-1])                       # descending order
     # fp64 decision margins: ids are well-defined if every margin is far above fp32 noise
     m = oracle.gating_margins(d["logits"], d["bias"], wl.top_k, wl.n_group, wl.topk_group)
     assert m.min() > 0
+
+
+def test_sigmoid_spec_accuracy_and_range():
+    x = torch.randn(1 << 16, generator=torch.Generator().manual_seed(3)) * 4
+    ref = torch.sigmoid(x.double())
+    rel = ((oracle.sigmoid_spec(x).double() - ref) / ref).abs().max()
+    assert rel < 5e-7
+    edge = oracle.sigmoid_spec(torch.tensor([-1e4, -88.0, 0.0, 88.0, 1e4]))
+    assert torch.isfinite(edge).all() and edge[2] == 0.5 and edge[-1] == 1.0 and edge[0] >= 0
 
 
 def test_gating_tie_break_is_lowest_index():
