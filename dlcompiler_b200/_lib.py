@@ -46,7 +46,15 @@ SIGNATURES = {
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_int,
                                  c_void_p, c_void_p]),
+    "dlb_paged_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_int,
+                                        c_void_p, c_void_p]),
 }
+
+DECODE_STATIC_FLOATS = 8 * 1024 * 1024
 
 _lib = None
 

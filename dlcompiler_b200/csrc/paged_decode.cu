@@ -19,6 +19,8 @@
 // swizzle-aware ldmatrix.  Each KV byte is read from HBM exactly once.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace dlb {
@@ -556,4 +558,89 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
                            : launch_decode<__nv_bfloat16, 64>(tk, tv, p, s);
   }
   return head_dim == 128 ? launch_decode<__half, 128>(tk, tv, p, s) : launch_decode<__half, 64>(tk, tv, p, s);
+}
+
+// ----------------------------------------------------------------------------
+// Allocation-free variant: the split-KV workspace lives in a fixed device array
+// ----------------------------------------------------------------------------
+// Some callers of a decode step cannot allocate device memory around the call:
+// a serving engine whose memory pool was sized once at start-up and handed out
+// completely to the KV cache, or a host thread that must not enter the allocator
+// because an allocation may synchronise the device (or fail) in the middle of a
+// latency-critical token loop.  For them the (acc, m, l) partials of the split
+// pass live in a file-scope device array instead of a caller-provided buffer.
+//
+// Limits and rules
+//   * the array holds DLB_DECODE_STATIC_FLOATS fp32 values (32 MiB); every GPU
+//     that loads this library carries it until the process exits;
+//   * a call needs batch * hq * max_splits * (head_dim + 2) floats (0 when
+//     max_splits == 1) and is rejected with DLB_ERR_TOO_LARGE beyond the limit;
+//   * the first call on each device resolves the array's device address (one
+//     cudaGetSymbolAddress with that device current); make that first call
+//     before starting any stream capture on the device;
+//   * all calls on a device share the array and it keeps the previous call's
+//     contents.  Nothing in it has to start at zero: every (sequence, head,
+//     split) slot the merge pass reads was written by the split pass of the same
+//     call.  Two calls whose kernels overlap on the GPU (different streams) race
+//     on it; serialise them.
+#define DLB_DECODE_STATIC_FLOATS (8ll * 1024 * 1024)
+
+namespace dlb {
+static __device__ __align__(256) float g_decode_scratch[DLB_DECODE_STATIC_FLOATS];
+
+// Device address of g_decode_scratch on the current device.  In host code the symbol's name
+// is only a handle, never an address a kernel may use; the address comes from the runtime.
+static int decode_scratch_address(float** out) {
+  static float* cache[64] = {nullptr};
+  static bool ready[64] = {false};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    set_last_error("paged_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  DLB_CHECK_ARG(dev >= 0 && dev < 64, DLB_ERR_UNSUPPORTED, "paged_decode_static: device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ready[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_error("paged_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : DLB_ERR_DRIVER;
+    }
+    cache[dev] = p;
+    ready[dev] = true;
+  }
+  *out = cache[dev];
+  return DLB_OK;
+}
+}  // namespace dlb
+
+extern "C" int dlb_paged_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       const void* block_table, const void* kv_seqlens, int64_t batch, int64_t hq,
+                                       int64_t hkv, int64_t head_dim, int64_t page_size, int64_t num_pages,
+                                       int64_t max_pages, int64_t q_stride_b, int64_t q_stride_h,
+                                       int64_t o_stride_b, int64_t o_stride_h, int64_t k_stride_page,
+                                       int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
+                                       int64_t v_stride_slot, int64_t v_stride_head, int64_t bt_stride,
+                                       int table_is_int64, int lens_is_int64, int64_t chunk, int64_t max_splits,
+                                       int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
+                                       void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(batch >= 0 && hq >= 1 && head_dim >= 1 && max_splits >= 1, DLB_ERR_BAD_ARG,
+                "paged_decode_static: bad sizes");
+  const int64_t need = dlb_paged_decode_workspace_floats(batch, hq, head_dim, max_splits);
+  DLB_CHECK_ARG(need <= DLB_DECODE_STATIC_FLOATS, DLB_ERR_TOO_LARGE,
+                "paged_decode_static: needs %lld workspace floats (batch*hq*max_splits*(head_dim+2)) but the static "
+                "scratch holds %lld; lower max_splits (larger chunk) or use dlb_paged_decode with your own buffer",
+                (long long)need, (long long)DLB_DECODE_STATIC_FLOATS);
+  float* scratch = nullptr;
+  const int rc = decode_scratch_address(&scratch);
+  if (rc != DLB_OK) return rc;
+  return dlb_paged_decode(q, k_cache, v_cache, out, block_table, kv_seqlens, scratch, batch, hq, hkv, head_dim,
+                          page_size, num_pages, max_pages, q_stride_b, q_stride_h, o_stride_b, o_stride_h,
+                          k_stride_page, k_stride_slot, k_stride_head, v_stride_page, v_stride_slot, v_stride_head,
+                          bt_stride, table_is_int64, lens_is_int64, chunk, max_splits, window, sm_scale, softcap,
+                          dtype, status, stream);
 }

@@ -119,6 +119,33 @@ int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, vo
                      int64_t max_splits, int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
                      void* stream);
 
+/* Capacity, in fp32 elements (32 MiB), of the fixed device array used by dlb_paged_decode_static. */
+#define DLB_DECODE_STATIC_FLOATS (8ll * 1024 * 1024)
+
+/* dlb_paged_decode without a caller-provided workspace: no counterpart in the reference (its
+ * wrapper allocates the split workspace with torch on every call, paged_attention.py:606).
+ * For callers that cannot allocate device memory around a decode step (a serving engine whose
+ * pool was handed out completely to the KV cache at start-up, or a latency-critical token loop
+ * that must stay out of the allocator because an allocation can synchronise the device or fail).
+ * The split-KV partials live in a device array that is part of the library image: every GPU that
+ * loads the library holds its 32 MiB until the process exits.  The call allocates nothing.
+ *   - needs dlb_paged_decode_workspace_floats(batch, hq, head_dim, max_splits) <=
+ *     DLB_DECODE_STATIC_FLOATS, otherwise it returns an error (status -5) and launches nothing;
+ *   - the first call on a device looks up the array's device address; make that call before any
+ *     stream capture on that device;
+ *   - all calls on a device share the array (it keeps the last call's contents; no part of it
+ *     needs clearing between calls), so calls whose kernels may overlap on the GPU must be
+ *     serialised by the caller.
+ * All other arguments are those of dlb_paged_decode. */
+int dlb_paged_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                            const void* block_table, const void* kv_seqlens, int64_t batch, int64_t hq, int64_t hkv,
+                            int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages,
+                            int64_t q_stride_b, int64_t q_stride_h, int64_t o_stride_b, int64_t o_stride_h,
+                            int64_t k_stride_page, int64_t k_stride_slot, int64_t k_stride_head,
+                            int64_t v_stride_page, int64_t v_stride_slot, int64_t v_stride_head, int64_t bt_stride,
+                            int table_is_int64, int lens_is_int64, int64_t chunk, int64_t max_splits, int64_t window,
+                            float sm_scale, float softcap, int dtype, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
