@@ -12,41 +12,35 @@
 
 namespace dlb {
 
-template <typename T> __device__ __forceinline__ float silu_mul_f32(float g, float u) {
-  return g / (1.0f + __expf(-g)) * u;
+__device__ __forceinline__ float silu_mul_f32(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
 template <typename T, int UNROLL>
 __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out,
-                                                               int64_t rows, int nvec /* N / 8 */,
-                                                               int64_t x_row_stride, int64_t out_row_stride,
-                                                               int n) {
+                                                               int nvec /* N / 8 */, int64_t x_row_stride,
+                                                               int64_t out_row_stride, int n) {
   using T2 = typename Elem<T>::T2;
-  const int64_t total = rows * (int64_t)nvec;
-  const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
+  // blockIdx.x = row, blockIdx.y = segment of the row: no integer division anywhere
+  const int64_t r = blockIdx.x;
+  const int c0 = blockIdx.y * (256 * UNROLL) + threadIdx.x;
+  const uint4* gp = reinterpret_cast<const uint4*>(x + r * x_row_stride);
+  const uint4* up = reinterpret_cast<const uint4*>(x + r * x_row_stride + n);
+  uint4* op = reinterpret_cast<uint4*>(out + r * out_row_stride);
 
   uint4 g[UNROLL], u[UNROLL];
-  int64_t orow[UNROLL];
-  int ocol[UNROLL];
 #pragma unroll
   for (int i = 0; i < UNROLL; ++i) {
-    const int64_t v = base + (int64_t)i * blockDim.x;
-    if (v < total) {
-      const int64_t r = v / nvec;
-      const int c = (int)(v - r * nvec);
-      orow[i] = r;
-      ocol[i] = c;
-      const uint4* gp = reinterpret_cast<const uint4*>(x + r * x_row_stride) + c;
-      const uint4* up = reinterpret_cast<const uint4*>(x + r * x_row_stride + n) + c;
-      g[i] = __ldcs(gp);
-      u[i] = __ldcs(up);
-    } else {
-      orow[i] = -1;
+    const int c = c0 + i * 256;
+    if (c < nvec) {
+      g[i] = __ldcs(gp + c);
+      u[i] = __ldcs(up + c);
     }
   }
 #pragma unroll
   for (int i = 0; i < UNROLL; ++i) {
-    if (orow[i] < 0) continue;
+    const int c = c0 + i * 256;
+    if (c >= nvec) continue;
     uint4 o;
     const T2* g2 = reinterpret_cast<const T2*>(&g[i]);
     const T2* u2 = reinterpret_cast<const T2*>(&u[i]);
@@ -55,9 +49,9 @@ __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restri
     for (int j = 0; j < 4; ++j) {
       const float2 gf = Elem<T>::to_f2(g2[j]);
       const float2 uf = Elem<T>::to_f2(u2[j]);
-      o2[j] = Elem<T>::from_f2(silu_mul_f32<T>(gf.x, uf.x), silu_mul_f32<T>(gf.y, uf.y));
+      o2[j] = Elem<T>::from_f2(silu_mul_f32(gf.x, uf.x), silu_mul_f32(gf.y, uf.y));
     }
-    __stcs(reinterpret_cast<uint4*>(out + orow[i] * out_row_stride) + ocol[i], o);
+    __stcs(op + c, o);
   }
 }
 
@@ -74,7 +68,7 @@ __global__ void __launch_bounds__(256) silu_and_mul_scalar_kernel(const T* __res
     const int c = (int)(idx - r * n);
     const float g = Elem<T>::to_f(x[r * x_row_stride + c]);
     const float u = Elem<T>::to_f(x[r * x_row_stride + n + c]);
-    out[r * out_row_stride + c] = Elem<T>::from_f(silu_mul_f32<T>(g, u));
+    out[r * out_row_stride + c] = Elem<T>::from_f(silu_mul_f32(g, u));
   }
 }
 
@@ -85,14 +79,29 @@ static int launch_silu(const void* x, void* out, int64_t rows, int n, int64_t xs
                       (((uintptr_t)x & 15) == 0) && (((uintptr_t)out & 15) == 0);
   if (vec_ok) {
     if constexpr (sizeof(T) == 2) {
-      constexpr int UNROLL = 4;
       const int nvec = n / VEC;
-      const int64_t total = rows * (int64_t)nvec;
-      const int64_t per_block = 256 * UNROLL;
-      const int64_t blocks = (total + per_block - 1) / per_block;
-      DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "silu_and_mul: too many blocks");
-      silu_and_mul_vec_kernel<T, UNROLL><<<(unsigned)blocks, 256, 0, stream>>>(
-          (const T*)x, (T*)out, rows, nvec, xs, os, n);
+      // vectors per thread: the choice that wastes the fewest idle threads in a row's last block
+      int best_u = 1;
+      int64_t best_waste = -1;
+      for (int u : {1, 2, 4, 8}) {
+        const int per_block = 256 * u;
+        const int64_t waste = (int64_t)((nvec + per_block - 1) / per_block) * per_block - nvec;
+        if (best_waste < 0 || waste < best_waste || (waste == best_waste && u <= 4)) {
+          best_waste = waste;
+          best_u = u;
+        }
+      }
+      const int segs = (nvec + 256 * best_u - 1) / (256 * best_u);
+      DLB_CHECK_ARG(rows <= 0x7fffffffLL && segs <= 65535, DLB_ERR_TOO_LARGE, "silu_and_mul: grid too large");
+      const dim3 grid((unsigned)rows, (unsigned)segs);
+      const T* xp = (const T*)x;
+      T* op = (T*)out;
+      switch (best_u) {
+        case 1: silu_and_mul_vec_kernel<T, 1><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        case 2: silu_and_mul_vec_kernel<T, 2><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        case 4: silu_and_mul_vec_kernel<T, 4><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        default: silu_and_mul_vec_kernel<T, 8><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+      }
     }
   } else {
     const int64_t total = rows * (int64_t)n;
