@@ -165,37 +165,51 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   }
 
   // ---- top-k: k rounds of warp arg-max (ties -> lower expert index) ----
+  // Scores become order-preserving unsigned keys so that one hardware warp reduction
+  // (redux.sync) finds the maximum; a second one picks the lowest expert index among equals.
+  // Each lane caches its local best; only the winning lane rescans after a round.
+  uint32_t key[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    const uint32_t b = __float_as_uint(c[v]);
+    key[v] = (b & 0x80000000u) ? ~b : (b | 0x80000000u);      // -inf maps to 0x007fffff: below every finite score
+  }
+  uint32_t lbest = 0;
+  int lidx = 0;
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    if (key[v] > lbest) {   // strict: the lower index wins a tie inside the lane
+      lbest = key[v];
+      lidx = v;
+    }
+  }
   float wsum = 0.f;
   float my_w = 0.f;   // lane i < K keeps weight i
   int my_id = 0;
   for (int k = 0; k < p.top_k; ++k) {
-    float best = -CUDART_INF_F;
-    int best_e = 0x7fffffff;
-    float best_s = 0.f;
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, lbest);
+    const int cand = (lbest == wmax) ? e0 + lidx : 0x7fffffff;
+    const int best_e = __reduce_min_sync(0xffffffffu, cand);
+    const int owner = best_e / VPL;
+    float ls = 0.f;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      if (c[v] > best) {  // strict: the lower index wins a tie inside the lane
-        best = c[v];
-        best_e = e0 + v;
-        best_s = s[v];
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
-      if (ob > best || (ob == best && oe < best_e)) {
-        best = ob;
-        best_e = oe;
-        best_s = os;
-      }
-    }
-    // every lane now agrees on (best, best_e, best_s)
-    if (best_e >= e0 && best_e < e0 + VPL) {
+    for (int v = 0; v < VPL; ++v)
+      if (v == lidx) ls = s[v];
+    const float best_s = __shfl_sync(0xffffffffu, ls, owner);
+    if (lane == owner) {
+      // retire the winner and rescan this lane only
 #pragma unroll
       for (int v = 0; v < VPL; ++v)
-        if (e0 + v == best_e) c[v] = -CUDART_INF_F;
+        if (v == lidx) key[v] = 0;
+      lbest = 0;
+      lidx = 0;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        if (key[v] > lbest) {
+          lbest = key[v];
+          lidx = v;
+        }
+      }
     }
     wsum += best_s;
     if (lane == k) {
