@@ -360,21 +360,35 @@ def run_ours(args):
     else:
         from dlcompiler_b200.distributed import ep_moe
 
-        ctx = ep_moe.EpMoeContext(dist.group.WORLD, wl.experts, dev)
+        t_local = wl.tokens // world
+        exchange = args.exchange
+        if exchange == "peer":
+            try:
+                ctx = ep_moe.EpPeerContext(dist.group.WORLD, wl.experts, dev, t_local, wl.top_k, wl.hidden, wl.hidden,
+                                           wl.inter)
+                ep_step = ep_moe.ep_fused_moe_peer
+                launches = ep_moe.PEER_KERNELS_PER_STEP
+            except Exception as exc:  # symmetric memory unavailable on this box: NCCL exchange instead
+                print(f"[bench] peer-memory exchange unavailable ({exc!r}); using the NCCL all-to-all path",
+                      file=sys.stderr)
+                exchange = "nccl"
+        if exchange == "nccl":
+            ctx = ep_moe.EpMoeContext(dist.group.WORLD, wl.experts, dev)
+            ep_step = ep_moe.ep_fused_moe
+            launches = ep_moe.KERNELS_PER_STEP
         e_local = wl.experts // world
         wts = wl.make()
         w1 = wts["w1"][rank * e_local:(rank + 1) * e_local].to(dev)
         w2 = wts["w2"][rank * e_local:(rank + 1) * e_local].to(dev)
         del wts
-        t_local = wl.tokens // world
         sl = slice(rank * t_local, (rank + 1) * t_local)
         hs, tw, ti = d["hidden_states"][sl].to(dev), tw_cpu[sl].to(dev), ti_cpu[sl].to(dev)
         events = []
 
         def step():
-            return ep_moe.ep_fused_moe(ctx, hs, w1, w2, tw, ti, wl.top_k, _events=events)
+            return ep_step(ctx, hs, w1, w2, tw, ti, wl.top_k, _events=events)
 
-        launches_per_step = ep_moe.KERNELS_PER_STEP
+        launches_per_step = launches
         with ClockSampler(local_rank) as clk:
             ms = time_steps(step, args.steps, args.warmup, barrier)
         torch.cuda.synchronize()
@@ -391,7 +405,7 @@ def run_ours(args):
             hs_d.copy_(hs_h, non_blocking=True)
             tw_d.copy_(tw_h, non_blocking=True)
             ti_d.copy_(ti_h, non_blocking=True)
-            out = ep_moe.ep_fused_moe(ctx, hs_d, w1, w2, tw_d, ti_d, wl.top_k)
+            out = ep_step(ctx, hs_d, w1, w2, tw_d, ti_d, wl.top_k)
             out_h.copy_(out, non_blocking=True)
 
         ms_e2e = time_steps(step_e2e, args.steps, args.warmup, barrier)
@@ -402,7 +416,9 @@ def run_ours(args):
         t = torch.tensor([ms, ms_e2e, gemm_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e, gemm_ms = t.tolist()
-        parallelism = f"ep{world}: tokens and experts sharded over {world} ranks, NCCL all-to-all dispatch/combine"
+        how = ("dispatch/combine by our own kernels over NVLink peer memory" if exchange == "peer"
+               else "NCCL all-to-all dispatch/combine")
+        parallelism = f"ep{world}: tokens and experts sharded over {world} ranks, {how}"
         flops = wl.flops()
 
     tflops = flops / ms / 1e9
@@ -457,6 +473,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ops", default="all", choices=["all", "none"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: token exchange by our peer-memory kernels (default) or by NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--cpu-sample", type=int, default=4096)
     args = ap.parse_args()

@@ -34,6 +34,15 @@ SIGNATURES = {
     "dlb_moe_grouped_gemm": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
                                      c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                      c_int, c_void_p, c_void_p]),
+    "dlb_moe_grouped_gemm_peer": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                          c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int64, c_int, c_void_p, c_void_p]),
+    "dlb_ep_plan": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "dlb_ep_dispatch": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int64,
+                                c_void_p]),
+    "dlb_ep_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

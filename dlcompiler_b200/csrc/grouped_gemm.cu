@@ -49,6 +49,8 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + CTRL_BYTES;
 constexpr int FLAG_FUSE_SILU = 1;
 constexpr int FLAG_WEIGHT = 2;
 constexpr int FLAG_SCATTER = 4;
+constexpr int FLAG_PEER = 8;       // scatter to (rank, slot) taken from row_meta: plain stores into peer memory
+constexpr int MAX_PEERS = 16;
 }  // namespace gg
 
 struct GroupedGemmParams {
@@ -66,6 +68,8 @@ struct GroupedGemmParams {
   int max_m_blocks;                  // rows of A / 128
   int idesc;
   int* status;
+  const int32_t* row_meta;           // FLAG_PEER: (source rank << 24) | slot for every row
+  void* peer_out[gg::MAX_PEERS];     // FLAG_PEER: base of every rank's result buffer
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -109,6 +113,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   constexpr bool kSilu = (FLAGS & FLAG_FUSE_SILU) != 0;
   constexpr bool kWeight = (FLAGS & FLAG_WEIGHT) != 0;
   constexpr bool kScatter = (FLAGS & FLAG_SCATTER) != 0;
+  constexpr bool kPeer = (FLAGS & FLAG_PEER) != 0;
   constexpr int BN_OUT = kSilu ? 128 : 256;   // output columns per tile
 
   extern __shared__ uint8_t smem_raw[];
@@ -241,13 +246,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int64_t out_row = sorted_row;
       bool row_valid = true;
       float w = 1.0f;
-      if constexpr (kWeight || kScatter) {
+      if constexpr (kWeight || kScatter || kPeer) {
         const int sid = p.sorted_token_ids[sorted_row];
         row_valid = sid < p.numel;
         if constexpr (kScatter) out_row = row_valid ? sid : 0;
         if constexpr (kWeight) w = row_valid ? p.topk_weights[sid] : 0.f;
       }
       T* orow = out + out_row * p.out_row_stride + col0;
+      if constexpr (kPeer) {
+        // the row goes back to the rank that sent it, at the slot it came from (peer memory, plain stores)
+        const int meta = row_valid ? p.row_meta[sorted_row] : 0;
+        orow = reinterpret_cast<T*>(p.peer_out[(meta >> 24) & (MAX_PEERS - 1)]) +
+               (int64_t)(meta & 0xffffff) * p.out_row_stride + col0;
+      }
 
       if constexpr (kSilu) {
 #pragma unroll 1
@@ -296,6 +307,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
     }
+    if constexpr (kPeer) __threadfence_system();   // peer stores performed before the kernel retires
   }
 
   // ------------------------------ teardown ------------------------------
@@ -324,17 +336,18 @@ static int launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, const Gr
 
 }  // namespace dlb
 
-extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
-                                    int num_experts, int64_t rows_per_expert, int64_t k, int64_t b_row_stride,
-                                    void* out, int64_t out_row_stride, int64_t n_out,
-                                    const int32_t* sorted_token_ids, const int32_t* block_start,
-                                    const float* topk_weights, int64_t numel, int flags, int dtype,
-                                    int32_t* status, void* stream) {
-  using namespace dlb;
+namespace dlb {
+static int grouped_gemm_impl(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b, int num_experts,
+                             int64_t rows_per_expert, int64_t k, int64_t b_row_stride, void* out,
+                             int64_t out_row_stride, int64_t n_out, const int32_t* sorted_token_ids,
+                             const int32_t* block_start, const float* topk_weights, int64_t numel, int flags,
+                             int dtype, int32_t* status, void* stream, const int32_t* row_meta,
+                             void* const* peer_out, int num_peers) {
   using namespace dlb::gg;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "grouped_gemm: dtype %d (need fp16 or bf16)", dtype);
-  DLB_CHECK_ARG(a && b && out && sorted_token_ids && block_start, DLB_ERR_BAD_ARG, "grouped_gemm: null pointer");
+  DLB_CHECK_ARG(a && b && sorted_token_ids && block_start, DLB_ERR_BAD_ARG, "grouped_gemm: null pointer");
+  DLB_CHECK_ARG(out != nullptr || (flags & FLAG_PEER), DLB_ERR_BAD_ARG, "grouped_gemm: null output");
   DLB_CHECK_ARG(num_experts >= 1 && num_experts <= MAX_EXPERTS, DLB_ERR_UNSUPPORTED, "grouped_gemm: experts=%d",
                 num_experts);
   DLB_CHECK_ARG(a_rows >= 0 && a_rows % BM == 0, DLB_ERR_BAD_ARG,
@@ -356,6 +369,13 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row
   } else {
     DLB_CHECK_ARG(rows_per_expert >= n_out, DLB_ERR_BAD_ARG, "grouped_gemm: rows_per_expert < n_out");
     if (flags & FLAG_WEIGHT) DLB_CHECK_ARG(topk_weights != nullptr, DLB_ERR_BAD_ARG, "grouped_gemm: null weights");
+  }
+  if (flags & FLAG_PEER) {
+    DLB_CHECK_ARG(row_meta != nullptr && peer_out != nullptr && num_peers >= 1 && num_peers <= MAX_PEERS,
+                  DLB_ERR_BAD_ARG, "grouped_gemm: peer scatter needs row_meta and 1..%d peer buffers", MAX_PEERS);
+    for (int i = 0; i < num_peers; ++i)
+      DLB_CHECK_ARG(peer_out[i] != nullptr && (((uintptr_t)peer_out[i]) & 15) == 0, DLB_ERR_ALIGNMENT,
+                    "grouped_gemm: peer buffer %d is null or unaligned", i);
   }
   if (a_rows == 0) return DLB_OK;
 
@@ -381,6 +401,8 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row
   p.max_m_blocks = (int)(a_rows / BM);
   p.idesc = (int)make_idesc_f16(BM, UMMA_N, dtype == DLB_DTYPE_BF16 ? 1u : 0u, 0u, 0u);
   p.status = status;
+  p.row_meta = row_meta;
+  for (int i = 0; i < MAX_PEERS; ++i) p.peer_out[i] = (peer_out != nullptr && i < num_peers) ? peer_out[i] : nullptr;
 
   const int grid = sm_count(current_device());
   cudaStream_t s = (cudaStream_t)stream;
@@ -400,8 +422,39 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row
     case FLAG_WEIGHT | FLAG_SCATTER:
       return bf ? launch_grouped<__nv_bfloat16, FLAG_WEIGHT | FLAG_SCATTER>(ta, tb, p, grid, s)
                 : launch_grouped<__half, FLAG_WEIGHT | FLAG_SCATTER>(ta, tb, p, grid, s);
+    case FLAG_WEIGHT | FLAG_PEER:
+      return bf ? launch_grouped<__nv_bfloat16, FLAG_WEIGHT | FLAG_PEER>(ta, tb, p, grid, s)
+                : launch_grouped<__half, FLAG_WEIGHT | FLAG_PEER>(ta, tb, p, grid, s);
     default:
       set_last_error("grouped_gemm: unsupported flag combination %d", flags);
       return DLB_ERR_UNSUPPORTED;
   }
+}
+}  // namespace dlb
+
+extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
+                                    int num_experts, int64_t rows_per_expert, int64_t k, int64_t b_row_stride,
+                                    void* out, int64_t out_row_stride, int64_t n_out,
+                                    const int32_t* sorted_token_ids, const int32_t* block_start,
+                                    const float* topk_weights, int64_t numel, int flags, int dtype,
+                                    int32_t* status, void* stream) {
+  DLB_CHECK_ARG((flags & dlb::gg::FLAG_PEER) == 0, DLB_ERR_BAD_ARG,
+                "grouped_gemm: peer scatter is only available through dlb_moe_grouped_gemm_peer");
+  return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride, out,
+                                out_row_stride, n_out, sorted_token_ids, block_start, topk_weights, numel, flags,
+                                dtype, status, stream, nullptr, nullptr, 0);
+}
+
+extern "C" int dlb_moe_grouped_gemm_peer(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
+                                         int num_experts, int64_t rows_per_expert, int64_t k, int64_t b_row_stride,
+                                         void* const* peer_out, int num_peers, int64_t out_row_stride,
+                                         int64_t n_out, const int32_t* sorted_token_ids,
+                                         const int32_t* block_start, const float* row_weights,
+                                         const int32_t* row_meta, int64_t numel, int dtype, int32_t* status,
+                                         void* stream) {
+  using namespace dlb::gg;
+  return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride,
+                                peer_out != nullptr && num_peers > 0 ? peer_out[0] : nullptr, out_row_stride, n_out,
+                                sorted_token_ids, block_start, row_weights, numel, FLAG_WEIGHT | FLAG_PEER, dtype,
+                                status, stream, row_meta, peer_out, num_peers);
 }

@@ -165,3 +165,134 @@ def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weig
     inverse[sorted_slots.long()] = torch.arange(numel, dtype=torch.int32, device=dev)
     partial = ops.gather_rows(back, inverse, numel, 1)                            # slot order [T*topk, H]
     return ops.combine(partial, T, topk)
+
+
+# ----------------------------------------------------------------------------------------------
+# Peer-memory variant: dispatch and combine are plain NVLink stores issued by our own kernels
+# ----------------------------------------------------------------------------------------------
+class EpPeerContext:
+    """Symmetric buffers and pointer tables for the peer-memory exchange (see csrc/ep_moe.cu).
+
+    Every rank allocates the same buffers through torch's symmetric-memory allocator (plumbing
+    only: it hands out device memory that every rank of the node can address) and keeps, for
+    each buffer, the device pointers of all ranks' copies.  Capacity covers the worst case of
+    every slot of every rank landing on one rank.
+    """
+
+    def __init__(self, group, num_experts: int, device, max_tokens_per_rank: int, top_k: int, hidden: int,
+                 out_hidden: int, inter: int, dtype=torch.bfloat16):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .. import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device
+        self.num_experts = num_experts
+        if num_experts % self.world != 0:
+            raise AssertionError(f"{num_experts} experts do not divide over {self.world} ranks")
+        self.experts_per_rank = num_experts // self.world
+        self.top_k, self.hidden, self.out_hidden, self.inter, self.dtype = top_k, hidden, out_hidden, inter, dtype
+        self.max_slots = max_tokens_per_rank * top_k
+        cap = self.world * self.max_slots + self.experts_per_rank * 128
+        self.cap = (cap + 127) // 128 * 128
+        if self.cap >= 1 << 24:
+            raise AssertionError("receive capacity exceeds the 24-bit slot field of the row metadata")
+
+        def sym(shape, dt):
+            t = symm_mem.empty(shape, dtype=dt, device=device)
+            hdl = symm_mem.rendezvous(t, group)
+            ptrs = []
+            for r in range(self.world):
+                remote = hdl.get_buffer(r, t.shape, t.dtype)
+                ptrs.append(remote.data_ptr())
+            if ptrs[self.rank] != t.data_ptr():
+                raise AssertionError("symmetric buffer pointer table does not contain the local buffer")
+            table = (ctypes.c_void_p * self.world)(*ptrs)
+            return t, hdl, table
+
+        self.counts, self._h_counts, self.counts_tbl = sym((self.world * num_experts,), torch.int32)
+        self.flags, self._h_flags, self.flags_tbl = sym((8 * 16,), torch.int32)
+        self.rows, self._h_rows, self.rows_tbl = sym((self.cap, hidden), dtype)
+        self.w, self._h_w, self.w_tbl = sym((self.cap,), torch.float32)
+        self.meta, self._h_meta, self.meta_tbl = sym((self.cap,), torch.int32)
+        self.back, self._h_back, self.back_tbl = sym((self.max_slots, out_hidden), dtype)
+        for t in (self.counts, self.flags, self.rows, self.w, self.meta, self.back):
+            t.zero_()
+        # plan outputs and the activation buffer are ordinary local memory
+        self.dest_base = torch.empty(num_experts, dtype=torch.int32, device=device)
+        self.block_start = torch.empty(self.experts_per_rank + 1, dtype=torch.int32, device=device)
+        self.num_post = torch.empty(1, dtype=torch.int32, device=device)
+        self.row_map = torch.empty(self.cap, dtype=torch.int32, device=device)
+        self.act = torch.empty((self.cap, inter), dtype=dtype, device=device)
+        self.epoch = 0
+        self.status = _lib.status_word(device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+
+PEER_KERNELS_PER_STEP = 8  # align, plan, dispatch, barrier, gemm, gemm(+peer scatter), barrier, combine
+
+
+def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int,
+                      _events: list = None):
+    """Expert-parallel fused_moe whose token exchange runs inside our own kernels over peer memory.
+
+    Same contract as `ep_fused_moe`.  Per step: sort slots -> publish counts + cross-GPU barrier +
+    receive layout (dlb_ep_plan) -> rows stored into the owners' buffers (dlb_ep_dispatch) ->
+    barrier -> grouped GEMM gate/up+silu on the received rows -> grouped GEMM down whose epilogue
+    stores each weighted row into the sending rank's result buffer -> barrier -> top-k combine.
+    Nothing returns to the host in between, so the launches queue back to back.
+    """
+    from .. import _lib
+    from ..kernels.fused_moe import _EventPair, _grouped_gemm
+
+    lib = _lib.load()
+    dev = hidden_states.device
+    T, H = hidden_states.shape
+    numel = T * topk
+    assert numel <= ctx.max_slots and H == ctx.hidden and topk == ctx.top_k
+    assert hidden_states.dtype == ctx.dtype and hidden_states.stride(1) == 1
+    assert w1_local.is_contiguous() and w2_local.is_contiguous()
+    ids = topk_ids.reshape(-1)
+    if ids.dtype not in (torch.int32, torch.int64):
+        ids = ids.to(torch.int64)
+    ids = ids.contiguous()
+    tw = topk_weights.to(torch.float32).reshape(-1).contiguous()
+    ctx.epoch += 1
+    stream = _lib.stream_ptr(dev)
+    sorted_slots, prefix = CudaOps.sort_slots(ids, ctx.num_experts)
+    with torch.cuda.device(dev):
+        rc = lib.dlb_ep_plan(prefix.data_ptr(), ctx.counts_tbl, ctx.flags_tbl, ctx.dest_base.data_ptr(),
+                             ctx.block_start.data_ptr(), ctx.num_post.data_ptr(), ctx.row_map.data_ptr(), ctx.rank,
+                             ctx.world, ctx.num_experts, ctx.cap, ctx.epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "ep_plan")
+        rc = lib.dlb_ep_dispatch(hidden_states.data_ptr(), hidden_states.stride(0), H, hidden_states.element_size(),
+                                 ids.data_ptr(), int(ids.dtype == torch.int64), tw.data_ptr(),
+                                 sorted_slots.data_ptr(), prefix.data_ptr(), ctx.dest_base.data_ptr(), ctx.rows_tbl,
+                                 ctx.w_tbl, ctx.meta_tbl, numel, topk, ctx.rank, ctx.world, ctx.num_experts, ctx.cap,
+                                 stream)
+        _lib.check(rc, "ep_dispatch")
+        rc = lib.dlb_ep_barrier(ctx.flags_tbl, 1, ctx.rank, ctx.world, ctx.epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "ep_barrier")
+    ev = _EventPair(_events, "grouped_gemm_gate_up_silu")
+    _grouped_gemm(ctx.rows, w1_local, ctx.act, ctx.inter, ctx.row_map, ctx.block_start, None, ctx.cap,
+                  _lib.GEMM_FUSE_SILU)
+    ev.stop()
+    E_local, H_out, inter = w2_local.shape
+    ev = _EventPair(_events, "grouped_gemm_down_peer_scatter")
+    with torch.cuda.device(dev):
+        rc = lib.dlb_moe_grouped_gemm_peer(ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(),
+                                           E_local, H_out, inter, w2_local.stride(1), ctx.back_tbl, ctx.world,
+                                           ctx.back.stride(0), H_out, ctx.row_map.data_ptr(),
+                                           ctx.block_start.data_ptr(), ctx.w.data_ptr(), ctx.meta.data_ptr(), ctx.cap,
+                                           _lib.dtype_code(ctx.act), ctx.status.data_ptr(), stream)
+        _lib.check(rc, "moe_grouped_gemm_peer")
+    ev.stop()
+    with torch.cuda.device(dev):
+        rc = lib.dlb_ep_barrier(ctx.flags_tbl, 2, ctx.rank, ctx.world, ctx.epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "ep_barrier")
+    return CudaOps.combine(ctx.back[:numel], T, topk)

@@ -87,6 +87,40 @@ int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, co
                          const int32_t* block_start, const float* topk_weights, int64_t numel, int flags,
                          int dtype, int32_t* status, void* stream);
 
+/* dlb_moe_grouped_gemm with the DLB_GEMM_WEIGHT epilogue whose rows are stored straight into the
+ * result buffers of the ranks that sent them (plain stores into peer memory over NVLink):
+ * row p goes to peer_out[row_meta[p] >> 24] + (row_meta[p] & 0xffffff) * out_row_stride.
+ * Fuses the down projection of python/dlBLAS/dlblas/kernels/fused_moe.py:359-373 with the
+ * expert-parallel combine exchange; the reference has no such exchange (it keeps tokens replicated,
+ * fused_moe.py:113-114, 329-332). */
+int dlb_moe_grouped_gemm_peer(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b, int num_experts,
+                              int64_t rows_per_expert, int64_t k, int64_t b_row_stride, void* const* peer_out,
+                              int num_peers, int64_t out_row_stride, int64_t n_out,
+                              const int32_t* sorted_token_ids, const int32_t* block_start, const float* row_weights,
+                              const int32_t* row_meta, int64_t numel, int dtype, int32_t* status, void* stream);
+
+/* Expert-parallel exchange over peer memory (one process per GPU; `*_sym` arguments are HOST arrays of
+ * `world` device pointers, one per rank, to buffers of identical size on every rank).  No counterpart
+ * in the reference.
+ *   dlb_ep_plan      publishes this rank's per-expert counts (expert_prefix = prefix sums from
+ *                    dlb_moe_align_block_size with block 1) into every rank's count matrix
+ *                    (counts_sym: int32 [world][experts]), synchronises the ranks through flags_sym
+ *                    (int32 [8][16], zero-initialised, epoch must grow by one per step), and derives the
+ *                    receive layout: dest_base[experts], block_start[experts/world + 1],
+ *                    num_post_padded[1], row_map[cap] (p for rows that will hold a token, cap otherwise).
+ *   dlb_ep_dispatch  stores every local slot's hidden row, routing weight and (rank << 24 | slot) into
+ *                    the owner rank's rows_sym [cap][hidden], w_sym [cap], meta_sym [cap].
+ *   dlb_ep_barrier   cross-GPU barrier on flag slot 1..7 (bounded wait; timeout -> status word). */
+int dlb_ep_plan(const int32_t* expert_prefix, void* const* counts_sym, void* const* flags_sym, int32_t* dest_base,
+                int32_t* block_start, int32_t* num_post_padded, int32_t* row_map, int rank, int world, int experts,
+                int64_t cap, int epoch, int32_t* status, void* stream);
+int dlb_ep_dispatch(const void* hidden, int64_t hidden_row_stride, int64_t hidden_cols, int elem_size,
+                    const void* topk_ids, int ids_are_int64, const float* topk_weights, const int32_t* sorted_slots,
+                    const int32_t* expert_prefix, const int32_t* dest_base, void* const* rows_sym,
+                    void* const* w_sym, void* const* meta_sym, int64_t numel, int top_k, int rank, int world,
+                    int experts, int64_t cap, void* stream);
+int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status, void* stream);
+
 /* out[t, :] = sum over k of partial[t * top_k + k, :] (fp32 accumulate, one rounding): the
  * `intermediate_cache2.sum(dim=1)` of python/dlBLAS/dlblas/kernels/fused_moe.py:375. */
 int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
