@@ -81,6 +81,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// Packed pairs of fp32 in one 64-bit register (sm_100 f32x2 arithmetic)
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 struct PrefillParams {
   void* out;
   float* lse;                     // [hq, total] or null
@@ -256,24 +281,28 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[s]);
 
-      // scale + mask
+      // mask (diagonal / tail blocks only), on the raw scores
       const int key0 = j * BN;
       const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0);
+      if (need_mask) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int key = key0 + h * 32 + c;
+            const bool visible = key < kv_end && (!p.causal || key <= q_pos);
+            if (!visible) sr[h][c] = 0xff800000u;   // -inf
+          }
+        }
+      }
+      // row max of the raw scores (3-input max), scaled once: scale > 0 keeps the order
       float mx = -CUDART_INF_F;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float v = __uint_as_float(sr[h][c]) * p.scale_log2;
-          if (need_mask) {
-            const int key = key0 + h * 32 + c;
-            const bool visible = key < kv_end && (!p.causal || key <= q_pos);
-            v = visible ? v : -CUDART_INF_F;
-          }
-          sr[h][c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1]));
       }
+      mx *= p.scale_log2;
       // lazy rescale decision
       float alpha = 1.f;
       bool rescale = false;
@@ -284,22 +313,35 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         m_ref = mx;
         rescale = true;
       }
-      // exponentiate, pack to 16 bit
+      // p = 2^(s * scale - m): one packed FMA per two scores, exponentials on the SFU,
+      // packed adds for the row sum, one conversion per pair
       uint32_t pk[32];
-      float psum = 0.f;
-      const float mref_safe = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
+      const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
+      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
+      const uint64_t negm2 = pack_f2(neg_m, neg_m);
+      uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float e0 = fast_exp2(__uint_as_float(sr[h][c]) - mref_safe);
-          const float e1 = fast_exp2(__uint_as_float(sr[h][c + 1]) - mref_safe);
-          psum += e0 + e1;
-          if constexpr (sizeof(T) == 2) {
-            typename Elem<T>::T2 v2 = Elem<T>::from_f2(e0, e1);
-            pk[h * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&v2);
-          }
+        for (int c = 0; c < 32; c += 4) {
+          float x0, x1, x2, x3;
+          unpack_f2(fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2), x0, x1);
+          unpack_f2(fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2), x2,
+                    x3);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1), e2 = fast_exp2(x2), e3 = fast_exp2(x3);
+          sum2a = add_f2(sum2a, pack_f2(e0, e1));
+          sum2b = add_f2(sum2b, pack_f2(e2, e3));
+          typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
+          typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
+          pk[h * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&v01);
+          pk[h * 16 + c / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
         }
+      }
+      float psum;
+      {
+        float a, b;
+        unpack_f2(add_f2(sum2a, sum2b), a, b);
+        psum = a + b;
       }
       l_sum = l_sum * alpha + psum;
 
