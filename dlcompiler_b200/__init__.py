@@ -8,6 +8,8 @@ no Triton, no backend dispatch and no CPU fallback on this path.
 from . import _lib
 from ._lib import DlblasError, check_device_status, is_built
 from .kernels.activation import silu_and_mul
+from .kernels.decode_attention import decode_attention_fwd
+from .kernels.flash_attention import flash_attention_fwd, flash_attention_v2
 from .kernels.fused_moe import fused_moe, fused_moe_kernel_launcher, get_start_end, moe_align_block_size
 from .kernels.moe_gating import grouped_topk_gating, softmax_topk
 from .kernels.paged_attention import paged_attention_fwd
@@ -16,5 +18,5 @@ from .kernels.prefill_attention import context_attention_fwd
 __all__ = [
     "DlblasError", "check_device_status", "is_built", "silu_and_mul", "fused_moe", "fused_moe_kernel_launcher",
     "get_start_end", "moe_align_block_size", "grouped_topk_gating", "softmax_topk", "paged_attention_fwd",
-    "context_attention_fwd",
+    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2",
 ]

@@ -32,20 +32,25 @@ namespace dlb {
 namespace fp {
 constexpr int BM = 128;           // query rows per CTA
 constexpr int BN = 64;            // keys per block
-constexpr int D = 128;            // head size
 constexpr int THREADS = 192;
-constexpr int Q_BYTES = BM * D * 2;            // 32 KiB (two 64-wide boxes)
-constexpr int KV_BYTES = BN * D * 2;           // 16 KiB (two 64-wide boxes)
+constexpr int Q_BOX = BM * 128;   // one 64-wide (128 B) column box of the Q tile
+constexpr int KV_BOX = BN * 128;  // one 64-wide column box of a K or V tile
 constexpr int P_BYTES = BM * BN * 2;           // 16 KiB
 constexpr int KV_STAGES = 2;
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + Q_BYTES;
-constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
-constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-constexpr int OFF_CTRL = OFF_P + P_BYTES;
-constexpr int SMEM_BYTES = OFF_CTRL + 128;   // two CTAs (plus 1 KiB system reserve each) fit one SM
-constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,256)
+constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
+// shared-memory layout for head size D (64 or 128)
+template <int D> struct Layout {
+  static constexpr int BOXES = D / 64;
+  static constexpr int Q_BYTES = BOXES * Q_BOX;
+  static constexpr int KV_BYTES = BOXES * KV_BOX;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
+  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
+  static constexpr int OFF_CTRL = OFF_P + P_BYTES;
+  static constexpr int SMEM_BYTES = OFF_CTRL + 128;   // D=128: two CTAs (plus 1 KiB system reserve each) fit one SM
+};
 }  // namespace fp
 
 static int make_tmap_tokens(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t tokens,
@@ -122,11 +127,15 @@ struct PrefillParams {
   int* status;
 };
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(fp::THREADS, 2)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
   using namespace fp;
+  using L = Layout<D>;
+  constexpr int BOXES = L::BOXES;
+  constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
+  constexpr int OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_P = L::OFF_P, OFF_CTRL = L::OFF_CTRL;
   // ---- which tile ----
   const int head = blockIdx.x % p.hq;
   const int t_lin = blockIdx.x / p.hq;
@@ -194,8 +203,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
       mbar_arrive_expect_tx(q_full, Q_BYTES);
-      tma_load_3d(smem + OFF_Q, &tmap_q, q_full, 0, head, start + q0);
-      tma_load_3d(smem + OFF_Q + Q_BYTES / 2, &tmap_q, q_full, 64, head, start + q0);
+#pragma unroll
+      for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(smem + OFF_Q + bx * Q_BOX, &tmap_q, q_full, bx * 64, head, start + q0);
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -203,13 +212,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, 21, j)) break;
         uint8_t* kd = smem + OFF_K + s * KV_BYTES;
         mbar_arrive_expect_tx(&k_full[s], KV_BYTES);
-        tma_load_3d(kd, &tmap_k, &k_full[s], 0, kvh, row);
-        tma_load_3d(kd + KV_BYTES / 2, &tmap_k, &k_full[s], 64, kvh, row);
+#pragma unroll
+        for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
         if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
         uint8_t* vd = smem + OFF_V + s * KV_BYTES;
         mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
-        tma_load_3d(vd, &tmap_v, &v_full[s], 0, kvh, row);
-        tma_load_3d(vd + KV_BYTES / 2, &tmap_v, &v_full[s], 64, kvh, row);
+#pragma unroll
+        for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[s], bx * 64, kvh, row);
       }
     }
   } else if (warp == 1) {
@@ -229,8 +238,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const uint32_t k_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t a_desc = make_smem_desc(q_addr + (ks >> 2) * (Q_BYTES / 2) + (ks & 3) * 32, 16, 1024, 2);
-            const uint64_t b_desc = make_smem_desc(k_addr + (ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32, 16, 1024, 2);
+            const uint64_t a_desc = make_smem_desc(q_addr + (ks >> 2) * Q_BOX + (ks & 3) * 32, 16, 1024, 2);
+            const uint64_t b_desc = make_smem_desc(k_addr + (ks >> 2) * KV_BOX + (ks & 3) * 32, 16, 1024, 2);
             umma_ss_f16(tmem_base + s * BN, a_desc, b_desc, p.idesc_qk, ks != 0 ? 1u : 0u);
           }
           umma_commit(&s_full[s]);
@@ -416,6 +425,20 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
 }
 
+template <typename T, int D>
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                          unsigned grid, cudaStream_t stream) {
+  auto kern = flash_prefill_kernel<T, D>;
+  constexpr int SMEM = fp::Layout<D>::SMEM_BYTES;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) {
+    set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  kern<<<grid, fp::THREADS, SMEM, stream>>>(tq, tk, tv, p);
+  return DLB_OK;
+}
+
 }  // namespace dlb
 
 extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
@@ -429,8 +452,9 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "flash_prefill: dtype %d (need fp16 or bf16)", dtype);
-  DLB_CHECK_ARG(head_dim == D, DLB_ERR_UNSUPPORTED, "flash_prefill: head_dim %lld not supported (128)",
-                (long long)head_dim);
+  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
+                "flash_prefill: head_dim %lld not supported (64 or 128)", (long long)head_dim);
+  const int D = (int)head_dim;
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "flash_prefill: bad head counts");
   DLB_CHECK_ARG(total_tokens >= 0 && max_seq_len >= 0, DLB_ERR_BAD_ARG, "flash_prefill: negative size");
   if (batch == 0 || total_tokens == 0 || max_seq_len == 0) return DLB_OK;
@@ -470,23 +494,20 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   // V tile in shared memory: two 64-wide (128 B) column boxes of BN key rows each.
   // MN-major canonical layout: 64 d contiguous, next 64-d atom at LBO; 8 key rows at
   // 128 B pitch, next group of 8 keys at SBO.
-  p.v_lbo = KV_BYTES / 2;
+  p.v_lbo = KV_BOX;
   p.v_sbo = 1024;
   p.status = status;
 
-  cudaError_t e;
   cudaStream_t s = (cudaStream_t)stream;
+  int rc2;
   if (dtype == DLB_DTYPE_BF16) {
-    auto kern = flash_prefill_kernel<__nv_bfloat16>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) { set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e)); return (int)e; }
-    kern<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(tq, tk, tv, p);
+    rc2 = D == 128 ? launch_prefill<__nv_bfloat16, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__nv_bfloat16, 64>(tq, tk, tv, p, (unsigned)grid, s);
   } else {
-    auto kern = flash_prefill_kernel<__half>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) { set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e)); return (int)e; }
-    kern<<<(unsigned)grid, THREADS, SMEM_BYTES, s>>>(tq, tk, tv, p);
+    rc2 = D == 128 ? launch_prefill<__half, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__half, 64>(tq, tk, tv, p, (unsigned)grid, s);
   }
+  if (rc2 != DLB_OK) return rc2;
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }

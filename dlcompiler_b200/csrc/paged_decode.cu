@@ -198,33 +198,38 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 
   if (warp == CONSUMER_WARPS) {
     // ------------------------------ producer ------------------------------
+    // A tile is 64 keys = 64 / min(page, 64) boxes per K/V half; the boxes are spread over the
+    // lanes of this warp so that small pages (down to one token per page) still issue quickly.
     if (lane == 0) {
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      const int keys_per_box = min(p.page_size, TILE_KEYS);
-      const int boxes_per_tile = TILE_KEYS / keys_per_box;
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % STAGES;
-        const uint32_t ph = (t / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 11, t)) break;
-        uint8_t* kdst = smem + s * STAGE_BYTES;
-        uint8_t* vdst = kdst + KV_BYTES;
-        mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-        const int tok0 = lo + t * TILE_KEYS;
-        for (int bx = 0; bx < boxes_per_tile; ++bx) {
-          const int tok = tok0 + bx * keys_per_box;
-          int page_slot = tok / p.page_size;
-          if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // tail boxes past the table: any valid page
-          int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
-          if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
-          const int slot0 = tok % p.page_size;
+    }
+    const int keys_per_box = min(p.page_size, TILE_KEYS);
+    const int boxes_per_tile = TILE_KEYS / keys_per_box;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % STAGES;
+      const uint32_t ph = (t / STAGES) & 1;
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 11, t) ? 1 : 0;
+        if (ok) mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      uint8_t* kdst = smem + s * STAGE_BYTES;
+      uint8_t* vdst = kdst + KV_BYTES;
+      const int tok0 = lo + t * TILE_KEYS;
+      for (int bx = lane; bx < boxes_per_tile; bx += 32) {
+        const int tok = tok0 + bx * keys_per_box;
+        int page_slot = tok / p.page_size;
+        if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // tail boxes past the table: any valid page
+        int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
+        if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
+        const int slot0 = tok % p.page_size;
 #pragma unroll
-          for (int h = 0; h < BOXES; ++h) {
-            tma_load_4d(kdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_k, &full_bar[s], h * 64, kvh, slot0,
-                        page);
-            tma_load_4d(vdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_v, &full_bar[s], h * 64, kvh, slot0,
-                        page);
-          }
+        for (int h = 0; h < BOXES; ++h) {
+          tma_load_4d(kdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_k, &full_bar[s], h * 64, kvh, slot0, page);
+          tma_load_4d(vdst + h * HALF_BYTES + bx * keys_per_box * 128, &tmap_v, &full_bar[s], h * 64, kvh, slot0, page);
         }
       }
     }
@@ -503,8 +508,8 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
                 "paged_decode: head_dim %lld not supported (64 or 128)", (long long)head_dim);
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "paged_decode: bad head counts");
-  DLB_CHECK_ARG(page_size >= 16 && (page_size & (page_size - 1)) == 0, DLB_ERR_UNSUPPORTED,
-                "paged_decode: page size %lld must be a power of two >= 16", (long long)page_size);
+  DLB_CHECK_ARG(page_size >= 1 && (page_size & (page_size - 1)) == 0, DLB_ERR_UNSUPPORTED,
+                "paged_decode: page size %lld must be a power of two", (long long)page_size);
   DLB_CHECK_ARG(chunk >= 64 && chunk % 64 == 0 && chunk % page_size == 0, DLB_ERR_BAD_ARG,
                 "paged_decode: chunk %lld must be a multiple of 64 and of the page size", (long long)chunk);
   DLB_CHECK_ARG(max_splits >= 1 && max_splits <= 65535, DLB_ERR_BAD_ARG, "paged_decode: max_splits out of range");

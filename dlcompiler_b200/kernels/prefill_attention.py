@@ -30,6 +30,7 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     b_seq_len = b_seq_len.to(torch.int32).contiguous()
     if lse is not None:
         assert lse.dtype == torch.float32 and lse.shape == (head, q.shape[0]) and lse.is_contiguous()
+    assert o.stride(0) % 8 == 0 and o.stride(1) % 8 == 0, "output strides must be multiples of 8 elements"
     lib = _lib.load()
     status = _lib.status_word(dev)
     with torch.cuda.device(dev):

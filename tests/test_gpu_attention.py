@@ -170,3 +170,105 @@ def test_decode_config_sample_and_properties(cuda_device):
         table = torch.arange(npg, dtype=torch.int32).unsqueeze(0)
         ref = oracle.paged_decode_attention(d["q"][b:b + 1], kc, vc, table, ctx[b:b + 1])
         torch.testing.assert_close(out[b:b + 1].float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+# ------------------------------------------------------------------ head size 64 and the dense entry points
+@pytest.mark.parametrize("lens,hq,hkv,dtype", [
+    ([100, 257], 4, 2, torch.bfloat16),
+    ([1024], 8, 8, torch.float16),
+])
+def test_prefill_head_size_64(cuda_device, lens, hq, hkv, dtype):
+    wl = W.PrefillWorkload(seq_lens=lens, hq=hq, hkv=hkv, head_dim=64, dtype=dtype)
+    d = wl.make()
+    out, lse = _run_prefill(cuda_device, d, lse=True)
+    ref, rlse = oracle.context_attention(d["q"], d["k"], d["v"], d["b_start_loc"], d["b_seq_len"], return_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(lse, rlse, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_flash_attention_bhmd(cuda_device, causal):
+    """[B, H, M, D] layout of flash_attention.py:170-211 with grouped heads, LSE of :152-155."""
+    from dlcompiler_b200 import flash_attention_fwd
+
+    g = torch.Generator().manual_seed(21)
+    B, H, Hk, M, D = 2, 4, 2, 300, 128
+    q = torch.randn(B, H, M, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Hk, M, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Hk, M, D, generator=g).to(torch.bfloat16)
+    o, L = flash_attention_fwd(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), causal=causal, sm_scale=0.11)
+    for b in range(B):
+        ref, rl = oracle.context_attention(q[b].transpose(0, 1).contiguous(), k[b].transpose(0, 1).contiguous(),
+                                           v[b].transpose(0, 1).contiguous(), torch.tensor([0]), torch.tensor([M]),
+                                           causal=causal, sm_scale=0.11, return_lse=True)
+        torch.testing.assert_close(o[b].cpu().transpose(0, 1).float(), ref.float(), rtol=RTOL, atol=ATOL)
+        torch.testing.assert_close(L[b].cpu(), rl, rtol=1e-3, atol=1e-3)
+
+
+def test_dense_flash_attention_v2_bshd(cuda_device):
+    """[b, s, h, d] layout, d = 64, non-causal: the reference benchmark's configuration
+    (benchmarks/flash_attention_v2.py:13-30 checks against scaled_dot_product_attention, atol 1e-2)."""
+    import torch.nn.functional as F
+
+    from dlcompiler_b200 import flash_attention_v2
+
+    g = torch.Generator().manual_seed(22)
+    b, s, h, d = 2, 777, 4, 64
+    q, k, v = (torch.rand(b, s, h, d, generator=g).to(torch.float16) for _ in range(3))
+    o = flash_attention_v2(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)).cpu()
+    ref = F.scaled_dot_product_attention(q.transpose(1, 2).float(), k.transpose(1, 2).float(),
+                                         v.transpose(1, 2).float()).transpose(1, 2)
+    torch.testing.assert_close(o.float(), ref, atol=1e-2, rtol=0)
+
+
+# ------------------------------------------------------------------ small pages and token-granular decode
+@pytest.mark.parametrize("page", [1, 2, 4, 8])
+def test_decode_small_pages(cuda_device, page):
+    from dlcompiler_b200 import _lib
+
+    wl = W.DecodeWorkload(batch=3, ctx_lo=5, ctx_hi=400, page=page, hq=8, hkv=2, head_dim=128)
+    d = wl.make()
+    dev = cuda_device
+    q = d["q"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    kc, vc, tb, ln = d["k_cache"].to(dev), d["v_cache"].to(dev), d["block_table"].to(dev), d["kv_seqlens"].to(dev)
+    lib = _lib.load()
+    chunk, splits = 256, (tb.size(1) * page + 255) // 256
+    part = torch.empty(max(lib.dlb_paged_decode_workspace_floats(3, 8, 128, splits), 1), device=dev)
+    rc = lib.dlb_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), tb.data_ptr(), ln.data_ptr(),
+                              part.data_ptr(), 3, 8, 2, 128, page, kc.size(0), tb.size(1), q.stride(0), q.stride(1),
+                              o.stride(0), o.stride(1), kc.stride(0), kc.stride(1), kc.stride(2), vc.stride(0),
+                              vc.stride(1), vc.stride(2), tb.stride(0), 0, 0, chunk, splits, -1, 128 ** -0.5, -1.0,
+                              _lib.DTYPE_BF16, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "paged_decode")
+    ref = oracle.paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["block_table"], d["kv_seqlens"])
+    torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("hq,hkv,cap", [(8, 8, 0.0), (32, 8, 0.0), (16, 2, 20.0)])
+def test_decode_attention_fwd_token_granular(cuda_device, hq, hkv, cap):
+    """decode_attention_fwd (decode_attention.py:559): request -> token table, page size one."""
+    from dlcompiler_b200 import decode_attention_fwd
+
+    g = torch.Generator().manual_seed(hq + hkv)
+    B, D, max_ctx, pool = 5, 128, 700, 4000
+    lens = torch.randint(1, max_ctx + 1, (B,), generator=g)
+    req_to_token = torch.zeros(9, max_ctx, dtype=torch.int32)
+    b_req_idx = torch.tensor([7, 2, 5, 0, 3])
+    perm = torch.randperm(pool, generator=g)
+    off = 0
+    for i in range(B):
+        n = int(lens[i])
+        req_to_token[b_req_idx[i], :n] = perm[off:off + n].to(torch.int32)
+        off += n
+    kb = torch.randn(pool, hkv, D, generator=g).to(torch.bfloat16)
+    vb = torch.randn(pool, hkv, D, generator=g).to(torch.bfloat16)
+    q = torch.randn(B, hq, D, generator=g).to(torch.bfloat16)
+    dev = cuda_device
+    o = torch.full_like(q, float("nan")).to(dev)
+    start = torch.cat([lens.new_zeros(1), lens.cumsum(0)[:-1]])
+    decode_attention_fwd(q.to(dev), kb.to(dev), vb.to(dev), o, req_to_token.to(dev), b_req_idx.to(dev),
+                         start.to(dev), lens.to(dev), None, max_ctx, D ** -0.5, logit_cap=cap)
+    ref = oracle.paged_decode_attention(q, kb.unsqueeze(1), vb.unsqueeze(1), req_to_token[b_req_idx], lens,
+                                        sm_scale=D ** -0.5, logit_softcapping=cap if cap > 0 else None)
+    torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
