@@ -8,6 +8,9 @@ no Triton, no backend dispatch and no CPU fallback on this path.
 from . import _lib
 from ._lib import DlblasError, check_device_status, is_built
 from .kernels.activation import silu_and_mul
+from .kernels.apply_rotary_pos_emb import apply_rotary_pos_emb
+from .kernels.fill_kv_cache import fill_kv_cache
+from .kernels.rms_norm import add_rms_norm, rms_norm
 from .kernels.decode_attention import decode_attention_fwd
 from .kernels.flash_attention import flash_attention_fwd, flash_attention_v2
 from .kernels.fused_moe import fused_moe, fused_moe_kernel_launcher, get_start_end, moe_align_block_size
@@ -18,5 +21,5 @@ from .kernels.prefill_attention import context_attention_fwd
 __all__ = [
     "DlblasError", "check_device_status", "is_built", "silu_and_mul", "fused_moe", "fused_moe_kernel_launcher",
     "get_start_end", "moe_align_block_size", "grouped_topk_gating", "softmax_topk", "paged_attention_fwd",
-    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2",
+    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2", "apply_rotary_pos_emb", "fill_kv_cache", "rms_norm", "add_rms_norm",
 ]

@@ -55,6 +55,12 @@ SIGNATURES = {
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_int,
                                  c_void_p, c_void_p]),
+    "dlb_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                             c_int64, c_float, c_int, c_int, c_void_p]),
+    "dlb_apply_rotary": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
+                                 c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
+                                 c_void_p]),
+    "dlb_fill_kv_cache": (c_int, [c_void_p] * 8 + [c_int64] * 19 + [c_int] * 5 + [c_void_p]),
     "dlb_paged_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                         c_int64, c_int64, c_int64, c_int64,

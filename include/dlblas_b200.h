@@ -153,6 +153,36 @@ int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, vo
                      int64_t max_splits, int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
                      void* stream);
 
+/* rms_norm with optional residual add.  new_x = x + residual in the storage dtype (written to
+ * out_residual when given); out = w * (new_x * rsqrt(mean(new_x^2) + eps)).  weight_after_cast = 0
+ * multiplies in fp32 and rounds once (python/dlBLAS/dlblas/kernels/rms_norm.py:8-132);
+ * weight_after_cast = 1 rounds the normalised value first and multiplies in the storage dtype
+ * (python/dlBLAS/dlblas/kernels/add_rms_norm.py:11-80).  out_residual uses residual_row_stride. */
+int dlb_rms_norm(const void* x, const void* weight, const void* residual, void* out, void* out_residual,
+                 int64_t rows, int64_t n, int64_t x_row_stride, int64_t residual_row_stride, int64_t out_row_stride,
+                 float eps, int weight_after_cast, int dtype, void* stream);
+
+/* Rotary position embedding, rotate-half convention, arithmetic in the tensors' dtype; cos/sin are
+ * [tokens, dim] in that dtype; outputs may alias the inputs.
+ * Replaces python/dlBLAS/dlblas/kernels/apply_rotary_pos_emb.py:8-164. */
+int dlb_apply_rotary(const void* q, const void* k, const void* cos, const void* sin, void* q_out, void* k_out,
+                     int64_t tokens, int hq, int hk, int dim, int64_t q_stride_t, int64_t q_stride_h,
+                     int64_t k_stride_t, int64_t k_stride_h, int64_t qo_stride_t, int64_t qo_stride_h,
+                     int64_t ko_stride_t, int64_t ko_stride_h, int dtype, void* stream);
+
+/* Scatter the new tokens' key/value states into the paged caches [pages, page_size, heads, d]:
+ * token i of sequence b lands in slot (history + i) % page_size of page
+ * block_offsets[b, (history + i) / page_size], history = kv_seq_length[b] - q_seq_length[b].
+ * Bit-exact copy.  Replaces python/dlBLAS/dlblas/kernels/fill_kv_cache.py:24-185. */
+int dlb_fill_kv_cache(const void* k_states, const void* v_states, void* k_caches, void* v_caches,
+                      const void* q_start_loc, const void* q_seq_length, const void* kv_seq_length,
+                      const void* block_offsets, int64_t batch, int64_t max_q_seq_length, int64_t page_size,
+                      int64_t heads, int64_t dim_k, int64_t dim_v, int64_t num_pages, int64_t max_pages,
+                      int64_t ks_stride_t, int64_t ks_stride_h, int64_t vs_stride_t, int64_t vs_stride_h,
+                      int64_t kc_stride_page, int64_t kc_stride_slot, int64_t kc_stride_head, int64_t vc_stride_page,
+                      int64_t vc_stride_slot, int64_t vc_stride_head, int64_t table_stride, int start_is_int64,
+                      int qlen_is_int64, int kvlen_is_int64, int table_is_int64, int elem_size, void* stream);
+
 /* Capacity, in fp32 elements (32 MiB), of the fixed device array used by dlb_paged_decode_static. */
 #define DLB_DECODE_STATIC_FLOATS (8ll * 1024 * 1024)
 

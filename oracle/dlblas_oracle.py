@@ -357,3 +357,60 @@ def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_sc
         p = torch.softmax(sc, dim=-1, dtype=torch.float32).to(vf.dtype)
         out[b] = torch.matmul(p.float(), vf.float()).squeeze(1).to(q.dtype)
     return out
+
+
+# --------------------------------------------------------------------------------------
+# rms_norm, rotary embedding, fill_kv_cache (the steps next to the hot path)
+# --------------------------------------------------------------------------------------
+def rms_norm_test_gt(x, weight, eps):
+    """Test ground truth, python/dlBLAS/tests/kernels/test_rms_norm.py:26-31: normalise in fp32, cast,
+    then multiply by the weight in the storage dtype."""
+    xf = x.to(torch.float32)
+    variance = xf.pow(2).mean(-1, keepdim=True)
+    xf = xf * torch.rsqrt(variance + eps)
+    return weight * xf.to(x.dtype)
+
+
+def rms_norm(x, weight, eps=1e-6, residual=None, weight_after_cast=False):
+    """Kernel-faithful form.  new_x = x + residual in the storage dtype
+    (python/dlBLAS/dlblas/kernels/rms_norm.py:68-70); weight_after_cast=False multiplies by the weight in
+    fp32 and rounds once (rms_norm.py:8-16), True rounds first and multiplies in the storage dtype
+    (python/dlBLAS/dlblas/kernels/add_rms_norm.py:33-38).  Returns (out, new_x)."""
+    new_x = x + residual if residual is not None else x
+    xf = new_x.to(torch.float32)
+    var = (xf * xf).sum(-1, keepdim=True) * (1.0 / x.size(-1))
+    normed = xf * torch.rsqrt(var + eps)
+    if weight_after_cast:
+        out = normed.to(x.dtype) * weight
+    else:
+        out = (weight.to(torch.float32) * normed).to(x.dtype)
+    return out, new_x
+
+
+def _rotate_half(x):
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def apply_rotary_pos_emb(q, k, cos, sin):
+    """Test ground truth, python/dlBLAS/tests/kernels/test_apply_rotary.py:80-86:
+    x * cos + rotate_half(x) * sin in the tensors' dtype (cos/sin broadcast over heads)."""
+    cos = cos.reshape(q.size(0), 1, -1).to(q.dtype)
+    sin = sin.reshape(q.size(0), 1, -1).to(q.dtype)
+    return q * cos + _rotate_half(q) * sin, k * cos + _rotate_half(k) * sin
+
+
+def fill_kv_cache(k_states, v_states, k_caches, v_caches, seq_lens, history_lens, block_offsets):
+    """Test ground truth, python/dlBLAS/tests/kernels/test_fill_kv_cache.py:97-137: new token i of
+    sequence b goes to slot (history + i) % page of page block_offsets[b, (history + i) // page]."""
+    page = k_caches.size(1)
+    kc, vc = k_caches.clone(), v_caches.clone()
+    start = 0
+    for b, (n, h) in enumerate(zip(seq_lens, history_lens)):
+        for i in range(n):
+            pos = h + i
+            pg = int(block_offsets[b, pos // page])
+            kc[pg, pos % page] = k_states[start + i]
+            vc[pg, pos % page] = v_states[start + i]
+        start += n
+    return kc, vc

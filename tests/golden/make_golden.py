@@ -165,6 +165,68 @@ def main():
         cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
                       "block_offsets": table, "kv_seqlens": full, "gt": fns["_conti_input"](gt, seq_lens)})
     torch.save(cases, os.path.join(HERE, "paged_decode.pt"))
+    # ---------------------------------------------------------------- rms_norm / add_rms_norm
+    fns = load_functions(os.path.join(tests, "test_rms_norm.py"), ["TestRMSNorm.gt"])
+    rms_gt = fns["TestRMSNorm.gt"]           # a fixture that `return`s its value
+    fuse = load_functions(os.path.join(tests, "test_add_rms_norm.py"), ["FuseRMSNorm.forward"])["FuseRMSNorm.forward"]
+
+    class _Holder:                           # the attributes FuseRMSNorm.forward reads from `self`
+        def __init__(self, w, eps):
+            self.weight, self.variance_epsilon = w, eps
+
+    cases = []
+    for i, (rows, n, dtype) in enumerate([(4, 8, torch.float16), (4, 8, torch.float32), (16, 4096, torch.bfloat16),
+                                          (8, 1000, torch.float16)]):
+        g = torch.Generator().manual_seed(4000 + i)
+        x = torch.rand(rows, n, generator=g).to(dtype)
+        w = torch.rand(n, generator=g).to(dtype)
+        res = torch.randn(rows, n, generator=g).to(dtype)
+        fused_out, fused_res = fuse(_Holder(w, 1e-6), x.clone(), res.clone())
+        cases.append({"x": x, "w": w, "res": res, "eps": 1e-6, "gt_rms": rms_gt(None, x, w, 1e-6),
+                      "gt_add_out": fused_out, "gt_add_res": fused_res})
+    torch.save(cases, os.path.join(HERE, "rms_norm.pt"))
+
+    # ---------------------------------------------------------------- rotary
+    fns = load_functions(os.path.join(tests, "test_apply_rotary.py"), ["_rotate_half", "TestApplyRotary.gt"])
+    cases = []
+    for i, (hq, hk, dim, dtype) in enumerate([(8, 8, 16, torch.bfloat16), (8, 4, 16, torch.float16),
+                                              (8, 4, 16, torch.float32), (4, 2, 128, torch.bfloat16)]):
+        g = torch.Generator().manual_seed(5000 + i)
+        tokens, max_len = 45, 16
+        q = torch.rand(tokens, hq, dim, generator=g).to(dtype)
+        k = torch.rand(tokens, hk, dim, generator=g).to(dtype)
+        pos = torch.randint(0, max_len, (tokens,), generator=g)
+        cos = torch.rand(max_len, dim, generator=g).to(dtype)[pos, None, :]
+        sin = torch.rand(max_len, dim, generator=g).to(dtype)[pos, None, :]
+        gq, gk = _fixture_value(fns["TestApplyRotary.gt"], q, k, cos, sin, pos)
+        cases.append({"q": q, "k": k, "cos": cos, "sin": sin, "gt_q": gq, "gt_k": gk})
+    torch.save(cases, os.path.join(HERE, "rotary.pt"))
+
+    # ---------------------------------------------------------------- fill_kv_cache
+    fns = load_functions(os.path.join(tests, "test_fill_kv_cache.py"), ["_div_up", "TestFillKVCache.gt"])
+    cases = []
+    for i, (seq_lens, hist) in enumerate([((1, 1, 1, 1), (1, 16, 31, 24)), ((1, 8, 16, 24), (1, 16, 31, 24)),
+                                          ((70, 3), (60, 200))]):
+        g = torch.Generator().manual_seed(6000 + i)
+        heads, d, page = (8, 128, 64) if i == 0 else (2, 64, 64)
+        kv_lens = [s + h for s, h in zip(seq_lens, hist)]
+        nblk = [(n + page - 1) // page for n in kv_lens]
+        B, mx = len(seq_lens), max(nblk)
+        ks = torch.rand(sum(seq_lens), heads, d, generator=g).to(torch.bfloat16)
+        vs = torch.rand(sum(seq_lens), heads, d, generator=g).to(torch.bfloat16)
+        kc = torch.zeros(B * mx, page, heads, d, dtype=torch.bfloat16)
+        vc = torch.rand(B * mx, page, heads, d, generator=g).to(torch.bfloat16)
+        table = torch.zeros(B, mx, dtype=torch.int64)
+        perm = torch.randperm(B * mx, generator=g)
+        off = 0
+        for b in range(B):
+            table[b, :nblk[b]] = perm[off:off + nblk[b]]
+            off += nblk[b]
+        gk, gv = _fixture_value(fns["TestFillKVCache.gt"], ks, vs, kc, vc, list(seq_lens), list(hist), table, page)
+        cases.append({"k_states": ks, "v_states": vs, "k_caches": kc, "v_caches": vc, "seq_lens": list(seq_lens),
+                      "history_lens": list(hist), "block_offsets": table, "gt_k": gk, "gt_v": gv})
+    torch.save(cases, os.path.join(HERE, "fill_kv_cache.pt"))
+
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".pt"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -70,3 +70,29 @@ def test_paged_decode_ground_truth(golden_dir):
         # reference test tolerance for fp16: atol=1e-3, rtol=1e-5 (test_paged_attention.py:286)
         tol = 1e-3 if out.dtype == torch.float16 else 8e-3
         torch.testing.assert_close(out, c["gt"], atol=tol, rtol=1e-5)
+
+
+def test_rms_norm_ground_truths(golden_dir):
+    for c in _load(golden_dir, "rms_norm.pt"):
+        x, w, res, eps = c["x"], c["w"], c["res"], c["eps"]
+        assert torch.equal(oracle.rms_norm_test_gt(x, w, eps), c["gt_rms"])
+        # the registry op's convention (cast, then weight) is exactly the fused module of test_add_rms_norm.py
+        out, new_x = oracle.rms_norm(x, w, eps, residual=res, weight_after_cast=True)
+        assert torch.equal(new_x, c["gt_add_res"])
+        torch.testing.assert_close(out, c["gt_add_out"], rtol=2 * torch.finfo(x.dtype).eps, atol=1e-6)
+        # the rms_norm.py kernel convention (weight in fp32, one rounding) differs by at most one rounding
+        out2, _ = oracle.rms_norm(x, w, eps)
+        torch.testing.assert_close(out2, c["gt_rms"], rtol=2 * torch.finfo(x.dtype).eps, atol=1e-6)
+
+
+def test_rotary_ground_truth(golden_dir):
+    for c in _load(golden_dir, "rotary.pt"):
+        q, k = oracle.apply_rotary_pos_emb(c["q"], c["k"], c["cos"], c["sin"])
+        assert torch.equal(q, c["gt_q"]) and torch.equal(k, c["gt_k"])
+
+
+def test_fill_kv_cache_ground_truth(golden_dir):
+    for c in _load(golden_dir, "fill_kv_cache.pt"):
+        kc, vc = oracle.fill_kv_cache(c["k_states"], c["v_states"], c["k_caches"], c["v_caches"], c["seq_lens"],
+                                      c["history_lens"], c["block_offsets"])
+        assert torch.equal(kc, c["gt_k"]) and torch.equal(vc, c["gt_v"])
