@@ -223,6 +223,70 @@ def bench_decode(dev, peaks, steps, warmup):
             "l2": "KV cache 4.4 GB > L2", "gpu_launches": 2 * steps}
 
 
+def _hbm_entry(workload, nbytes, ms, peaks, launches, note):
+    gbs = nbytes / ms / 1e6
+    return {"workload": workload, "ms": ms, "value": gbs, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "basis": peaks["basis"]},
+            "l2": note, "gpu_launches": launches}
+
+
+def bench_neighbours(dev, peaks, steps, warmup):
+    """The steps either side of the hot path (rms_norm, rotary, fill_kv_cache, token-granular decode)."""
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    # rms_norm with residual: 4 tensors of [16384, 4096] bf16 move per pass
+    T, H = 16384, 4096
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    r = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    w = torch.rand(H, generator=g, device=dev).to(torch.bfloat16)
+    o, o_r = torch.empty_like(x), torch.empty_like(x)
+    ms = time_steps(lambda: dl.rms_norm(x, w, 1e-6, residual=r, out=o, out_residual=o_r), steps, warmup)
+    out["rms_norm"] = _hbm_entry("rms_norm + residual bf16 [16384, 4096]", 4 * T * H * 2 + H * 2, ms, peaks, steps,
+                                 "537 MB per pass > L2")
+    del x, r, o, o_r
+    # rotary embedding in place on the prefill configuration's q and k
+    tok, hq, hk, d = 32768, 32, 8, 128
+    q = torch.randn(tok, hq, d, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(tok, hk, d, generator=g, device=dev).to(torch.bfloat16)
+    cos = torch.rand(tok, d, generator=g, device=dev).to(torch.bfloat16)
+    sin = torch.rand(tok, d, generator=g, device=dev).to(torch.bfloat16)
+    ms = time_steps(lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k), steps, warmup)
+    out["apply_rotary_pos_emb"] = _hbm_entry("rotary in place, q [32768, 32, 128] k [32768, 8, 128] bf16",
+                                             2 * (q.numel() + k.numel()) * 2 + 2 * cos.numel() * 2, ms, peaks, steps,
+                                             "688 MB per pass > L2")
+    # fill_kv_cache: the prefill configuration's 4 x 8192 new tokens into 64-token pages
+    B, S, page = 4, 8192, 64
+    pages = B * S // page
+    kc = torch.empty(pages, page, hk, d, dtype=torch.bfloat16, device=dev)
+    vc = torch.empty_like(kc)
+    table = torch.randperm(pages, generator=g, device=dev).to(torch.int32).view(B, S // page)
+    qlen = torch.full((B,), S, dtype=torch.int32, device=dev)
+    start = torch.arange(B, dtype=torch.int32, device=dev) * S
+    v_states = torch.randn(tok, hk, d, generator=g, device=dev).to(torch.bfloat16)
+    ms = time_steps(lambda: dl.fill_kv_cache(k, v_states, kc, vc, start, qlen, qlen, S, table), steps, warmup)
+    out["fill_kv_cache"] = _hbm_entry("fill_kv_cache 4 x 8192 tokens, 8 heads x 128, page 64, bf16",
+                                      4 * k.numel() * 2, ms, peaks, steps, "268 MB per pass > L2")
+    del q, k, v_states, kc, vc, cos, sin
+    # token-granular decode (page size 1): 16 requests of the decode configuration
+    wl = W.DecodeWorkload(batch=16, page=1)
+    dd = wl.make(device=dev)
+    qd = dd["q"].to(dev)
+    od = torch.empty_like(qd)
+    tb, ln = dd["block_table"].to(dev), dd["kv_seqlens"].to(dev)
+    kb, vb = dd["k_cache"].squeeze(1), dd["v_cache"].squeeze(1)
+    req = torch.arange(wl.batch, device=dev)
+    ms = time_steps(lambda: dl.decode_attention_fwd(qd, kb, vb, od, tb, req, None, ln, None, tb.size(1), d ** -0.5),
+                    steps, warmup)
+    out["decode_attention_fwd"] = _hbm_entry(f"decode_attention_fwd (page size 1) B=16 ctx_sum={int(ln.sum())} bf16",
+                                             wl.bytes(dd["kv_seqlens"]), ms, peaks, 2 * steps, "KV 1.1 GB > L2")
+    return out
+
+
 # --------------------------------------------------------------------------- CPU baseline
 def cpu_fused_moe(sample_tokens, threads=None, budget_s=12.0, max_passes=6):
     """Times the CPU checker's fused_moe (reference test ground truth) on a token sample of C3:
@@ -451,6 +515,9 @@ def run_ours(args):
                 ops[name] = fn(dev, peaks, max(args.steps, 10), max(args.warmup, 3))
             dl.check_device_status()
             line["ops"] = ops
+            torch.cuda.empty_cache()
+            line["ops_next"] = bench_neighbours(dev, peaks, max(args.steps, 10), max(args.warmup, 3))
+            dl.check_device_status()
         if args.cpu_baseline:
             del w1, w2
             torch.cuda.empty_cache()

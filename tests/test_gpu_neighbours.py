@@ -11,6 +11,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _ulp(out, ref, n=2):
+    if out.numel() == 0:
+        assert out.shape == ref.shape
+        return
     eps = torch.finfo(out.dtype).eps
     torch.testing.assert_close(out.float(), ref.float(), rtol=n * eps, atol=n * eps * max(1.0, ref.abs().max().item()))
 
