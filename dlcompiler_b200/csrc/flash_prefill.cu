@@ -39,6 +39,10 @@ constexpr int P_BYTES = BM * BN * 2;           // 16 KiB
 constexpr int KV_STAGES = 2;
 constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
+// Bit g set: group g (of every 8 groups of four scores) computes 2^x with the polynomial instead of the
+// SFU.  Measured on B200: the softmax warps are issue-bound, not SFU-bound, so 0 (all SFU) is fastest
+// (0x52 = 37.5 % polynomial was 10 % slower on the 4 x 8192 benchmark).
+constexpr unsigned POLY_EXP2_GROUPS = 0x00;
 // shared-memory layout for head size D (64 or 128)
 template <int D> struct Layout {
   static constexpr int BOXES = D / 64;
@@ -109,6 +113,32 @@ __device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
+}
+
+// 2^x for two scores at once on the FMA/ALU pipes (no SFU): round-to-nearest split x = n + f
+// with the 1.5 * 2^23 trick, degree-3 polynomial for 2^f on [-0.5, 0.5] (max relative error
+// 7.5e-5, far below the 16-bit rounding of P), exponent added as an integer.  The softmax loop
+// sends a fixed share of its exponentials here so that the SFU, which can retire only 16
+// exponentials per clock per SM, stops being the longest pipe.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& e0, float& e1) {
+  float xa, xb;
+  unpack_f2(x2, xa, xb);
+  xa = fmaxf(xa, -126.f);
+  xb = fmaxf(xb, -126.f);
+  const uint64_t x = pack_f2(xa, xb);
+  const uint64_t magic = pack_f2(12582912.f, 12582912.f);
+  const uint64_t t = add_f2(x, magic);                                   // low mantissa bits = round(x)
+  const uint64_t r = add_f2(t, pack_f2(-12582912.f, -12582912.f));       // round(x) as a float
+  const uint64_t f = fma_f2(r, pack_f2(-1.f, -1.f), x);                  // x - round(x)
+  uint64_t p = fma_f2(pack_f2(0.05517083778977394f, 0.05517083778977394f), f,
+                      pack_f2(0.24260935187339783f, 0.24260935187339783f));
+  p = fma_f2(p, f, pack_f2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma_f2(p, f, pack_f2(0.9999281764030457f, 0.9999281764030457f));
+  float pa, pb, ta, tb;
+  unpack_f2(p, pa, pb);
+  unpack_f2(t, ta, tb);
+  e0 = __int_as_float(__float_as_int(pa) + (__float_as_int(ta) << 23));
+  e1 = __int_as_float(__float_as_int(pb) + (__float_as_int(tb) << 23));
 }
 
 struct PrefillParams {
@@ -305,12 +335,17 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
       // row max of the raw scores (3-input max), scaled once: scale > 0 keeps the order
-      float mx = -CUDART_INF_F;
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // 4 independent chains
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) mx = max3(mx, __uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1]));
+        for (int c = 0; c < 32; c += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = max3(mx4[u], __uint_as_float(sr[h][c + 2 * u]), __uint_as_float(sr[h][c + 2 * u + 1]));
+        }
       }
+      float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]);
       mx *= p.scale_log2;
       // lazy rescale decision
       float alpha = 1.f;
@@ -333,11 +368,25 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
-          float x0, x1, x2, x3;
-          unpack_f2(fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2), x0, x1);
-          unpack_f2(fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2), x2,
-                    x3);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1), e2 = fast_exp2(x2), e3 = fast_exp2(x3);
+          const uint64_t a01 =
+              fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2);
+          const uint64_t a23 =
+              fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2);
+          float e0, e1, e2, e3;
+          // groups of four scores selected by POLY_EXP2_GROUPS take the polynomial path, the rest the SFU
+          const int grp = ((h * 32 + c) >> 2) & 7;
+          if (((POLY_EXP2_GROUPS >> grp) & 1) != 0) {
+            exp2_poly2(a01, e0, e1);
+            exp2_poly2(a23, e2, e3);
+          } else {
+            float x0, x1, x2, x3;
+            unpack_f2(a01, x0, x1);
+            unpack_f2(a23, x2, x3);
+            e0 = fast_exp2(x0);
+            e1 = fast_exp2(x1);
+            e2 = fast_exp2(x2);
+            e3 = fast_exp2(x3);
+          }
           sum2a = add_f2(sum2a, pack_f2(e0, e1));
           sum2b = add_f2(sum2b, pack_f2(e2, e3));
           typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);

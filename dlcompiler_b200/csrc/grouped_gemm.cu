@@ -36,6 +36,10 @@ constexpr int BK = 64;            // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_N = 256;
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
+// k-blocks an explicit L2 prefetch of the weight tiles runs ahead of the ring's loads.  Measured on
+// B200 at the benchmark shape: 6 made the step 18 % SLOWER (the 8 CTAs that share a weight tile all
+// prefetch it, and the extra TMA traffic competes with the loads), so it is off.
+constexpr int PREFETCH_DISTANCE = 0;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_BYTES = UMMA_N * BK * 2;    // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -166,29 +170,65 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // Two walkers over the same (tile, k-block) sequence: `ld` feeds the shared-memory ring, `pf`
+    // runs PREFETCH_DISTANCE k-blocks ahead and only pulls the weight tiles into L2, so that the
+    // ring's loads find them there instead of paying the HBM round trip.
     if (lane == 0) {
-      TileCursor cur;
+      struct Walker {
+        TileCursor cur;
+        int tile, kb, m_blk, n_blk;
+        bool valid;
+      };
+      auto start_walker = [&](Walker& w) {
+        w.tile = blockIdx.x;
+        w.kb = 0;
+        w.valid = w.tile < total_tiles;
+        if (w.valid) w.cur.locate(bs, p.num_experts, n_tiles, w.tile, w.m_blk, w.n_blk);
+      };
+      auto advance = [&](Walker& w) {
+        if (++w.kb == k_blocks) {
+          w.kb = 0;
+          w.tile += gridDim.x;
+          w.valid = w.tile < total_tiles;
+          if (w.valid) w.cur.locate(bs, p.num_experts, n_tiles, w.tile, w.m_blk, w.n_blk);
+        }
+      };
+      auto prefetch_b = [&](const Walker& w) {
+        const int b_row = w.cur.e * p.rows_per_expert + w.n_blk * BN_OUT;
+        tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row);
+        if constexpr (kSilu) tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row + p.up_row_offset);
+      };
+      Walker ld, pf;
+      start_walker(ld);
+      start_walker(pf);
+      for (int i = 0; i < PREFETCH_DISTANCE && pf.valid; ++i) {
+        prefetch_b(pf);
+        advance(pf);
+      }
       uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        int m_blk, n_blk;
-        cur.locate(bs, p.num_experts, n_tiles, tile, m_blk, n_blk);
-        const int b_row = cur.e * p.rows_per_expert + n_blk * BN_OUT;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 1, tile)) { ok = false; break; }
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          uint8_t* b_dst = a_dst + A_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, &full_bar[s], kb * BK, m_blk * BM);
-          if constexpr (kSilu) {
-            tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * BK, b_row);
-            tma_load_2d(b_dst + B_BYTES / 2, &tmap_b, &full_bar[s], kb * BK, b_row + p.up_row_offset);
-          } else {
-            tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * BK, b_row);
+      while (ld.valid) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 1, ld.tile)) break;
+        uint8_t* a_dst = smem + s * STAGE_BYTES;
+        uint8_t* b_dst = a_dst + A_BYTES;
+        const int b_row = ld.cur.e * p.rows_per_expert + ld.n_blk * BN_OUT;
+        mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(a_dst, &tmap_a, &full_bar[s], ld.kb * BK, ld.m_blk * BM);
+        if constexpr (kSilu) {
+          tma_load_2d(b_dst, &tmap_b, &full_bar[s], ld.kb * BK, b_row);
+          tma_load_2d(b_dst + B_BYTES / 2, &tmap_b, &full_bar[s], ld.kb * BK, b_row + p.up_row_offset);
+        } else {
+          tma_load_2d(b_dst, &tmap_b, &full_bar[s], ld.kb * BK, b_row);
+        }
+        if constexpr (PREFETCH_DISTANCE > 0) {
+          if (pf.valid) {
+            prefetch_b(pf);
+            advance(pf);
           }
         }
+        advance(ld);
+        ++it;
       }
     }
   } else if (warp == 1) {
