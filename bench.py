@@ -109,10 +109,17 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- helpers
-def time_steps(fn, steps, warmup, barrier=None):
-    """W untimed steps, then K steps between CUDA events on the current stream; returns ms per step."""
-    for _ in range(warmup):
+def time_steps(fn, steps, warmup, barrier=None, min_warm_s=0.0):
+    """W untimed steps (repeated until at least `min_warm_s` seconds of load have passed, so that the
+    clock sampler sees the device under load), then K steps between CUDA events on the current stream;
+    returns ms per step."""
+    t0 = time.perf_counter()
+    done = 0
+    while done < warmup or time.perf_counter() - t0 < min_warm_s:
         fn()
+        done += 1
+        if done % 8 == 0:
+            torch.cuda.synchronize()
     torch.cuda.synchronize()
     if barrier is not None:
         barrier()
@@ -372,6 +379,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist_mod
 
+        os.environ["NCCL_DEBUG"] = os.environ.get("DLB_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
@@ -396,7 +404,7 @@ def run_ours(args):
 
         launches_per_step = 5
         with ClockSampler(local_rank) as clk:
-            ms = time_steps(step, args.steps, args.warmup)
+            ms = time_steps(step, args.steps, args.warmup, min_warm_s=0.3)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]
         gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
@@ -454,7 +462,8 @@ def run_ours(args):
 
         launches_per_step = launches
         with ClockSampler(local_rank) as clk:
-            ms = time_steps(step, args.steps, args.warmup, barrier)
+            # every rank must run the same number of steps (they meet in cross-GPU barriers): fixed count
+            ms = time_steps(step, args.steps, max(args.warmup, 200), barrier)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]
         gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
