@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libdlblas_b200.so")
 
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
-GEMM_FUSE_SILU, GEMM_WEIGHT, GEMM_SCATTER = 1, 2, 4
+GEMM_FUSE_SILU, GEMM_WEIGHT, GEMM_SCATTER, GEMM_PEER = 1, 2, 4, 8
 
 _DTYPES = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: DTYPE_F32}
 
@@ -34,14 +34,17 @@ SIGNATURES = {
     "dlb_moe_grouped_gemm": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
                                      c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                      c_int, c_void_p, c_void_p]),
-    "dlb_moe_grouped_gemm_peer": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
-                                          c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                                          c_int64, c_int, c_void_p, c_void_p]),
-    "dlb_ep_plan": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                            c_int, c_int64, c_int, c_void_p, c_void_p]),
-    "dlb_ep_dispatch": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int64,
-                                c_void_p]),
+    "dlb_moe_grouped_gemm_sync": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                          c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_void_p, c_void_p]),
+    "dlb_ep_route": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "dlb_ep_send": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int64,
+                            c_int, c_void_p]),
+    "dlb_ep_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_int, c_int,
+                               c_void_p, c_void_p]),
     "dlb_ep_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -2,12 +2,13 @@
 //
 // The reference has no collective code at all; its expert-parallel hook leaves
 // tokens replicated (python/dlBLAS/dlblas/kernels/fused_moe.py:113-114, 329-332).
-// Here tokens are sharded: every rank sorts its (token, k) slots by expert, the
-// ranks exchange their per-expert counts, and each rank then stores its rows
-// DIRECTLY into the destination rank's receive buffer with plain peer stores,
-// already in the expert-major, 128-row-block-padded layout the grouped GEMM
-// consumes.  No host round trip, no staging copy, no library collective: the
-// whole step is a fixed sequence of kernel launches.
+// Here tokens are sharded: every rank counts its (token, k) slots per expert, the
+// ranks exchange the counts through peer stores, and each rank then stores its
+// rows DIRECTLY into the destination rank's receive buffer, already in the
+// expert-major, 128-row-block-padded layout the grouped GEMM consumes.  The
+// grouped GEMMs wait on / raise the cross-GPU flags themselves, so a step is five
+// launches (route, send, GEMM, GEMM, combine) with no host round trip, no staging
+// copy and no library collective.
 //
 // Buffers with the suffix _sym are symmetric: every rank owns one of the same
 // size and holds the device pointers of all peers' copies.
@@ -74,56 +75,80 @@ __device__ __forceinline__ bool cross_gpu_barrier(const PeerPtrs& flags, int slo
   return ok;
 }
 
-struct EpPlanParams {
-  const int32_t* expert_prefix;   // [E + 1] prefix of this rank's per-expert slot counts (moe_align, block 1)
-  PeerPtrs counts;                // counts_sym of every rank
-  PeerPtrs flags;                 // flags_sym of every rank
-  int32_t* dest_base;             // [E] out: first row, in the owner's rows_sym, of this rank's slots of expert e
-  int32_t* block_start;           // [E/G + 1] out: first 128-row block of each LOCAL expert
-  int32_t* num_post_padded;       // [1] out
-  int32_t* row_map;               // [cap] out: p if row p holds a token, cap otherwise
-  int rank, world, experts, cap, epoch;
+__global__ void __launch_bounds__(32) ep_barrier_kernel(const PeerPtrs flags, int slot, int rank, int world,
+                                                        int epoch, int* status) {
+  cross_gpu_barrier(flags, slot, rank, world, epoch, status, 42 + slot);
+}
+
+// ----------------------------------------------------------------------------
+// Fused routing step: histogram + count exchange + receive layout + per-slot destination rows.
+// One CTA.  Replaces (moe_align with block 1) + ep_plan: the stable rank of every slot inside its
+// expert is turned directly into the row it will occupy in the owner's receive buffer.
+// ----------------------------------------------------------------------------
+struct EpRouteParams {
+  const void* topk_ids;           // [numel] GLOBAL expert ids
+  PeerPtrs counts, flags;
+  int32_t* dest_pos;              // [numel] out: row in the owner's rows_sym (-1: id out of range)
+  int32_t* block_start;           // [E/G + 1]
+  int32_t* num_post_padded;       // [1]
+  int32_t* row_map;               // [cap]
+  int numel, ids_are_int64, rank, world, experts, cap, epoch;
   int* status;
 };
 
-__global__ void __launch_bounds__(ep::PLAN_THREADS) ep_plan_kernel(const EpPlanParams p) {
-  __shared__ int tot[ep::MAX_EXPERTS];      // rows of expert e over all ranks
-  __shared__ int before[ep::MAX_EXPERTS];   // rows of expert e from ranks below mine
-  __shared__ int lstart[ep::MAX_EXPERTS];   // local experts: first row / row count
-  __shared__ int lcount[ep::MAX_EXPERTS];
-  __shared__ int n_post;
-  const int t = threadIdx.x;
-  const int epr = p.experts / p.world;
+__device__ __forceinline__ int load_id(const void* ids, int i, int is64) {
+  return is64 ? (int)reinterpret_cast<const int64_t*>(ids)[i] : reinterpret_cast<const int32_t*>(ids)[i];
+}
 
-  // 1. publish my counts into every rank's matrix (peer stores)
-  for (int e = t; e < p.experts; e += ep::PLAN_THREADS) {
-    const int c = p.expert_prefix[e + 1] - p.expert_prefix[e];
-    for (int r = 0; r < p.world; ++r) reinterpret_cast<int32_t*>(p.counts.p[r])[p.rank * p.experts + e] = c;
+__global__ void __launch_bounds__(ep::PLAN_THREADS) ep_route_kernel(const EpRouteParams p) {
+  extern __shared__ int32_t sm[];
+  const int E = p.experts;
+  int32_t* counts = sm;                 // [E] my slots per expert
+  int32_t* tot = counts + E;            // [E] rows per expert over all ranks
+  int32_t* base = tot + E;              // [E] first destination row of my slots of expert e
+  int32_t* running = base + E;          // [E] my slots of expert e placed so far
+  int32_t* lstart = running + E;        // [E] local experts: first row
+  int32_t* lcount = lstart + E;         // [E] local experts: rows
+  int32_t* warp_cnt = lcount + E;       // [32][E]
+  __shared__ int n_post;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int epr = E / p.world;
+  constexpr int NW = ep::PLAN_THREADS / 32;
+
+  for (int e = t; e < E; e += ep::PLAN_THREADS) {
+    counts[e] = 0;
+    running[e] = 0;
   }
+  __syncthreads();
+  for (int i = t; i < p.numel; i += ep::PLAN_THREADS) {
+    const int e = load_id(p.topk_ids, i, p.ids_are_int64);
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  for (int e = t; e < E; e += ep::PLAN_THREADS)
+    for (int r = 0; r < p.world; ++r) reinterpret_cast<int32_t*>(p.counts.p[r])[p.rank * E + e] = counts[e];
   __threadfence_system();
   __syncthreads();
-  // 2. barrier: after it my own matrix is complete
   cross_gpu_barrier(p.flags, 0, p.rank, p.world, p.epoch, p.status, 41);
   __syncthreads();
   const volatile int32_t* cm = reinterpret_cast<const volatile int32_t*>(p.counts.p[p.rank]);
-  for (int e = t; e < p.experts; e += ep::PLAN_THREADS) {
+  for (int e = t; e < E; e += ep::PLAN_THREADS) {
     int sum = 0, bef = 0;
     for (int s = 0; s < p.world; ++s) {
-      const int c = cm[s * p.experts + e];
+      const int c = cm[s * E + e];
       if (s < p.rank) bef += c;
       sum += c;
     }
     tot[e] = sum;
-    before[e] = bef;
+    base[e] = bef;                      // completed with the padded expert offset below
   }
   __syncthreads();
-  // 3. padded layouts of every rank's receive buffer (serial over experts, E <= 1024)
   if (t == 0) {
     for (int r = 0; r < p.world; ++r) {
       int acc = 0;
       for (int el = 0; el < epr; ++el) {
         const int e = r * epr + el;
-        p.dest_base[e] = acc + before[e];
+        base[e] += acc;
         if (r == p.rank) {
           lstart[el] = acc;
           lcount[el] = tot[e];
@@ -140,7 +165,6 @@ __global__ void __launch_bounds__(ep::PLAN_THREADS) ep_plan_kernel(const EpPlanP
     }
   }
   __syncthreads();
-  // 4. which rows of my receive buffer will hold tokens
   for (int row = t; row < p.cap; row += ep::PLAN_THREADS) {
     int v = p.cap;
     if (row < n_post) {
@@ -150,31 +174,53 @@ __global__ void __launch_bounds__(ep::PLAN_THREADS) ep_plan_kernel(const EpPlanP
     }
     p.row_map[row] = v;
   }
+  // stable placement: slots in index order, PLAN_THREADS per round
+  for (int first = 0; first < p.numel; first += ep::PLAN_THREADS) {
+    for (int i = t; i < NW * E; i += ep::PLAN_THREADS) warp_cnt[i] = 0;
+    __syncthreads();
+    const int slot = first + t;
+    int e = -1;
+    if (slot < p.numel) {
+      const int v = load_id(p.topk_ids, slot, p.ids_are_int64);
+      if (v >= 0 && v < E) e = v;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_cnt[warp * E + e] = __popc(peers);
+    __syncthreads();
+    for (int x = t; x < E; x += ep::PLAN_THREADS) {
+      int acc = running[x];
+      for (int w = 0; w < NW; ++w) {
+        const int c = warp_cnt[w * E + x];
+        warp_cnt[w * E + x] = acc;
+        acc += c;
+      }
+      running[x] = acc;
+    }
+    __syncthreads();
+    if (slot < p.numel) p.dest_pos[slot] = e >= 0 ? base[e] + warp_cnt[warp * E + e] + rank_in_warp : -1;
+    __syncthreads();
+  }
 }
 
-struct EpDispatchParams {
-  const void* hidden;             // [T, H] this rank's tokens
-  const void* topk_ids;           // [T * top_k] GLOBAL expert ids (int32 or int64)
-  const float* topk_weights;      // [T * top_k]
-  const int32_t* sorted_slots;    // [numel] slots sorted by expert
-  const int32_t* expert_prefix;   // [E + 1]
-  const int32_t* dest_base;       // [E]
-  PeerPtrs rows, w, meta;         // rows_sym / w_sym / meta_sym of every rank
-  int64_t hidden_row_stride;      // elements
-  int numel, top_k, row_vecs /* H * elemsize / 16 */, experts, world, rank, cap, ids_are_int64;
+// Slot-indexed dispatch; the last CTA to finish signals every rank (flag slot 1), nobody waits here.
+struct EpSendParams {
+  const void* hidden;
+  const void* topk_ids;
+  const float* topk_weights;
+  const int32_t* dest_pos;
+  PeerPtrs rows, w, meta, flags;
+  int* done_counter;
+  int64_t hidden_row_stride;
+  int numel, top_k, row_vecs, experts, world, rank, cap, ids_are_int64, epoch;
 };
 
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams p) {
+__global__ void __launch_bounds__(256) ep_send_kernel(const EpSendParams p) {
   const int epr = p.experts / p.world;
-  for (int j = blockIdx.x; j < p.numel; j += gridDim.x) {
-    const int slot = p.sorted_slots[j];
-    if (slot < 0 || slot >= p.numel) continue;   // slots whose id was out of range are absent from the list
-    const int e = p.ids_are_int64 ? (int)reinterpret_cast<const int64_t*>(p.topk_ids)[slot]
-                                  : reinterpret_cast<const int32_t*>(p.topk_ids)[slot];
-    if (e < 0 || e >= p.experts) continue;
-    const int r = e / epr;
-    const int pos = p.dest_base[e] + (j - p.expert_prefix[e]);
-    if (pos >= p.cap) continue;
+  for (int slot = blockIdx.x; slot < p.numel; slot += gridDim.x) {
+    const int pos = p.dest_pos[slot];
+    if (pos < 0 || pos >= p.cap) continue;
+    const int r = load_id(p.topk_ids, slot, p.ids_are_int64) / epr;
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.hidden) +
                                                       (int64_t)(slot / p.top_k) * p.hidden_row_stride * 2);
     uint4* dst = reinterpret_cast<uint4*>(p.rows.p[r]) + (int64_t)pos * p.row_vecs;
@@ -184,12 +230,73 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams
       reinterpret_cast<int32_t*>(p.meta.p[r])[pos] = (p.rank << 24) | slot;
     }
   }
-  __threadfence_system();   // peer stores are performed before the barrier kernel that follows signals
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(p.done_counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *p.done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        st_release_sys(reinterpret_cast<int*>(p.flags.p[r]) + 1 * ep::FLAG_STRIDE + p.rank, p.epoch);
+    }
+  }
 }
 
-__global__ void __launch_bounds__(32) ep_barrier_kernel(const PeerPtrs flags, int slot, int rank, int world,
-                                                        int epoch, int* status) {
-  cross_gpu_barrier(flags, slot, rank, world, epoch, status, 42 + slot);
+// Top-k combine that first waits (bounded) until every rank has signalled flag slot 2.
+template <typename T>
+__global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ partial, T* __restrict__ out,
+                                                         int64_t tokens, int top_k, int hidden,
+                                                         int64_t out_row_stride, const int* wait_flags, int world,
+                                                         int epoch, int* status) {
+  using T2 = typename Elem<T>::T2;
+  if (threadIdx.x < world) {
+    uint64_t t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+      if (ld_acquire_sys(wait_flags + threadIdx.x) >= epoch) break;
+      if ((spin & 0x3f) == 0x3f) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > DLB_WAIT_BUDGET_NS) {
+          if (status != nullptr && atomicCAS(status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
+            status[1] = 44;
+            status[2] = (int)blockIdx.x;
+            status[3] = (int)threadIdx.x;
+          }
+          break;
+        }
+      }
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  const int vecs = hidden / 8;
+  const int64_t total = tokens * (int64_t)vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int v = (int)(idx - t * vecs);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      // written by other GPUs during this step: bypass any stale cached copy
+      const uint4 x = __ldcv(reinterpret_cast<const uint4*>(partial + (t * top_k + k) * (int64_t)hidden) + v);
+      const T2* x2 = reinterpret_cast<const T2*>(&x);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<T>::to_f2(x2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    T2* o2 = reinterpret_cast<T2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = Elem<T>::from_f2(acc[2 * j], acc[2 * j + 1]);
+    *(reinterpret_cast<uint4*>(out + t * out_row_stride) + v) = o;
+  }
 }
 
 static int fill_ptrs(PeerPtrs* out, void* const* in, int world, const char* what) {
@@ -205,86 +312,6 @@ static int fill_ptrs(PeerPtrs* out, void* const* in, int world, const char* what
 
 }  // namespace dlb
 
-extern "C" int dlb_ep_plan(const int32_t* expert_prefix, void* const* counts_sym, void* const* flags_sym,
-                           int32_t* dest_base, int32_t* block_start, int32_t* num_post_padded, int32_t* row_map,
-                           int rank, int world, int experts, int64_t cap, int epoch, int32_t* status,
-                           void* stream) {
-  using namespace dlb;
-  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
-                "ep_plan: rank %d of %d", rank, world);
-  DLB_CHECK_ARG(experts >= world && experts <= ep::MAX_EXPERTS && experts % world == 0, DLB_ERR_BAD_ARG,
-                "ep_plan: %d experts over %d ranks", experts, world);
-  DLB_CHECK_ARG(cap >= 128 && cap % 128 == 0 && cap < (1LL << 24), DLB_ERR_BAD_ARG,
-                "ep_plan: capacity %lld must be a multiple of 128 below 2^24", (long long)cap);
-  DLB_CHECK_ARG(expert_prefix && dest_base && block_start && num_post_padded && row_map, DLB_ERR_BAD_ARG,
-                "ep_plan: null pointer");
-  EpPlanParams p;
-  int rc = fill_ptrs(&p.counts, counts_sym, world, "counts");
-  if (rc != DLB_OK) return rc;
-  rc = fill_ptrs(&p.flags, flags_sym, world, "flags");
-  if (rc != DLB_OK) return rc;
-  p.expert_prefix = expert_prefix;
-  p.dest_base = dest_base;
-  p.block_start = block_start;
-  p.num_post_padded = num_post_padded;
-  p.row_map = row_map;
-  p.rank = rank;
-  p.world = world;
-  p.experts = experts;
-  p.cap = (int)cap;
-  p.epoch = epoch;
-  p.status = status;
-  ep_plan_kernel<<<1, ep::PLAN_THREADS, 0, (cudaStream_t)stream>>>(p);
-  DLB_CUDA_LAUNCH_CHECK();
-  return DLB_OK;
-}
-
-extern "C" int dlb_ep_dispatch(const void* hidden, int64_t hidden_row_stride, int64_t hidden_cols, int elem_size,
-                               const void* topk_ids, int ids_are_int64, const float* topk_weights,
-                               const int32_t* sorted_slots, const int32_t* expert_prefix, const int32_t* dest_base,
-                               void* const* rows_sym, void* const* w_sym, void* const* meta_sym, int64_t numel,
-                               int top_k, int rank, int world, int experts, int64_t cap, void* stream) {
-  using namespace dlb;
-  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
-                "ep_dispatch: rank %d of %d", rank, world);
-  DLB_CHECK_ARG(elem_size == 2, DLB_ERR_UNSUPPORTED, "ep_dispatch: 16-bit rows only");
-  DLB_CHECK_ARG((hidden_cols * elem_size) % 16 == 0 && (hidden_row_stride * elem_size) % 16 == 0 &&
-                    (((uintptr_t)hidden) & 15) == 0,
-                DLB_ERR_ALIGNMENT, "ep_dispatch: rows must be 16-byte aligned multiples of 16 bytes");
-  DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 24) && top_k >= 1, DLB_ERR_BAD_ARG, "ep_dispatch: bad sizes");
-  if (numel == 0) return DLB_OK;
-  DLB_CHECK_ARG(hidden && topk_ids && topk_weights && sorted_slots && expert_prefix && dest_base, DLB_ERR_BAD_ARG,
-                "ep_dispatch: null pointer");
-  EpDispatchParams p;
-  int rc = fill_ptrs(&p.rows, rows_sym, world, "rows");
-  if (rc != DLB_OK) return rc;
-  rc = fill_ptrs(&p.w, w_sym, world, "weights");
-  if (rc != DLB_OK) return rc;
-  rc = fill_ptrs(&p.meta, meta_sym, world, "meta");
-  if (rc != DLB_OK) return rc;
-  p.hidden = hidden;
-  p.topk_ids = topk_ids;
-  p.topk_weights = topk_weights;
-  p.sorted_slots = sorted_slots;
-  p.expert_prefix = expert_prefix;
-  p.dest_base = dest_base;
-  p.hidden_row_stride = hidden_row_stride;
-  p.numel = (int)numel;
-  p.top_k = top_k;
-  p.row_vecs = (int)(hidden_cols * elem_size / 16);
-  p.experts = experts;
-  p.world = world;
-  p.rank = rank;
-  p.cap = (int)cap;
-  p.ids_are_int64 = ids_are_int64;
-  int64_t blocks = numel;
-  const int64_t limit = (int64_t)sm_count(current_device()) * 16;
-  if (blocks > limit) blocks = limit;
-  ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
-  DLB_CUDA_LAUNCH_CHECK();
-  return DLB_OK;
-}
-
 extern "C" int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status,
                               void* stream) {
   using namespace dlb;
@@ -295,6 +322,129 @@ extern "C" int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int wo
   const int rc = fill_ptrs(&f, flags_sym, world, "flags");
   if (rc != DLB_OK) return rc;
   ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, slot, rank, world, epoch, status);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_ep_route(const void* topk_ids, int ids_are_int64, int64_t numel, void* const* counts_sym,
+                            void* const* flags_sym, int32_t* dest_pos, int32_t* block_start,
+                            int32_t* num_post_padded, int32_t* row_map, int rank, int world, int experts,
+                            int64_t cap, int epoch, int32_t* status, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
+                "ep_route: rank %d of %d", rank, world);
+  DLB_CHECK_ARG(experts >= world && experts <= ep::MAX_EXPERTS && experts % world == 0, DLB_ERR_BAD_ARG,
+                "ep_route: %d experts over %d ranks", experts, world);
+  DLB_CHECK_ARG(cap >= 128 && cap % 128 == 0 && cap < (1LL << 24), DLB_ERR_BAD_ARG,
+                "ep_route: capacity %lld must be a multiple of 128 below 2^24", (long long)cap);
+  DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 24), DLB_ERR_BAD_ARG, "ep_route: numel out of range");
+  DLB_CHECK_ARG((numel == 0 || (topk_ids && dest_pos)) && block_start && num_post_padded && row_map,
+                DLB_ERR_BAD_ARG, "ep_route: null pointer");
+  EpRouteParams p;
+  int rc = fill_ptrs(&p.counts, counts_sym, world, "counts");
+  if (rc != DLB_OK) return rc;
+  rc = fill_ptrs(&p.flags, flags_sym, world, "flags");
+  if (rc != DLB_OK) return rc;
+  p.topk_ids = topk_ids;
+  p.dest_pos = dest_pos;
+  p.block_start = block_start;
+  p.num_post_padded = num_post_padded;
+  p.row_map = row_map;
+  p.numel = (int)numel;
+  p.ids_are_int64 = ids_are_int64;
+  p.rank = rank;
+  p.world = world;
+  p.experts = experts;
+  p.cap = (int)cap;
+  p.epoch = epoch;
+  p.status = status;
+  const size_t smem = sizeof(int32_t) * (size_t)experts * (6 + ep::PLAN_THREADS / 32);
+  cudaError_t e = cudaFuncSetAttribute(ep_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_last_error("ep_route: smem attribute: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  ep_route_kernel<<<1, ep::PLAN_THREADS, smem, (cudaStream_t)stream>>>(p);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_t hidden_cols, int elem_size,
+                           const void* topk_ids, int ids_are_int64, const float* topk_weights,
+                           const int32_t* dest_pos, void* const* rows_sym, void* const* w_sym,
+                           void* const* meta_sym, void* const* flags_sym, int32_t* done_counter, int64_t numel,
+                           int top_k, int rank, int world, int experts, int64_t cap, int epoch, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
+                "ep_send: rank %d of %d", rank, world);
+  DLB_CHECK_ARG(elem_size == 2, DLB_ERR_UNSUPPORTED, "ep_send: 16-bit rows only");
+  DLB_CHECK_ARG((hidden_cols * elem_size) % 16 == 0 && (hidden_row_stride * elem_size) % 16 == 0 &&
+                    (((uintptr_t)hidden) & 15) == 0,
+                DLB_ERR_ALIGNMENT, "ep_send: rows must be 16-byte aligned multiples of 16 bytes");
+  DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 24) && top_k >= 1 && done_counter != nullptr, DLB_ERR_BAD_ARG,
+                "ep_send: bad sizes");
+  DLB_CHECK_ARG(numel == 0 || (hidden && topk_ids && topk_weights && dest_pos), DLB_ERR_BAD_ARG,
+                "ep_send: null pointer");
+  EpSendParams p;
+  int rc = fill_ptrs(&p.rows, rows_sym, world, "rows");
+  if (rc != DLB_OK) return rc;
+  rc = fill_ptrs(&p.w, w_sym, world, "weights");
+  if (rc != DLB_OK) return rc;
+  rc = fill_ptrs(&p.meta, meta_sym, world, "meta");
+  if (rc != DLB_OK) return rc;
+  rc = fill_ptrs(&p.flags, flags_sym, world, "flags");
+  if (rc != DLB_OK) return rc;
+  p.hidden = hidden;
+  p.topk_ids = topk_ids;
+  p.topk_weights = topk_weights;
+  p.dest_pos = dest_pos;
+  p.done_counter = done_counter;
+  p.hidden_row_stride = hidden_row_stride;
+  p.numel = (int)numel;
+  p.top_k = top_k;
+  p.row_vecs = (int)(hidden_cols * elem_size / 16);
+  p.experts = experts;
+  p.world = world;
+  p.rank = rank;
+  p.cap = (int)cap;
+  p.ids_are_int64 = ids_are_int64;
+  p.epoch = epoch;
+  int64_t blocks = numel < 1 ? 1 : numel;
+  const int64_t limit = (int64_t)sm_count(current_device()) * 8;
+  if (blocks > limit) blocks = limit;
+  ep_send_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
+                              int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
+                              int32_t* status, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0, DLB_ERR_BAD_ARG, "ep_combine: bad sizes");
+  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && wait_flags != nullptr, DLB_ERR_BAD_ARG,
+                "ep_combine: bad wait arguments");
+  DLB_CHECK_ARG(hidden % 8 == 0 && out_row_stride % 8 == 0, DLB_ERR_ALIGNMENT,
+                "ep_combine: hidden and row stride must be multiples of 8");
+  DLB_CHECK_ARG((((uintptr_t)partial | (uintptr_t)out) & 15) == 0, DLB_ERR_ALIGNMENT, "ep_combine: unaligned pointer");
+  const int64_t total = tokens * (hidden / 8);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks < 1) blocks = 1;   // the wait still has to happen so that the next step may reuse the buffers
+  const int64_t limit = (int64_t)sm_count(current_device()) * 8;
+  if (blocks > limit) blocks = limit;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DLB_DTYPE_BF16) {
+    ep_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
+        (const __nv_bfloat16*)partial, (__nv_bfloat16*)out, tokens, top_k, (int)hidden, out_row_stride, wait_flags,
+        world, epoch, status);
+  } else if (dtype == DLB_DTYPE_F16) {
+    ep_combine_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)partial, (__half*)out, tokens, top_k,
+                                                                (int)hidden, out_row_stride, wait_flags, world, epoch,
+                                                                status);
+  } else {
+    set_last_error("ep_combine: unsupported dtype %d", dtype);
+    return DLB_ERR_UNSUPPORTED;
+  }
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }

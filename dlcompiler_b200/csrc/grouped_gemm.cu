@@ -74,6 +74,11 @@ struct GroupedGemmParams {
   int* status;
   const int32_t* row_meta;           // FLAG_PEER: (source rank << 24) | slot for every row
   void* peer_out[gg::MAX_PEERS];     // FLAG_PEER: base of every rank's result buffer
+  // optional cross-GPU synchronisation (expert parallelism); null pointers switch it off
+  const int* wait_flags;             // before the first load: wait until wait_flags[r] >= sync_epoch for r < sync_world
+  int* signal_flags[gg::MAX_PEERS];  // after the last store: the last CTA writes sync_epoch to signal_flags[r][0]
+  int* done_counter;                 // device counter used to find the last CTA (left at zero)
+  int sync_world, sync_epoch;
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -198,6 +203,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row);
         if constexpr (kSilu) tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row + p.up_row_offset);
       };
+      if (p.wait_flags != nullptr) {
+        // rows of A are stored by other GPUs: do not read them before every rank has signalled
+        uint64_t t0 = 0;
+        for (int r = 0; r < p.sync_world; ++r) {
+          for (uint32_t spin = 0;; ++spin) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + r) : "memory");
+            if (v >= p.sync_epoch) break;
+            if ((spin & 0x3f) == 0x3f) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (now - t0 > DLB_WAIT_BUDGET_NS) {
+                if (p.status != nullptr && atomicCAS(p.status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
+                  p.status[1] = 5;
+                  p.status[2] = (int)blockIdx.x;
+                  p.status[3] = r;
+                }
+                break;   // proceed on stale data rather than hang; the status word reports it
+              }
+            }
+          }
+        }
+        __threadfence_system();
+      }
       Walker ld, pf;
       start_walker(ld);
       start_walker(pf);
@@ -357,6 +386,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.done_counter != nullptr && threadIdx.x == 0) {
+    // every CTA's stores are fenced above (epilogue) and ordered by the barrier; the CTA that
+    // arrives last tells every rank that this GPU's rows are in place
+    __threadfence();
+    const int prev = atomicAdd(p.done_counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *p.done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.sync_world; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.signal_flags[r]), "r"(p.sync_epoch) : "memory");
+    }
+  }
 }
 
 template <typename T, int FLAGS>
@@ -382,7 +423,9 @@ static int grouped_gemm_impl(const void* a, int64_t a_rows, int64_t a_row_stride
                              int64_t out_row_stride, int64_t n_out, const int32_t* sorted_token_ids,
                              const int32_t* block_start, const float* topk_weights, int64_t numel, int flags,
                              int dtype, int32_t* status, void* stream, const int32_t* row_meta,
-                             void* const* peer_out, int num_peers) {
+                             void* const* peer_out, int num_peers, const int32_t* wait_flags = nullptr,
+                             void* const* signal_flags = nullptr, int32_t* done_counter = nullptr,
+                             int sync_world = 0, int sync_epoch = 0) {
   using namespace dlb::gg;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "grouped_gemm: dtype %d (need fp16 or bf16)", dtype);
@@ -443,6 +486,18 @@ static int grouped_gemm_impl(const void* a, int64_t a_rows, int64_t a_row_stride
   p.status = status;
   p.row_meta = row_meta;
   for (int i = 0; i < MAX_PEERS; ++i) p.peer_out[i] = (peer_out != nullptr && i < num_peers) ? peer_out[i] : nullptr;
+  DLB_CHECK_ARG(sync_world >= 0 && sync_world <= MAX_PEERS, DLB_ERR_BAD_ARG, "grouped_gemm: sync_world %d", sync_world);
+  DLB_CHECK_ARG((signal_flags == nullptr) == (done_counter == nullptr), DLB_ERR_BAD_ARG,
+                "grouped_gemm: signal flags and done counter go together");
+  p.wait_flags = wait_flags;
+  p.done_counter = done_counter;
+  p.sync_world = sync_world;
+  p.sync_epoch = sync_epoch;
+  for (int i = 0; i < MAX_PEERS; ++i)
+    p.signal_flags[i] = (signal_flags != nullptr && i < sync_world) ? (int*)signal_flags[i] : nullptr;
+  if (signal_flags != nullptr)
+    for (int i = 0; i < sync_world; ++i)
+      DLB_CHECK_ARG(signal_flags[i] != nullptr, DLB_ERR_BAD_ARG, "grouped_gemm: null signal flag of rank %d", i);
 
   const int grid = sm_count(current_device());
   cudaStream_t s = (cudaStream_t)stream;
@@ -479,22 +534,29 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row
                                     const float* topk_weights, int64_t numel, int flags, int dtype,
                                     int32_t* status, void* stream) {
   DLB_CHECK_ARG((flags & dlb::gg::FLAG_PEER) == 0, DLB_ERR_BAD_ARG,
-                "grouped_gemm: peer scatter is only available through dlb_moe_grouped_gemm_peer");
+                "grouped_gemm: peer scatter is only available through dlb_moe_grouped_gemm_sync");
   return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride, out,
                                 out_row_stride, n_out, sorted_token_ids, block_start, topk_weights, numel, flags,
                                 dtype, status, stream, nullptr, nullptr, 0);
 }
 
-extern "C" int dlb_moe_grouped_gemm_peer(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
+// Grouped GEMM with optional cross-GPU synchronisation for expert parallelism: waits, before its
+// first load, until wait_flags[r] >= epoch for every rank r (A's rows are stored by other GPUs), and
+// after its last store lets the last CTA write `epoch` to signal_flags[r] of every rank.
+extern "C" int dlb_moe_grouped_gemm_sync(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b,
                                          int num_experts, int64_t rows_per_expert, int64_t k, int64_t b_row_stride,
-                                         void* const* peer_out, int num_peers, int64_t out_row_stride,
+                                         void* out, void* const* peer_out, int num_peers, int64_t out_row_stride,
                                          int64_t n_out, const int32_t* sorted_token_ids,
                                          const int32_t* block_start, const float* row_weights,
-                                         const int32_t* row_meta, int64_t numel, int dtype, int32_t* status,
+                                         const int32_t* row_meta, int64_t numel, int flags, int dtype,
+                                         const int32_t* wait_flags, void* const* signal_flags,
+                                         int32_t* done_counter, int sync_world, int sync_epoch, int32_t* status,
                                          void* stream) {
   using namespace dlb::gg;
-  return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride,
-                                peer_out != nullptr && num_peers > 0 ? peer_out[0] : nullptr, out_row_stride, n_out,
-                                sorted_token_ids, block_start, row_weights, numel, FLAG_WEIGHT | FLAG_PEER, dtype,
-                                status, stream, row_meta, peer_out, num_peers);
+  void* o = out;
+  if ((flags & FLAG_PEER) && o == nullptr && peer_out != nullptr && num_peers > 0) o = peer_out[0];
+  return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride, o,
+                                out_row_stride, n_out, sorted_token_ids, block_start, row_weights, numel, flags,
+                                dtype, status, stream, row_meta, peer_out, num_peers, wait_flags, signal_flags,
+                                done_counter, sync_world, sync_epoch);
 }

@@ -223,7 +223,11 @@ class EpPeerContext:
         for t in (self.counts, self.flags, self.rows, self.w, self.meta, self.back):
             t.zero_()
         # plan outputs and the activation buffer are ordinary local memory
-        self.dest_base = torch.empty(num_experts, dtype=torch.int32, device=device)
+        self.dest_pos = torch.empty(max(self.max_slots, 1), dtype=torch.int32, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)     # last-CTA counters (send, down GEMM)
+        # flag slot 2, entry `rank`, of every rank: raised by this rank's down GEMM
+        self.signal2_tbl = (ctypes.c_void_p * self.world)(
+            *[int(self.flags_tbl[r]) + 4 * (2 * 16 + self.rank) for r in range(self.world)])
         self.block_start = torch.empty(self.experts_per_rank + 1, dtype=torch.int32, device=device)
         self.num_post = torch.empty(1, dtype=torch.int32, device=device)
         self.row_map = torch.empty(self.cap, dtype=torch.int32, device=device)
@@ -234,21 +238,22 @@ class EpPeerContext:
         dist.barrier(group)
 
 
-PEER_KERNELS_PER_STEP = 8  # align, plan, dispatch, barrier, gemm, gemm(+peer scatter), barrier, combine
+PEER_KERNELS_PER_STEP = 5  # route, send, gemm (gate/up), gemm (down + peer scatter), combine
 
 
 def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int,
                       _events: list = None):
     """Expert-parallel fused_moe whose token exchange runs inside our own kernels over peer memory.
 
-    Same contract as `ep_fused_moe`.  Per step: sort slots -> publish counts + cross-GPU barrier +
-    receive layout (dlb_ep_plan) -> rows stored into the owners' buffers (dlb_ep_dispatch) ->
-    barrier -> grouped GEMM gate/up+silu on the received rows -> grouped GEMM down whose epilogue
-    stores each weighted row into the sending rank's result buffer -> barrier -> top-k combine.
-    Nothing returns to the host in between, so the launches queue back to back.
+    Same contract as `ep_fused_moe`.  Five launches per step, nothing returns to the host in between:
+      route    count slots per expert, exchange counts (peer stores + cross-GPU barrier), receive
+               layout, destination row of every slot
+      send     rows, weights and (rank, slot) tags stored into the owners' buffers; last CTA raises a flag
+      GEMM     gate/up + silu on the received rows (its producer waits for every rank's flag first)
+      GEMM     down x weight, epilogue stores each row into the SENDER's result buffer; last CTA raises a flag
+      combine  waits for every rank's flag, then sums each token's top-k rows
     """
     from .. import _lib
-    from ..kernels.fused_moe import _EventPair, _grouped_gemm
 
     lib = _lib.load()
     dev = hidden_states.device
@@ -263,36 +268,49 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
     ids = ids.contiguous()
     tw = topk_weights.to(torch.float32).reshape(-1).contiguous()
     ctx.epoch += 1
+    epoch, world, rank = ctx.epoch, ctx.world, ctx.rank
     stream = _lib.stream_ptr(dev)
-    sorted_slots, prefix = CudaOps.sort_slots(ids, ctx.num_experts)
+    is64 = int(ids.dtype == torch.int64)
+    dt = _lib.dtype_code(ctx.act)
+    E_local, N1, _ = w1_local.shape
+    _, H_out, inter = w2_local.shape
+    out = torch.empty((T, H_out), dtype=ctx.dtype, device=dev)
+    flags_local = ctx.flags.data_ptr()
     with torch.cuda.device(dev):
-        rc = lib.dlb_ep_plan(prefix.data_ptr(), ctx.counts_tbl, ctx.flags_tbl, ctx.dest_base.data_ptr(),
-                             ctx.block_start.data_ptr(), ctx.num_post.data_ptr(), ctx.row_map.data_ptr(), ctx.rank,
-                             ctx.world, ctx.num_experts, ctx.cap, ctx.epoch, ctx.status.data_ptr(), stream)
-        _lib.check(rc, "ep_plan")
-        rc = lib.dlb_ep_dispatch(hidden_states.data_ptr(), hidden_states.stride(0), H, hidden_states.element_size(),
-                                 ids.data_ptr(), int(ids.dtype == torch.int64), tw.data_ptr(),
-                                 sorted_slots.data_ptr(), prefix.data_ptr(), ctx.dest_base.data_ptr(), ctx.rows_tbl,
-                                 ctx.w_tbl, ctx.meta_tbl, numel, topk, ctx.rank, ctx.world, ctx.num_experts, ctx.cap,
-                                 stream)
-        _lib.check(rc, "ep_dispatch")
-        rc = lib.dlb_ep_barrier(ctx.flags_tbl, 1, ctx.rank, ctx.world, ctx.epoch, ctx.status.data_ptr(), stream)
-        _lib.check(rc, "ep_barrier")
-    ev = _EventPair(_events, "grouped_gemm_gate_up_silu")
-    _grouped_gemm(ctx.rows, w1_local, ctx.act, ctx.inter, ctx.row_map, ctx.block_start, None, ctx.cap,
-                  _lib.GEMM_FUSE_SILU)
-    ev.stop()
-    E_local, H_out, inter = w2_local.shape
-    ev = _EventPair(_events, "grouped_gemm_down_peer_scatter")
-    with torch.cuda.device(dev):
-        rc = lib.dlb_moe_grouped_gemm_peer(ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(),
-                                           E_local, H_out, inter, w2_local.stride(1), ctx.back_tbl, ctx.world,
-                                           ctx.back.stride(0), H_out, ctx.row_map.data_ptr(),
-                                           ctx.block_start.data_ptr(), ctx.w.data_ptr(), ctx.meta.data_ptr(), ctx.cap,
-                                           _lib.dtype_code(ctx.act), ctx.status.data_ptr(), stream)
-        _lib.check(rc, "moe_grouped_gemm_peer")
-    ev.stop()
-    with torch.cuda.device(dev):
-        rc = lib.dlb_ep_barrier(ctx.flags_tbl, 2, ctx.rank, ctx.world, ctx.epoch, ctx.status.data_ptr(), stream)
-        _lib.check(rc, "ep_barrier")
-    return CudaOps.combine(ctx.back[:numel], T, topk)
+        rc = lib.dlb_ep_route(ids.data_ptr(), is64, numel, ctx.counts_tbl, ctx.flags_tbl, ctx.dest_pos.data_ptr(),
+                              ctx.block_start.data_ptr(), ctx.num_post.data_ptr(), ctx.row_map.data_ptr(), rank, world,
+                              ctx.num_experts, ctx.cap, epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "ep_route")
+        rc = lib.dlb_ep_send(hidden_states.data_ptr(), hidden_states.stride(0), H, hidden_states.element_size(),
+                             ids.data_ptr(), is64, tw.data_ptr(), ctx.dest_pos.data_ptr(), ctx.rows_tbl, ctx.w_tbl,
+                             ctx.meta_tbl, ctx.flags_tbl, ctx.counters[0:1].data_ptr(), numel, topk, rank, world,
+                             ctx.num_experts, ctx.cap, epoch, stream)
+        _lib.check(rc, "ep_send")
+        if _events is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        rc = lib.dlb_moe_grouped_gemm_sync(
+            ctx.rows.data_ptr(), ctx.cap, ctx.rows.stride(0), w1_local.data_ptr(), E_local, N1, H, w1_local.stride(1),
+            ctx.act.data_ptr(), None, 0, ctx.act.stride(0), ctx.inter, ctx.row_map.data_ptr(),
+            ctx.block_start.data_ptr(), None, None, ctx.cap, _lib.GEMM_FUSE_SILU, dt,
+            flags_local + 4 * (1 * 16), None, None, world, epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "moe_grouped_gemm_sync(gate/up)")
+        if _events is not None:
+            e1.record()
+            _events.append(("grouped_gemm_gate_up_silu", e0, e1))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        rc = lib.dlb_moe_grouped_gemm_sync(
+            ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(), E_local, H_out, inter,
+            w2_local.stride(1), None, ctx.back_tbl, world, ctx.back.stride(0), H_out, ctx.row_map.data_ptr(),
+            ctx.block_start.data_ptr(), ctx.w.data_ptr(), ctx.meta.data_ptr(), ctx.cap,
+            _lib.GEMM_WEIGHT | _lib.GEMM_PEER, dt, None, ctx.signal2_tbl, ctx.counters[1:2].data_ptr(), world, epoch,
+            ctx.status.data_ptr(), stream)
+        _lib.check(rc, "moe_grouped_gemm_sync(down)")
+        if _events is not None:
+            e1.record()
+            _events.append(("grouped_gemm_down_peer_scatter", e0, e1))
+        rc = lib.dlb_ep_combine(ctx.back.data_ptr(), out.data_ptr(), T, topk, H_out, out.stride(0), dt,
+                                flags_local + 4 * (2 * 16), world, epoch, ctx.status.data_ptr(), stream)
+        _lib.check(rc, "ep_combine")
+    return out

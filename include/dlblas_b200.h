@@ -87,38 +87,53 @@ int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row_stride, co
                          const int32_t* block_start, const float* topk_weights, int64_t numel, int flags,
                          int dtype, int32_t* status, void* stream);
 
-/* dlb_moe_grouped_gemm with the DLB_GEMM_WEIGHT epilogue whose rows are stored straight into the
- * result buffers of the ranks that sent them (plain stores into peer memory over NVLink):
- * row p goes to peer_out[row_meta[p] >> 24] + (row_meta[p] & 0xffffff) * out_row_stride.
- * Fuses the down projection of python/dlBLAS/dlblas/kernels/fused_moe.py:359-373 with the
- * expert-parallel combine exchange; the reference has no such exchange (it keeps tokens replicated,
- * fused_moe.py:113-114, 329-332). */
-int dlb_moe_grouped_gemm_peer(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b, int num_experts,
-                              int64_t rows_per_expert, int64_t k, int64_t b_row_stride, void* const* peer_out,
-                              int num_peers, int64_t out_row_stride, int64_t n_out,
+/* dlb_moe_grouped_gemm with the pieces expert parallelism needs (no counterpart in the reference, which
+ * keeps tokens replicated: python/dlBLAS/dlblas/kernels/fused_moe.py:113-114, 329-332):
+ *   - flags may add DLB_GEMM_PEER (8, with DLB_GEMM_WEIGHT): row p is stored straight into the result
+ *     buffer of the rank that sent it, peer_out[row_meta[p] >> 24] + (row_meta[p] & 0xffffff) *
+ *     out_row_stride, with plain stores into peer memory over NVLink (fuses the down projection of
+ *     fused_moe.py:359-373 with the combine exchange);
+ *   - wait_flags (device int32[sync_world], may be NULL): before its first load the kernel waits until
+ *     wait_flags[r] >= sync_epoch for every rank r (A's rows are stored by other GPUs);
+ *   - signal_flags (HOST array of sync_world device pointers, may be NULL) + done_counter (device int32,
+ *     zero): after its last store the last CTA writes sync_epoch to *signal_flags[r] for every rank r.
+ * Waits are bounded; a timeout is reported in `status` and the kernel proceeds. */
+#define DLB_GEMM_PEER 8
+int dlb_moe_grouped_gemm_sync(const void* a, int64_t a_rows, int64_t a_row_stride, const void* b, int num_experts,
+                              int64_t rows_per_expert, int64_t k, int64_t b_row_stride, void* out,
+                              void* const* peer_out, int num_peers, int64_t out_row_stride, int64_t n_out,
                               const int32_t* sorted_token_ids, const int32_t* block_start, const float* row_weights,
-                              const int32_t* row_meta, int64_t numel, int dtype, int32_t* status, void* stream);
+                              const int32_t* row_meta, int64_t numel, int flags, int dtype,
+                              const int32_t* wait_flags, void* const* signal_flags, int32_t* done_counter,
+                              int sync_world, int sync_epoch, int32_t* status, void* stream);
 
 /* Expert-parallel exchange over peer memory (one process per GPU; `*_sym` arguments are HOST arrays of
  * `world` device pointers, one per rank, to buffers of identical size on every rank).  No counterpart
- * in the reference.
- *   dlb_ep_plan      publishes this rank's per-expert counts (expert_prefix = prefix sums from
- *                    dlb_moe_align_block_size with block 1) into every rank's count matrix
- *                    (counts_sym: int32 [world][experts]), synchronises the ranks through flags_sym
- *                    (int32 [8][16], zero-initialised, epoch must grow by one per step), and derives the
- *                    receive layout: dest_base[experts], block_start[experts/world + 1],
- *                    num_post_padded[1], row_map[cap] (p for rows that will hold a token, cap otherwise).
- *   dlb_ep_dispatch  stores every local slot's hidden row, routing weight and (rank << 24 | slot) into
- *                    the owner rank's rows_sym [cap][hidden], w_sym [cap], meta_sym [cap].
- *   dlb_ep_barrier   cross-GPU barrier on flag slot 1..7 (bounded wait; timeout -> status word). */
-int dlb_ep_plan(const int32_t* expert_prefix, void* const* counts_sym, void* const* flags_sym, int32_t* dest_base,
-                int32_t* block_start, int32_t* num_post_padded, int32_t* row_map, int rank, int world, int experts,
-                int64_t cap, int epoch, int32_t* status, void* stream);
-int dlb_ep_dispatch(const void* hidden, int64_t hidden_row_stride, int64_t hidden_cols, int elem_size,
-                    const void* topk_ids, int ids_are_int64, const float* topk_weights, const int32_t* sorted_slots,
-                    const int32_t* expert_prefix, const int32_t* dest_base, void* const* rows_sym,
-                    void* const* w_sym, void* const* meta_sym, int64_t numel, int top_k, int rank, int world,
-                    int experts, int64_t cap, void* stream);
+ * in the reference.  flags_sym: int32 [8][16] zero-initialised; slot s, source rank r at [s * 16 + r];
+ * `epoch` must grow by one per step.
+ *   dlb_ep_route    counts this rank's slots per GLOBAL expert, publishes the counts into every rank's
+ *                   count matrix (counts_sym: int32 [world][experts]), synchronises the ranks (flag slot
+ *                   0), derives the receive layout (block_start[experts/world + 1], num_post_padded[1],
+ *                   row_map[cap]: p for rows that will hold a token, cap otherwise) and the row every
+ *                   local slot will occupy in its owner's buffer (dest_pos[numel], stable inside an
+ *                   expert, -1 for ids out of range).
+ *   dlb_ep_send     stores every slot's hidden row, routing weight and (rank << 24 | slot) into the owner
+ *                   rank's rows_sym [cap][hidden], w_sym [cap], meta_sym [cap]; the last CTA raises flag
+ *                   slot 1 on every rank (done_counter: device int32, zero).
+ *   dlb_ep_combine  dlb_moe_combine that first waits until wait_flags[r] >= epoch for every rank r.
+ *   dlb_ep_barrier  stand-alone cross-GPU barrier on a flag slot (bounded wait; timeout -> status). */
+int dlb_ep_route(const void* topk_ids, int ids_are_int64, int64_t numel, void* const* counts_sym,
+                 void* const* flags_sym, int32_t* dest_pos, int32_t* block_start, int32_t* num_post_padded,
+                 int32_t* row_map, int rank, int world, int experts, int64_t cap, int epoch, int32_t* status,
+                 void* stream);
+int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_t hidden_cols, int elem_size,
+                const void* topk_ids, int ids_are_int64, const float* topk_weights, const int32_t* dest_pos,
+                void* const* rows_sym, void* const* w_sym, void* const* meta_sym, void* const* flags_sym,
+                int32_t* done_counter, int64_t numel, int top_k, int rank, int world, int experts, int64_t cap,
+                int epoch, void* stream);
+int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
+                   int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
+                   int32_t* status, void* stream);
 int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status, void* stream);
 
 /* out[t, :] = sum over k of partial[t * top_k + k, :] (fp32 accumulate, one rounding): the
