@@ -325,6 +325,7 @@ def run_reference(args):
     """The reference arm: CPU implementation on the host cores, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        args._stdout_guard.restore()
         return
     from dlcompiler_b200 import workloads as W
     from oracle import dlblas_oracle as oracle
@@ -355,6 +356,7 @@ def run_reference(args):
                                    "test ground truth (the reference's Triton kernels cannot run on CPU)"},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    args._stdout_guard.restore()
     print(json.dumps(line), flush=True)
 
 
@@ -404,7 +406,7 @@ def run_ours(args):
 
         launches_per_step = 5
         with ClockSampler(local_rank) as clk:
-            ms = time_steps(step, args.steps, args.warmup, min_warm_s=0.3)
+            ms = time_steps(step, args.steps, args.warmup, min_warm_s=args.warm_seconds)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]
         gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
@@ -463,7 +465,7 @@ def run_ours(args):
         launches_per_step = launches
         with ClockSampler(local_rank) as clk:
             # every rank must run the same number of steps (they meet in cross-GPU barriers): fixed count
-            ms = time_steps(step, args.steps, max(args.warmup, 200), barrier)
+            ms = time_steps(step, args.steps, max(args.warmup, 1000), barrier)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]
         gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
@@ -535,11 +537,27 @@ def run_ours(args):
                                     "sample": f"first {args.cpu_sample} of 4096 tokens, best of {passes} passes "
                                               f"({secs:.2f} s each); torch CPU restatement of the reference test "
                                               "ground truth"}
+    args._stdout_guard.restore()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+class _StdoutToStderr:
+    """Libraries (NCCL) print banners on stdout; the contract is ONE JSON line there.  Everything
+    written to file descriptor 1 goes to stderr until `restore()`."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self._saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def restore(self):
+        sys.stdout.flush()
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
 
 
 def main():
@@ -553,8 +571,12 @@ def main():
                     help="N > 1: token exchange by our peer-memory kernels (default) or by NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--cpu-sample", type=int, default=4096)
+    ap.add_argument("--warm-seconds", type=float, default=0.3,
+                    help="N = 1: keep warming up until this much wall time has passed (device under load)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    guard = _StdoutToStderr()
+    args._stdout_guard = guard
     if args.impl == "reference":
         run_reference(args)
     else:
