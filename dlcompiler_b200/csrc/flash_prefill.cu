@@ -22,7 +22,8 @@
 //              (16-bit, swizzled K-major) to shared memory for the next MMA,
 //              rescales O in TMEM only when the row max grew by more than
 //              2^8 (lazy rescaling), and finally normalises and stores O
-// CTAs are ordered by decreasing causal work so the tail of the grid is short.
+// CTAs are ordered (sequence, kv head) group by group, heavy causal tiles first inside a group, so the
+// resident CTAs share K/V through L2 and the tail of each group is short.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -167,10 +168,17 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
   constexpr int OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_P = L::OFF_P, OFF_CTRL = L::OFF_CTRL;
   // ---- which tile ----
-  const int head = blockIdx.x % p.hq;
-  const int t_lin = blockIdx.x / p.hq;
-  const int seq = t_lin % p.batch;
-  const int tile = p.max_tiles - 1 - t_lin / p.batch;     // heavy (late) tiles first
+  // CTA order: (sequence, kv head) groups one after the other; inside a group the heavy (late, causal)
+  // tiles first, the q heads of the group adjacent.  The CTAs resident at any time then share the K/V
+  // of one or two groups (4 MiB each at 8k tokens), which stay in L2 instead of being re-read from HBM.
+  int x = blockIdx.x;
+  const int hig = x % p.group;
+  x /= p.group;
+  const int tile = p.max_tiles - 1 - x % p.max_tiles;
+  x /= p.max_tiles;
+  const int kvh_ = x % p.hkv;
+  const int seq = x / p.hkv;
+  const int head = kvh_ * p.group + hig;
   const int seq_len = p.b_seq_len[seq];
   const int q0 = tile * BM;
   if (q0 >= seq_len) return;

@@ -183,6 +183,50 @@ struct RotaryParams {
   int hq, hk, dim;
 };
 
+// Vector path: 16-bit types, half a head a multiple of 8 elements, 16-byte aligned rows.  One thread
+// rotates 8 lower-half and the matching 8 upper-half elements (two 128-bit loads, two stores).
+template <typename T> __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
+  using T2 = typename Elem<T>::T2;
+  const int64_t t = blockIdx.x;
+  const int half = p.dim >> 1;
+  const int hv = half >> 3;                      // vectors per half head
+  const uint4* cs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.cos) + t * p.dim);
+  const uint4* sn = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.sin) + t * p.dim);
+  const int total = (p.hq + p.hk) * hv;
+  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int h = idx / hv;
+    const int i = idx - h * hv;
+    const T* src;
+    T* dst;
+    if (h < p.hq) {
+      src = reinterpret_cast<const T*>(p.q) + t * p.q_st + (int64_t)h * p.q_sh;
+      dst = reinterpret_cast<T*>(p.qo) + t * p.qo_st + (int64_t)h * p.qo_sh;
+    } else {
+      src = reinterpret_cast<const T*>(p.k) + t * p.k_st + (int64_t)(h - p.hq) * p.k_sh;
+      dst = reinterpret_cast<T*>(p.ko) + t * p.ko_st + (int64_t)(h - p.hq) * p.ko_sh;
+    }
+    const uint4 lo = *(reinterpret_cast<const uint4*>(src) + i);
+    const uint4 hi = *(reinterpret_cast<const uint4*>(src + half) + i);
+    const uint4 cl = __ldg(cs + i), ch = __ldg(cs + hv + i), sl = __ldg(sn + i), sh = __ldg(sn + hv + i);
+    uint4 olo, ohi;
+    const T* l8 = reinterpret_cast<const T*>(&lo);
+    const T* h8 = reinterpret_cast<const T*>(&hi);
+    const T* cl8 = reinterpret_cast<const T*>(&cl);
+    const T* ch8 = reinterpret_cast<const T*>(&ch);
+    const T* sl8 = reinterpret_cast<const T*>(&sl);
+    const T* sh8 = reinterpret_cast<const T*>(&sh);
+    T* ol8 = reinterpret_cast<T*>(&olo);
+    T* oh8 = reinterpret_cast<T*>(&ohi);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ol8[j] = rot_lo<T>(l8[j], h8[j], cl8[j], sl8[j]);
+      oh8[j] = rot_hi<T>(l8[j], h8[j], ch8[j], sh8[j]);
+    }
+    *(reinterpret_cast<uint4*>(dst) + i) = olo;
+    *(reinterpret_cast<uint4*>(dst + half) + i) = ohi;
+  }
+}
+
 // One CTA per token; threads sweep (head, element of the lower half).
 template <typename T> __global__ void __launch_bounds__(256) rotary_kernel(const RotaryParams p) {
   const int64_t t = blockIdx.x;
@@ -251,23 +295,37 @@ __global__ void __launch_bounds__(256) fill_kv_cache_kernel(const FillParams p) 
   const int per_tok = p.heads * (k_units + v_units);
   const int total = (slot_hi - slot_lo) * per_tok;
   using U = typename std::conditional<UNIT == 16, uint4, typename std::conditional<UNIT == 4, uint32_t, uint16_t>::type>::type;
-  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+  // blockIdx.z splits a page; four independent copies in flight per thread
+  auto locate = [&](int idx, const U*& src, U*& dst) {
     const int s = idx / per_tok;
     int r = idx - s * per_tok;
     const int slot = slot_lo + s;
     const int64_t tok = tok0 + s;
     if (r < p.heads * k_units) {
       const int h = r / k_units, u = r - h * k_units;
-      const U* src = reinterpret_cast<const U*>(reinterpret_cast<const uint8_t*>(p.ks) + (tok * p.ks_st + h * p.ks_sh) * es) + u;
-      U* dst = reinterpret_cast<U*>(reinterpret_cast<uint8_t*>(p.kc) + (page * p.kc_sp + slot * p.kc_ss + h * p.kc_sh) * es) + u;
-      *dst = *src;
+      src = reinterpret_cast<const U*>(reinterpret_cast<const uint8_t*>(p.ks) + (tok * p.ks_st + h * p.ks_sh) * es) + u;
+      dst = reinterpret_cast<U*>(reinterpret_cast<uint8_t*>(p.kc) + (page * p.kc_sp + slot * p.kc_ss + h * p.kc_sh) * es) + u;
     } else {
       r -= p.heads * k_units;
       const int h = r / v_units, u = r - h * v_units;
-      const U* src = reinterpret_cast<const U*>(reinterpret_cast<const uint8_t*>(p.vs) + (tok * p.vs_st + h * p.vs_sh) * es) + u;
-      U* dst = reinterpret_cast<U*>(reinterpret_cast<uint8_t*>(p.vc) + (page * p.vc_sp + slot * p.vc_ss + h * p.vc_sh) * es) + u;
-      *dst = *src;
+      src = reinterpret_cast<const U*>(reinterpret_cast<const uint8_t*>(p.vs) + (tok * p.vs_st + h * p.vs_sh) * es) + u;
+      dst = reinterpret_cast<U*>(reinterpret_cast<uint8_t*>(p.vc) + (page * p.vc_sp + slot * p.vc_ss + h * p.vc_sh) * es) + u;
     }
+  };
+  const int stride = blockDim.x * gridDim.z;
+  for (int idx = threadIdx.x + blockIdx.z * blockDim.x; idx < total; idx += 4 * stride) {
+    const U* src[4];
+    U* dst[4];
+    U val[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (idx + j * stride < total) locate(idx + j * stride, src[j], dst[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (idx + j * stride < total) val[j] = *src[j];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (idx + j * stride < total) *dst[j] = val[j];
   }
 }
 
@@ -314,6 +372,19 @@ extern "C" int dlb_apply_rotary(const void* q, const void* k, const void* cos, c
   RotaryParams p{q, k, cos, sin, q_out, k_out, q_stride_t, q_stride_h, k_stride_t, k_stride_h,
                  qo_stride_t, qo_stride_h, ko_stride_t, ko_stride_h, tokens, hq, hk, dim};
   cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = dtype != DLB_DTYPE_F32 && (dim / 2) % 8 == 0 &&
+                   ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)cos |
+                      (uintptr_t)sin) & 15) == 0) &&
+                   q_stride_t % 8 == 0 && q_stride_h % 8 == 0 && k_stride_t % 8 == 0 && k_stride_h % 8 == 0 &&
+                   qo_stride_t % 8 == 0 && qo_stride_h % 8 == 0 && ko_stride_t % 8 == 0 && ko_stride_h % 8 == 0;
+  if (vec) {
+    const int work = (hq + hk) * (dim / 16);
+    const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
+    if (dtype == DLB_DTYPE_BF16) rotary_vec_kernel<__nv_bfloat16><<<(unsigned)tokens, threads, 0, s>>>(p);
+    else rotary_vec_kernel<__half><<<(unsigned)tokens, threads, 0, s>>>(p);
+    DLB_CUDA_LAUNCH_CHECK();
+    return DLB_OK;
+  }
   const int work = (hq + hk) * (dim / 2);
   const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
   switch (dtype) {
@@ -367,7 +438,7 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
   for (int64_t v : {dim_k, dim_v, ks_stride_t, ks_stride_h, vs_stride_t, vs_stride_h, kc_stride_page, kc_stride_slot,
                     kc_stride_head, vc_stride_page, vc_stride_slot, vc_stride_head})
     ok16 = ok16 && mult(v, 16);
-  dim3 grid((unsigned)batch, (unsigned)blocks);
+  dim3 grid((unsigned)batch, (unsigned)blocks, 4);
   cudaStream_t s = (cudaStream_t)stream;
   if (ok16) fill_kv_cache_kernel<16><<<grid, 256, 0, s>>>(p);
   else if (elem_size == 4) fill_kv_cache_kernel<4><<<grid, 256, 0, s>>>(p);
