@@ -33,7 +33,17 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch of the grouped GEMM kernel from the committed ncu capture
 # (profiles/grouped_gemm_*.md); None until a capture exists for the benchmark shape.
-NCU_TRAFFIC = {"grouped_gemm": None, "silu_and_mul": None, "paged_decode": None}
+NCU_TRAFFIC = {
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark shapes, from the one-pass
+    # ncu capture summarised in profiles/dram_traffic_full_size.md
+    "grouped_gemm": {"gate_up_silu": 2968.7e6, "down_scatter": 1468.0e6, "per_step": 4436.7e6},
+    "silu_and_mul": 229.0e6,
+    "flash_prefill": 2126.8e6,
+    "paged_decode": 4430.5e6,
+    "rms_norm": 480.8e6,
+    "apply_rotary_pos_emb": 629.3e6,
+    "fill_kv_cache": 221.9e6,
+}
 
 
 def load_peaks():
@@ -203,7 +213,8 @@ def bench_prefill(dev, peaks, steps, warmup):
     return {"workload": "C4 varlen causal GQA prefill bf16 B=4 S=8192 Hq=32 Hkv=8 D=128", "ms": ms, "value": tf,
             "unit": "TFLOP/s",
             "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": tf / peaks["bf16_tflops_sustained"], "traffic": None, "basis": peaks["basis"]},
+                         "frac": tf / peaks["bf16_tflops_sustained"], "traffic": NCU_TRAFFIC["flash_prefill"],
+                         "basis": peaks["basis"]},
             "l2": "q/k/v/o 670 MB > L2", "gpu_launches": steps}
 
 
@@ -255,6 +266,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     ms = time_steps(lambda: dl.rms_norm(x, w, 1e-6, residual=r, out=o, out_residual=o_r), steps, warmup)
     out["rms_norm"] = _hbm_entry("rms_norm + residual bf16 [16384, 4096]", 4 * T * H * 2 + H * 2, ms, peaks, steps,
                                  "537 MB per pass > L2")
+    out["rms_norm"]["roofline"]["traffic"] = NCU_TRAFFIC["rms_norm"]
     del x, r, o, o_r
     # rotary embedding in place on the prefill configuration's q and k
     tok, hq, hk, d = 32768, 32, 8, 128
@@ -266,6 +278,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     out["apply_rotary_pos_emb"] = _hbm_entry("rotary in place, q [32768, 32, 128] k [32768, 8, 128] bf16",
                                              2 * (q.numel() + k.numel()) * 2 + 2 * cos.numel() * 2, ms, peaks, steps,
                                              "688 MB per pass > L2")
+    out["apply_rotary_pos_emb"]["roofline"]["traffic"] = NCU_TRAFFIC["apply_rotary_pos_emb"]
     # fill_kv_cache: the prefill configuration's 4 x 8192 new tokens into 64-token pages
     B, S, page = 4, 8192, 64
     pages = B * S // page
@@ -278,6 +291,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     ms = time_steps(lambda: dl.fill_kv_cache(k, v_states, kc, vc, start, qlen, qlen, S, table), steps, warmup)
     out["fill_kv_cache"] = _hbm_entry("fill_kv_cache 4 x 8192 tokens, 8 heads x 128, page 64, bf16",
                                       4 * k.numel() * 2, ms, peaks, steps, "268 MB per pass > L2")
+    out["fill_kv_cache"]["roofline"]["traffic"] = NCU_TRAFFIC["fill_kv_cache"]
     del q, k, v_states, kc, vc, cos, sin
     # token-granular decode (page size 1): 16 requests of the decode configuration
     wl = W.DecodeWorkload(batch=16, page=1)
@@ -571,7 +585,7 @@ def main():
                     help="N > 1: token exchange by our peer-memory kernels (default) or by NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--cpu-sample", type=int, default=4096)
-    ap.add_argument("--warm-seconds", type=float, default=0.3,
+    ap.add_argument("--warm-seconds", type=float, default=1.0,
                     help="N = 1: keep warming up until this much wall time has passed (device under load)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
