@@ -524,7 +524,8 @@ def run_ours(args):
                                "gate/up GEMM+silu -> down GEMM x weight -> combine)",
                    "parallelism": parallelism, "l2": "expert weights 2.8 GB per pass > 126 MB L2"},
         "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (2 launches per step)", "achieved": gemm_tf,
-                     "peak": peak, "unit": "TFLOP/s", "frac": gemm_tf / peak, "traffic": NCU_TRAFFIC["grouped_gemm"],
+                     "peak": peak, "unit": "TFLOP/s", "frac": gemm_tf / peak, "traffic": NCU_TRAFFIC["grouped_gemm"]["per_step"] / 2,
+                     "traffic_by_launch": NCU_TRAFFIC["grouped_gemm"],
                      "basis": f"{peaks['basis']} sustained cuBLAS bf16", "ms_per_step_in_kernel": gemm_ms},
         "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e},
