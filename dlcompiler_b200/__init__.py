@@ -17,9 +17,10 @@ from .kernels.fused_moe import fused_moe, fused_moe_kernel_launcher, get_start_e
 from .kernels.moe_gating import grouped_topk_gating, softmax_topk
 from .kernels.paged_attention import paged_attention_fwd
 from .kernels.prefill_attention import context_attention_fwd
+from .kernels.topk_gating import topk_gating
 
 __all__ = [
     "DlblasError", "check_device_status", "is_built", "silu_and_mul", "fused_moe", "fused_moe_kernel_launcher",
     "get_start_end", "moe_align_block_size", "grouped_topk_gating", "softmax_topk", "paged_attention_fwd",
-    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2", "apply_rotary_pos_emb", "fill_kv_cache", "rms_norm", "add_rms_norm",
+    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2", "apply_rotary_pos_emb", "fill_kv_cache", "rms_norm", "add_rms_norm", "topk_gating",
 ]

@@ -31,6 +31,7 @@ struct GatingParams {
   const float* bias;     // [E] or null
   int32_t* ids;          // [T, K]
   float* weights;        // [T, K]
+  float* probs;          // optional [T, E] output of the un-biased scores (softmax probabilities / sigmoid)
   int64_t tokens;
   int64_t ld;
   int experts;
@@ -131,6 +132,11 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? s[v] / sum : -CUDART_INF_F;
   }
+  if (p.probs != nullptr) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+      if (e0 + v < E) p.probs[token * E + e0 + v] = s[v];
+  }
   if (p.scoring == DLB_SCORE_SIGMOID || p.bias != nullptr) {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
@@ -226,6 +232,156 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   }
 }
 
+// Launch the one-warp-per-token router for prepared parameters.
+static int launch_gating(const GatingParams& p, void* stream) {
+  int vpl = 1;
+  while (vpl * 32 < p.experts) vpl <<= 1;
+  const int warps = 8;
+  const int64_t blocks = (p.tokens + warps - 1) / warps;
+  DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gating: too many tokens");
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (vpl) {
+    case 1: grouped_topk_kernel<1><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 2: grouped_topk_kernel<2><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 4: grouped_topk_kernel<4><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 8: grouped_topk_kernel<8><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    default: grouped_topk_kernel<16><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+  }
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+// ----------------------------------------------------------------------------
+// GShard-style top-k gating with capacity (the reference's `topk_gating` family,
+// python/dlBLAS/dlblas/kernels/topk_gating.py:259-290 and topk_gating_fwd_part1/2/3.py;
+// torch statement in python/dlBLAS/benchmarks/topk_gating.py:132-206).
+//   gates = softmax(logits); the k choices of every token queue up per expert in
+//   (choice-major, token) order; a choice is kept if its queue position is below the
+//   capacity; weights = kept gate values normalised over the token's kept choices.
+// Queue positions come from the stable counting sort of moe_align (block 1) over the
+// choice-major id list, so no [k, S, E] mask tensors are materialised.
+// ----------------------------------------------------------------------------
+// Deterministic column sums of gates [S, E]: stage 1 reduces row chunks, stage 2 the partials.
+__global__ void __launch_bounds__(256) gshard_colsum_stage1(const float* __restrict__ gates, float* __restrict__ part,
+                                                            int64_t S, int E, int rows_per_block) {
+  const int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t r1 = min(S, r0 + rows_per_block);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float acc = 0.f;
+    for (int64_t r = r0; r < r1; ++r) acc += gates[r * E + e];
+    part[(int64_t)blockIdx.x * E + e] = acc;
+  }
+}
+// me[e] = sum / S;  ce[e] = first-choice count / S;  l_aux = mean(me * ce) * E * E
+__global__ void __launch_bounds__(256) gshard_aux_kernel(const float* __restrict__ part, int nblk,
+                                                         const int32_t* __restrict__ ids_km /* [K*S] */,
+                                                         int64_t S, int E, float* __restrict__ me,
+                                                         float* __restrict__ ce, float* __restrict__ l_aux) {
+  extern __shared__ float sh[];   // [E] first-choice counts, then reduction scratch
+  float* cnt = sh;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0.f;
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&cnt[ids_km[i]], 1.0f);   // integers: exact
+  __syncthreads();
+  float local = 0.f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float acc = 0.f;
+    for (int b = 0; b < nblk; ++b) acc += part[(int64_t)b * E + e];
+    const float m = acc / (float)S, c = cnt[e] / (float)S;
+    me[e] = m;
+    ce[e] = c;
+    local += m * c;
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    l_aux[0] = t / (float)E * (float)E * (float)E;
+  }
+}
+// Queue position of every (choice, token) slot and the per-expert token lists.
+__global__ void __launch_bounds__(256) gshard_queue_kernel(const int32_t* __restrict__ sorted_slots,
+                                                           const int32_t* __restrict__ prefix,
+                                                           const int32_t* __restrict__ ids_km,
+                                                           int32_t* __restrict__ loc, int64_t* __restrict__ select,
+                                                           int64_t KS, int64_t S, int E, int capacity) {
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < KS; p += (int64_t)gridDim.x * blockDim.x) {
+    const int slot = sorted_slots[p];
+    const int e = ids_km[slot];
+    const int l = (int)p - prefix[e];
+    loc[slot] = l;
+    if (l < capacity) select[(int64_t)e * capacity + l] = slot % S;   // token of the l-th kept choice
+  }
+}
+// Capacity slots no choice filled are given the lowest-numbered tokens that did not choose the expert
+// within capacity; they carry no weight (the reference fills them with arbitrary zero-valued tokens).
+__global__ void __launch_bounds__(256) gshard_fill_kernel(const int32_t* __restrict__ prefix,
+                                                          int64_t* __restrict__ select, int E, int capacity,
+                                                          int64_t S) {
+  const int e = blockIdx.x;
+  const int kept = min(prefix[e + 1] - prefix[e], capacity);
+  // the kept tokens of this expert, as a bitmap in shared memory
+  extern __shared__ uint32_t bits[];
+  const int words = (int)((S + 31) / 32);
+  for (int w = threadIdx.x; w < words; w += blockDim.x) bits[w] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < kept; i += blockDim.x) {
+    const int64_t t = select[(int64_t)e * capacity + i];
+    atomicOr(&bits[t >> 5], 1u << (t & 31));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int out = kept;
+    for (int64_t t = 0; t < S && out < capacity; ++t)
+      if (!((bits[t >> 5] >> (t & 31)) & 1u)) select[(int64_t)e * capacity + out++] = t;
+  }
+}
+// Per token: drop choices beyond capacity, normalise the kept gate values, emit e * capacity + position.
+__global__ void __launch_bounds__(256) gshard_assign_kernel(const float* __restrict__ gates,
+                                                            const int32_t* __restrict__ ids_km,
+                                                            const int32_t* __restrict__ loc,
+                                                            int32_t* __restrict__ ec_idx, float* __restrict__ weights,
+                                                            int64_t S, int E, int K, int capacity, float eps) {
+  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  float denom = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int e = ids_km[k * S + s];
+    if (loc[k * S + s] < capacity) denom += gates[s * E + e];
+  }
+  denom = fmaxf(denom, eps);
+  for (int k = 0; k < K; ++k) {
+    const int e = ids_km[k * S + s];
+    const int l = loc[k * S + s];
+    const bool kept = l < capacity;
+    const float g = kept ? gates[s * E + e] : 0.f;
+    weights[k * S + s] = g / denom;
+    ec_idx[k * S + s] = kept && g > 0.f ? e * capacity + l : (kept ? l : 0);
+  }
+}
+// grad_logits[s, i] = g_i * (gg_i - sum_j g_j gg_j),  gg_e = grad_l_aux * ce[e] * E / S
+// (python/dlBLAS/dlblas/kernels/topk_gating_bwd.py:20-66)
+__global__ void __launch_bounds__(256) gshard_bwd_kernel(const float* __restrict__ gates, const float* __restrict__ ce,
+                                                         const float* __restrict__ grad_l_aux,
+                                                         float* __restrict__ grad_logits, int64_t S, int E) {
+  const int lane = threadIdx.x & 31;
+  const int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (s >= S) return;
+  const float scale = grad_l_aux[0] * (float)E / (float)S;
+  float dot = 0.f;
+  for (int e = lane; e < E; e += 32) dot += gates[s * E + e] * (ce[e] * scale);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  for (int e = lane; e < E; e += 32) {
+    const float g = gates[s * E + e];
+    grad_logits[s * E + e] = g * (ce[e] * scale - dot);
+  }
+}
+
 }  // namespace dlb
 
 extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, int32_t* ids, float* weights,
@@ -262,19 +418,82 @@ extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, i
     DLB_CHECK_ARG(((uintptr_t)logits & 15) == 0 && (logits_row_stride % 4) == 0, DLB_ERR_ALIGNMENT,
                   "gating: logits rows must be 16-byte aligned");
   }
-  GatingParams p{logits, bias, ids, weights, tokens, logits_row_stride, experts, n_group,
+  GatingParams p{logits, bias, ids, weights, nullptr, tokens, logits_row_stride, experts, n_group,
                  topk_group, top_k, scoring, renormalize, scale};
-  const int warps = 8;
-  const int64_t blocks = (tokens + warps - 1) / warps;
-  DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gating: too many tokens");
+  return launch_gating(p, stream);
+}
+
+
+extern "C" int dlb_gshard_gate(const float* logits, int64_t tokens, int experts, int top_k, float* gates,
+                               int32_t* ids /* [tokens, top_k] */, float* scratch_weights, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0 && experts >= 1 && experts <= 512 && top_k >= 1 && top_k <= 32 && top_k <= experts,
+                DLB_ERR_BAD_ARG, "gshard_gate: bad sizes");
+  if (tokens == 0) return DLB_OK;
+  DLB_CHECK_ARG(logits && gates && ids && scratch_weights, DLB_ERR_BAD_ARG, "gshard_gate: null pointer");
+  int vpl = 1;
+  while (vpl * 32 < experts) vpl <<= 1;
+  if (vpl >= 4)
+    DLB_CHECK_ARG(((uintptr_t)logits & 15) == 0 && experts % 4 == 0, DLB_ERR_ALIGNMENT,
+                  "gshard_gate: logits rows must be 16-byte aligned");
+  GatingParams p{logits, nullptr, ids, scratch_weights, gates, tokens, experts, experts, 1, 1, top_k,
+                 DLB_SCORE_SOFTMAX, 0, 1.0f};
+  return launch_gating(p, stream);
+}
+
+extern "C" int dlb_gshard_assign(const float* gates, const int32_t* ids_choice_major, const int32_t* sorted_slots,
+                                 const int32_t* expert_prefix, int64_t tokens, int experts, int top_k,
+                                 int64_t capacity, float* colsum_scratch, int64_t colsum_blocks, int32_t* loc,
+                                 float* me, float* ce, float* l_aux, int32_t* ec_idx, float* weights,
+                                 int64_t* expert_select_token_idx, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 1 && experts >= 1 && experts <= 1024 && top_k >= 1 && capacity >= 1 && colsum_blocks >= 1,
+                DLB_ERR_BAD_ARG, "gshard_assign: bad sizes");
+  DLB_CHECK_ARG(tokens * top_k < (1LL << 31) && (int64_t)experts * capacity < (1LL << 31), DLB_ERR_TOO_LARGE,
+                "gshard_assign: problem too large");
+  DLB_CHECK_ARG(gates && ids_choice_major && sorted_slots && expert_prefix && colsum_scratch && loc && me && ce &&
+                    l_aux && ec_idx && weights && expert_select_token_idx,
+                DLB_ERR_BAD_ARG, "gshard_assign: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  switch (vpl) {
-    case 1: grouped_topk_kernel<1><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 2: grouped_topk_kernel<2><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 4: grouped_topk_kernel<4><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 8: grouped_topk_kernel<8><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    default: grouped_topk_kernel<16><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+  const int rows_per_block = (int)((tokens + colsum_blocks - 1) / colsum_blocks);
+  gshard_colsum_stage1<<<(unsigned)colsum_blocks, 256, 0, s>>>(gates, colsum_scratch, tokens, experts, rows_per_block);
+  DLB_CUDA_LAUNCH_CHECK();
+  gshard_aux_kernel<<<1, 256, experts * sizeof(float), s>>>(colsum_scratch, (int)colsum_blocks, ids_choice_major,
+                                                            tokens, experts, me, ce, l_aux);
+  DLB_CUDA_LAUNCH_CHECK();
+  const int64_t KS = tokens * top_k;
+  int64_t blocks = (KS + 255) / 256;
+  if (blocks > 4096) blocks = 4096;
+  gshard_queue_kernel<<<(unsigned)blocks, 256, 0, s>>>(sorted_slots, expert_prefix, ids_choice_major, loc,
+                                                       expert_select_token_idx, KS, tokens, experts, (int)capacity);
+  DLB_CUDA_LAUNCH_CHECK();
+  const size_t bitmap = (size_t)((tokens + 31) / 32) * 4;
+  DLB_CHECK_ARG(bitmap <= 200 * 1024, DLB_ERR_TOO_LARGE, "gshard_assign: more than 1.6M tokens");
+  cudaError_t e = cudaFuncSetAttribute(gshard_fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bitmap);
+  if (e != cudaSuccess) {
+    set_last_error("gshard_assign: smem attribute: %s", cudaGetErrorString(e));
+    return (int)e;
   }
+  gshard_fill_kernel<<<(unsigned)experts, 256, bitmap, s>>>(expert_prefix, expert_select_token_idx, experts,
+                                                            (int)capacity, tokens);
+  DLB_CUDA_LAUNCH_CHECK();
+  gshard_assign_kernel<<<(unsigned)((tokens + 255) / 256), 256, 0, s>>>(gates, ids_choice_major, loc, ec_idx, weights,
+                                                                        tokens, experts, top_k, (int)capacity,
+                                                                        1.1920928955078125e-07f);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_gshard_gate_bwd(const float* gates, const float* ce, const float* grad_l_aux, float* grad_logits,
+                                   int64_t tokens, int experts, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0 && experts >= 1, DLB_ERR_BAD_ARG, "gshard_gate_bwd: bad sizes");
+  if (tokens == 0) return DLB_OK;
+  DLB_CHECK_ARG(gates && ce && grad_l_aux && grad_logits, DLB_ERR_BAD_ARG, "gshard_gate_bwd: null pointer");
+  const int64_t blocks = (tokens + 7) / 8;
+  DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gshard_gate_bwd: too many tokens");
+  gshard_bwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(gates, ce, grad_l_aux, grad_logits, tokens,
+                                                                        experts);
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }

@@ -56,6 +56,30 @@ int dlb_grouped_topk_gating(const float* logits, const float* bias, int32_t* ids
                             int experts, int64_t logits_row_stride, int n_group, int topk_group, int top_k,
                             int scoring, int renormalize, float scale, void* stream);
 
+/* GShard-style top-k gating with capacity (forward + backward of the auxiliary loss), the reference's
+ * `topk_gating` op: python/dlBLAS/dlblas/kernels/topk_gating.py:259-290 (autograd function),
+ * topk_gating_fwd_part1.py:24-81, topk_gating_fwd_part2.py:11-66, topk_gating_fwd_part3.py:11-62,135-169,
+ * topk_gating_bwd.py:20-85; torch statement python/dlBLAS/benchmarks/topk_gating.py:132-206.
+ *   dlb_gshard_gate     gates = softmax(logits) [tokens, experts] fp32 and the k largest experts per token
+ *                       (ids [tokens, top_k], descending, ties to the lower index).
+ *   dlb_gshard_assign   from the choice-major id list [top_k * tokens] and its stable sort by expert
+ *                       (dlb_moe_align_block_size with block 1): queue position of every choice (loc),
+ *                       me / ce / l_aux = mean(me * ce) * E^2, kept choices (position < capacity),
+ *                       weights = kept gate / max(sum of the token's kept gates, fp32 eps),
+ *                       ec_idx = expert * capacity + position (0 when dropped),
+ *                       expert_select_token_idx [experts * capacity] int64 = tokens of each expert's queue
+ *                       in arrival order, unfilled capacity padded with unrelated zero-weight tokens.
+ *                       colsum_scratch: fp32 [colsum_blocks * experts].
+ *   dlb_gshard_gate_bwd grad_logits = softmax backward of grad_l_aux * ce * E / tokens. */
+int dlb_gshard_gate(const float* logits, int64_t tokens, int experts, int top_k, float* gates, int32_t* ids,
+                    float* scratch_weights, void* stream);
+int dlb_gshard_assign(const float* gates, const int32_t* ids_choice_major, const int32_t* sorted_slots,
+                      const int32_t* expert_prefix, int64_t tokens, int experts, int top_k, int64_t capacity,
+                      float* colsum_scratch, int64_t colsum_blocks, int32_t* loc, float* me, float* ce, float* l_aux,
+                      int32_t* ec_idx, float* weights, int64_t* expert_select_token_idx, void* stream);
+int dlb_gshard_gate_bwd(const float* gates, const float* ce, const float* grad_l_aux, float* grad_logits,
+                        int64_t tokens, int experts, void* stream);
+
 /* moe_align_block_size: stable counting sort of the numel (token, k) slots by expert id, each expert
  * segment padded to a multiple of `block` with the sentinel `numel`.  Block-padded form of the
  * reference's argsort + [start, end) ranges

@@ -414,3 +414,58 @@ def fill_kv_cache(k_states, v_states, k_caches, v_caches, seq_lens, history_lens
             vc[pg, pos % page] = v_states[start + i]
         start += n
     return kc, vc
+
+
+# --------------------------------------------------------------------------------------
+# GShard-style top-k gating with capacity (the reference's `topk_gating` op)
+# --------------------------------------------------------------------------------------
+def topk_gating(logits, k, capacity_factor=1.0, min_capacity=2):
+    """Restatement of python/dlBLAS/benchmarks/topk_gating.py:132-206 (`fused_topkgating_opt`, the torch
+    reference the dlBLAS benchmark checks its kernels against), with the two points that code leaves to
+    `torch.topk`'s unspecified tie order made explicit: equal gate values go to the lower expert index,
+    and `expert_select_token_idx` lists each expert's kept tokens in queue order (choice-major, then
+    token), padding unfilled capacity with the lowest-numbered tokens that were not kept.
+    Returns (l_aux, token_rearranged_ec_idx int32 [k*s], token_exp_weights [k*s],
+    expert_select_token_idx int64 [e*c], priority [s, e]) -- `priority` (k - choice for kept choices, else 0)
+    is what the reference feeds to torch.topk and lets tests compare selections up to ties."""
+    x = logits.float()
+    S, E = x.shape
+    gates = F.softmax(x, dim=1)
+    capacity = int(torch.ceil((S / E) * torch.tensor(capacity_factor * k)).to(torch.int64))
+    capacity = max(capacity, int(min_capacity))
+    _, idx = _stable_topk(x, k)                                   # softmax is monotone: rank on the logits
+    idx_km = idx.t().reshape(-1)                                  # [k*s], choice-major
+    masks = F.one_hot(idx_km, num_classes=E)
+    locations = torch.cumsum(masks, dim=0) - 1
+    masks = masks.reshape(k, S, E)
+    locations = locations.reshape(k, S, E)
+    me = gates.mean(dim=0)
+    ce = masks[0].float().mean(dim=0)
+    l_aux = torch.mean(me * ce) * E * E
+    masks = masks * torch.lt(locations, capacity)
+    locations_s = torch.sum(locations * masks, dim=2)
+    gate_s, indices_s = torch.max(gates * masks.float(), dim=2)
+    indices_s = torch.where(gate_s > 0, indices_s, torch.zeros_like(indices_s))
+    denom = torch.clamp(gate_s.sum(dim=0), min=torch.finfo(torch.float32).eps)
+    gate_s = gate_s / denom
+    ec_idx = (indices_s.int() * capacity + locations_s.int()).reshape(-1)
+    priority = (masks * torch.arange(k, 0, -1).reshape(k, 1, 1)).sum(dim=0)          # [s, e]
+    select = torch.zeros(E, capacity, dtype=torch.int64)
+    for e in range(E):
+        order = torch.nonzero(idx_km == e).flatten()[:capacity] % S                  # queue order
+        kept = order.tolist()
+        fill = [t for t in range(S) if t not in set(kept)][:capacity - len(kept)]
+        select[e] = torch.tensor(kept + fill, dtype=torch.int64)
+    return l_aux, ec_idx, gate_s.reshape(-1), select.reshape(-1), priority
+
+
+def topk_gating_backward(logits, k, grad_l_aux=1.0):
+    """d l_aux / d logits by autograd through the same expression (me depends on the logits, ce does not)."""
+    x = logits.float().clone().requires_grad_(True)
+    S, E = x.shape
+    gates = F.softmax(x, dim=1)
+    _, idx = _stable_topk(x.detach(), k)
+    ce = F.one_hot(idx[:, 0], num_classes=E).float().mean(dim=0)
+    l_aux = torch.mean(gates.mean(dim=0) * ce) * E * E
+    l_aux.backward(torch.tensor(grad_l_aux))
+    return x.grad

@@ -36,7 +36,7 @@ class _StripCuda(ast.NodeTransformer):
         return node
 
 
-def load_functions(path: str, names: list[str]) -> dict:
+def load_functions(path: str, names: list[str], extra_ns: dict | None = None) -> dict:
     """Compile the named functions (`func` or `Class.method`) of a reference file in memory."""
     tree = ast.parse(open(path).read())
     found = {}
@@ -52,6 +52,7 @@ def load_functions(path: str, names: list[str]) -> dict:
     if missing:
         raise RuntimeError(f"{path}: cannot find {missing}")
     ns = {"torch": torch, "math": math, "F": F}
+    ns.update(extra_ns or {})
     out = {}
     for key, node in found.items():
         node.decorator_list = []
@@ -226,6 +227,27 @@ def main():
         cases.append({"k_states": ks, "v_states": vs, "k_caches": kc, "v_caches": vc, "seq_lens": list(seq_lens),
                       "history_lens": list(hist), "block_offsets": table, "gt_k": gk, "gt_v": gv})
     torch.save(cases, os.path.join(HERE, "fill_kv_cache.pt"))
+
+    # ---------------------------------------------------------------- GShard top-k gating with capacity
+    from collections import namedtuple
+    from typing import Tuple
+
+    info = namedtuple("GatingTokenRearrangeInfo",
+                      ["token_rearranged_ec_idx", "token_exp_weights", "expert_select_token_idx"])
+    bench_file = os.path.join(args.reference, "python/dlBLAS/benchmarks/topk_gating.py")
+    fns = load_functions(bench_file, ["_capacity", "fused_topkgating_opt"],
+                         {"Tensor": torch.Tensor, "Tuple": Tuple, "TUTEL_INSTALLED": False,
+                          "GatingTokenRearrangeInfo": info})
+    cases = []
+    for i, (S, E, k, cf, mc) in enumerate([(256, 8, 2, 1.0, 2), (512, 64, 8, 1.0, 2), (128, 16, 4, 0.5, 4),
+                                           (64, 32, 2, 2.0, 2)]):
+        g = torch.Generator().manual_seed(7000 + i)
+        logits = torch.randn(S, E, generator=g)
+        l_aux, rearr = fns["fused_topkgating_opt"](logits, k, cf, mc)
+        cases.append({"logits": logits, "k": k, "capacity_factor": cf, "min_capacity": mc, "l_aux": l_aux,
+                      "ec_idx": rearr.token_rearranged_ec_idx, "weights": rearr.token_exp_weights,
+                      "select": rearr.expert_select_token_idx})
+    torch.save(cases, os.path.join(HERE, "topk_gating.pt"))
 
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".pt"):

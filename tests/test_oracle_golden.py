@@ -96,3 +96,22 @@ def test_fill_kv_cache_ground_truth(golden_dir):
         kc, vc = oracle.fill_kv_cache(c["k_states"], c["v_states"], c["k_caches"], c["v_caches"], c["seq_lens"],
                                       c["history_lens"], c["block_offsets"])
         assert torch.equal(kc, c["gt_k"]) and torch.equal(vc, c["gt_v"])
+
+
+def _selection_priorities(select, priority, E):
+    """Priority of every selected (expert, token) pair, sorted per expert: equal for any valid tie order."""
+    cap = select.numel() // E
+    sel = select.view(E, cap)
+    return torch.stack([priority[sel[e], e].sort(descending=True)[0] for e in range(E)])
+
+
+def test_gshard_topk_gating_ground_truth(golden_dir):
+    for c in _load(golden_dir, "topk_gating.pt"):
+        E = c["logits"].size(1)
+        l_aux, ec, w, sel, prio = oracle.topk_gating(c["logits"], c["k"], c["capacity_factor"], c["min_capacity"])
+        torch.testing.assert_close(l_aux, c["l_aux"], rtol=1e-6, atol=1e-7)
+        assert torch.equal(ec, c["ec_idx"])
+        torch.testing.assert_close(w, c["weights"], rtol=1e-6, atol=1e-8)
+        assert sel.shape == c["select"].shape
+        # torch.topk leaves the order among equal priorities open: compare what was selected, not where
+        assert torch.equal(_selection_priorities(sel, prio, E), _selection_priorities(c["select"], prio, E))
