@@ -9,15 +9,16 @@
 //
 // One CTA = one (sequence, q-head, 128-query tile); two CTAs are resident per
 // SM (256 TMEM columns and ~113 KiB of shared memory each), so one CTA's
-// softmax overlaps the other's MMAs.  Inside a CTA, 192 threads:
-//   warp 0     TMA producer: Q tile once, then K and V tiles of 64 keys into
+// softmax overlaps the other's MMAs.  Inside a CTA, 192 threads (168 registers each; moving registers
+// to the softmax warps with setmaxnreg was tried: ptxas keeps allocating under the launch bound and spills):
+//   warp 4     TMA producer: Q tile once, then K and V tiles of 64 keys into
 //              2-stage rings (3-D tensor maps over [token, head, d], 128-byte swizzle)
-//   warp 1     one lane issues tcgen05.mma: S_j = Q K_j^T (M128 N64 K16 x 8) into
+//   warp 5     one lane issues tcgen05.mma: S_j = Q K_j^T (M128 N64 K16 x 8) into
 //              a double-buffered TMEM S, then O += P_{j-1} V_{j-1}
 //              (M128 N128 K16 x 4, V as an MN-major operand straight from the
 //              row-major tile), software-pipelined so S_j is computed while
 //              the softmax of block j-1 runs
-//   warps 2-5  softmax: one thread per query row reads its S row from TMEM
+//   warps 0-3  softmax: one thread per query row reads its S row from TMEM
 //              (tcgen05.ld), online softmax in the base-2 domain, writes P
 //              (16-bit, swizzled K-major) to shared memory for the next MMA,
 //              rescales O in TMEM only when the row max grew by more than
@@ -33,7 +34,9 @@ namespace dlb {
 namespace fp {
 constexpr int BM = 128;           // query rows per CTA
 constexpr int BN = 64;            // keys per block
-constexpr int THREADS = 192;
+constexpr int THREADS = 192;      // warps 0-3 softmax (TMEM quadrant = warp id), warp 4 TMA, warp 5 MMA
+constexpr int WARP_TMA = 4;
+constexpr int WARP_MMA = 5;
 constexpr int Q_BOX = BM * 128;   // one 64-wide (128 B) column box of the Q tile
 constexpr int KV_BOX = BN * 128;  // one 64-wide column box of a K or V tile
 constexpr int P_BYTES = BM * BN * 2;           // 16 KiB
@@ -224,7 +227,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == WARP_MMA) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -234,7 +237,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;
 
-  if (warp == 0) {
+  if (warp == WARP_TMA) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -259,7 +262,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[s], bx * 64, kvh, row);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 23, 0);
@@ -303,9 +306,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------ softmax / correction / epilogue ------------------------------
-    const int quad = warp & 3;
+    const int quad = warp;
     const int row = quad * 32 + lane;              // query row inside the tile == TMEM lane
     const int q_pos = q0 + row;                    // position inside the sequence
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
@@ -365,53 +368,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         m_ref = mx;
         rescale = true;
       }
-      // p = 2^(s * scale - m): one packed FMA per two scores, exponentials on the SFU,
-      // packed adds for the row sum, one conversion per pair
-      uint32_t pk[32];
-      const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
-      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
-      const uint64_t negm2 = pack_f2(neg_m, neg_m);
-      uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-#pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const uint64_t a01 =
-              fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2);
-          const uint64_t a23 =
-              fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2);
-          float e0, e1, e2, e3;
-          // groups of four scores selected by POLY_EXP2_GROUPS take the polynomial path, the rest the SFU
-          const int grp = ((h * 32 + c) >> 2) & 7;
-          if (((POLY_EXP2_GROUPS >> grp) & 1) != 0) {
-            exp2_poly2(a01, e0, e1);
-            exp2_poly2(a23, e2, e3);
-          } else {
-            float x0, x1, x2, x3;
-            unpack_f2(a01, x0, x1);
-            unpack_f2(a23, x2, x3);
-            e0 = fast_exp2(x0);
-            e1 = fast_exp2(x1);
-            e2 = fast_exp2(x2);
-            e3 = fast_exp2(x3);
-          }
-          sum2a = add_f2(sum2a, pack_f2(e0, e1));
-          sum2b = add_f2(sum2b, pack_f2(e2, e3));
-          typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
-          typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
-          pk[h * 16 + c / 2] = *reinterpret_cast<uint32_t*>(&v01);
-          pk[h * 16 + c / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
-        }
-      }
-      float psum;
-      {
-        float a, b;
-        unpack_f2(add_f2(sum2a, sum2b), a, b);
-        psum = a + b;
-      }
-      l_sum = l_sum * alpha + psum;
-
-      // P buffer and O are free once P_{j-1} V_{j-1} has retired
+      // P buffer and O are free once P_{j-1} V_{j-1} has retired (normally long before this point)
       if (j > 0) {
         ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 29, j);
         ok = __all_sync(0xffffffffu, ok);
@@ -430,11 +387,54 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           tmem_wait_st();
         }
       }
-      // write P row (64 x 16 bit = 128 B) in the swizzled K-major layout
+      // p = 2^(s * scale - m): one packed FMA per two scores, exponentials on the SFU, packed adds for
+      // the row sum, one conversion per pair; every 8 values go straight to their swizzled 16-byte
+      // chunk of the K-major P tile, so few packed values stay live
+      const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
+      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
+      const uint64_t negm2 = pack_f2(neg_m, neg_m);
+      uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int u = 0; u < 8; u += 4) {
+            const uint64_t a01 = fma_f2(
+                pack_f2(__uint_as_float(sr[h][c + u]), __uint_as_float(sr[h][c + u + 1])), scale2, negm2);
+            const uint64_t a23 = fma_f2(
+                pack_f2(__uint_as_float(sr[h][c + u + 2]), __uint_as_float(sr[h][c + u + 3])), scale2, negm2);
+            float e0, e1, e2, e3;
+            // groups of four scores selected by POLY_EXP2_GROUPS take the polynomial path, the rest the SFU
+            const int grp = ((h * 32 + c + u) >> 2) & 7;
+            if (((POLY_EXP2_GROUPS >> grp) & 1) != 0) {
+              exp2_poly2(a01, e0, e1);
+              exp2_poly2(a23, e2, e3);
+            } else {
+              float x0, x1, x2, x3;
+              unpack_f2(a01, x0, x1);
+              unpack_f2(a23, x2, x3);
+              e0 = fast_exp2(x0);
+              e1 = fast_exp2(x1);
+              e2 = fast_exp2(x2);
+              e3 = fast_exp2(x3);
+            }
+            sum2a = add_f2(sum2a, pack_f2(e0, e1));
+            sum2b = add_f2(sum2b, pack_f2(e2, e3));
+            typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
+            typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
+            pk[u / 2] = *reinterpret_cast<uint32_t*>(&v01);
+            pk[u / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
+          }
+          const int chunk = (h * 32 + c) >> 3;
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+      {
+        float a, b;
+        unpack_f2(add_f2(sum2a, sum2b), a, b);
+        l_sum = l_sum * alpha + (a + b);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -476,7 +476,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == WARP_MMA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
