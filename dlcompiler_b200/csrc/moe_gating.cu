@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 
   // ---- top-k: k rounds of warp arg-max (ties -> lower expert index) ----
   // Scores become order-preserving unsigned keys so that one hardware warp reduction
-  // (redux.sync) finds the maximum; a second one picks the lowest expert index among equals.
+  // (redux.sync) finds the maximum; a ballot picks the lowest lane (= lowest expert index) among equals.
   // Each lane caches its local best; only the winning lane rescans after a round.
   uint32_t key[VPL];
 #pragma unroll
@@ -182,11 +182,13 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   }
   uint32_t lbest = 0;
   int lidx = 0;
+  float lbest_s = 0.f;          // un-biased score of the lane's current best
 #pragma unroll
   for (int v = 0; v < VPL; ++v) {
     if (key[v] > lbest) {   // strict: the lower index wins a tie inside the lane
       lbest = key[v];
       lidx = v;
+      lbest_s = s[v];
     }
   }
   float wsum = 0.f;
@@ -194,26 +196,23 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   int my_id = 0;
   for (int k = 0; k < p.top_k; ++k) {
     const uint32_t wmax = __reduce_max_sync(0xffffffffu, lbest);
-    const int cand = (lbest == wmax) ? e0 + lidx : 0x7fffffff;
-    const int best_e = __reduce_min_sync(0xffffffffu, cand);
-    const int owner = best_e / VPL;
-    float ls = 0.f;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v)
-      if (v == lidx) ls = s[v];
-    const float best_s = __shfl_sync(0xffffffffu, ls, owner);
+    // lanes hold ascending expert ranges, so the lowest lane with the maximum holds the lowest index
+    const int owner = __ffs(__ballot_sync(0xffffffffu, lbest == wmax)) - 1;
+    const int best_e = owner * VPL + __shfl_sync(0xffffffffu, lidx, owner);
+    const float best_s = __shfl_sync(0xffffffffu, lbest_s, owner);
     if (lane == owner) {
       // retire the winner and rescan this lane only
-#pragma unroll
-      for (int v = 0; v < VPL; ++v)
-        if (v == lidx) key[v] = 0;
+      const int gone = lidx;
       lbest = 0;
       lidx = 0;
+      lbest_s = 0.f;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
+        if (v == gone) key[v] = 0;
         if (key[v] > lbest) {
           lbest = key[v];
           lidx = v;
+          lbest_s = s[v];
         }
       }
     }
