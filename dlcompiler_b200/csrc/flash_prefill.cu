@@ -39,7 +39,6 @@ constexpr int WARP_TMA = 4;
 constexpr int WARP_MMA = 5;
 constexpr int Q_BOX = BM * 128;   // one 64-wide (128 B) column box of the Q tile
 constexpr int KV_BOX = BN * 128;  // one 64-wide column box of a K or V tile
-constexpr int P_BYTES = BM * BN * 2;           // 16 KiB
 constexpr int KV_STAGES = 2;
 constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
@@ -55,8 +54,7 @@ template <int D> struct Layout {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-  static constexpr int OFF_CTRL = OFF_P + P_BYTES;
+  static constexpr int OFF_CTRL = OFF_V + KV_STAGES * KV_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 128;   // D=128: two CTAs (plus 1 KiB system reserve each) fit one SM
 };
 }  // namespace fp
@@ -169,7 +167,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   using L = Layout<D>;
   constexpr int BOXES = L::BOXES;
   constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
-  constexpr int OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_P = L::OFF_P, OFF_CTRL = L::OFF_CTRL;
+  constexpr int OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_CTRL = L::OFF_CTRL;
   // ---- which tile ----
   // CTA order: (sequence, kv head) groups one after the other; inside a group the heavy (late, causal)
   // tiles first, the q heads of the group adjacent.  The CTAs resident at any time then share the K/V
@@ -203,9 +201,11 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* v_full = bars + 5;     // [2]
   uint64_t* v_empty = bars + 7;    // [2]
   uint64_t* s_full = bars + 9;     // [2]
-  uint64_t* s_empty = bars + 11;   // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* pv_done = bars + 14;
+  // p_full is per S/P buffer: a fast softmax warp may finish block j+1 before a slow one finishes
+  // block j, and its arrival must not count toward block j's phase
+  uint64_t* p_full = bars + 11;    // [2]
+  uint64_t* pv_done = bars + 13;   // one phase per P.V; waited on only before O is rescaled
+  uint64_t* o_done = bars + 14;    // the last P.V retired: O is final
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -220,10 +220,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 128);
     }
-    mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
+    mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -267,14 +267,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 23, 0);
       const uint32_t q_addr = smem_u32(smem + OFF_Q);
-      const uint32_t p_addr = smem_u32(smem + OFF_P);
       for (int j = 0; ok && j <= nb; ++j) {
         if (j < nb) {
           // S_j = Q K_j^T
           const int s = j & 1;
           const uint32_t ph = (j >> 1) & 1;
           if (!mbar_wait(&k_full[s], ph, abort_flag, p.status, 24, j)) { ok = false; break; }
-          if (!mbar_wait(&s_empty[s], ph ^ 1, abort_flag, p.status, 25, j)) { ok = false; break; }
+          // S buffer s also carried P_{j-2}: P_{j-2} V_{j-2} was issued before this MMA and the tensor
+          // pipe runs one thread's MMAs in order, so no barrier is needed before overwriting it
           tc_fence_after_sync();
           const uint32_t k_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
 #pragma unroll
@@ -291,18 +291,19 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           const int jj = j - 1;
           const int s = jj & 1;
           const uint32_t ph = (jj >> 1) & 1;
-          if (!mbar_wait(p_full, jj & 1, abort_flag, p.status, 26, jj)) { ok = false; break; }
+          if (!mbar_wait(&p_full[s], ph, abort_flag, p.status, 26, jj)) { ok = false; break; }
           if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, 27, jj)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t v_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks) {
-            const uint64_t a_desc = make_smem_desc(p_addr + ks * 32, 16, 1024, 2);
+            // A = P_{jj} from TMEM (16-bit pairs in the first 32 columns of S buffer s), 8 columns per K16 step
             const uint64_t b_desc = make_smem_desc(v_addr + ks * 16 * 128, p.v_lbo, p.v_sbo, 2);
-            umma_ss_f16(tmem_o, a_desc, b_desc, p.idesc_pv, (jj | ks) != 0 ? 1u : 0u);
+            umma_ts_f16(tmem_o, tmem_base + s * BN + ks * 8, b_desc, p.idesc_pv, (jj | ks) != 0 ? 1u : 0u);
           }
           umma_commit(pv_done);
           umma_commit(&v_empty[s]);
+          if (jj == nb - 1) umma_commit(o_done);
         }
       }
     }
@@ -314,7 +315,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
     float m_ref = -CUDART_INF_F;                   // reference max used for exponentiation (scaled, log2 domain)
     float l_sum = 0.f;
-    uint8_t* p_row = smem + OFF_P + row * 128;
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
       const int s = j & 1;
@@ -327,9 +327,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_32x32b_x32(tmem_base + lane_field + s * BN, sr[0]);
       tmem_ld_32x32b_x32(tmem_base + lane_field + s * BN + 32, sr[1]);
       tmem_wait_ld();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[s]);
 
       // mask (diagonal / tail blocks only), on the raw scores
       const int key0 = j * BN;
@@ -368,13 +365,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         m_ref = mx;
         rescale = true;
       }
-      // P buffer and O are free once P_{j-1} V_{j-1} has retired (normally long before this point)
-      if (j > 0) {
+      // O may be rescaled only once P_{j-1} V_{j-1} has retired.  (P_{j-2} V_{j-2} retired before S_j was
+      // signalled, so the barrier is never more than one phase behind and the parity wait is exact.)
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
         ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 29, j);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, rescale)) {
+        {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
@@ -388,8 +386,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
       // p = 2^(s * scale - m): one packed FMA per two scores, exponentials on the SFU, packed adds for
-      // the row sum, one conversion per pair; every 8 values go straight to their swizzled 16-byte
-      // chunk of the K-major P tile, so few packed values stay live
+      // the row sum, one conversion per pair; each half row (32 scores -> 16 packed registers) goes
+      // back to TMEM over the first columns of the S buffer it came from, where the P.V MMA reads it
+      // as its A operand
       const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
       const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
       const uint64_t negm2 = pack_f2(neg_m, neg_m);
@@ -397,8 +396,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
 #pragma unroll
+        uint32_t pk[16];
+#pragma unroll
         for (int c = 0; c < 32; c += 8) {
-          uint32_t pk[4];
 #pragma unroll
           for (int u = 0; u < 8; u += 4) {
             const uint64_t a01 = fma_f2(
@@ -424,24 +424,24 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             sum2b = add_f2(sum2b, pack_f2(e2, e3));
             typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
             typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
-            pk[u / 2] = *reinterpret_cast<uint32_t*>(&v01);
-            pk[u / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
+            pk[(c + u) / 2] = *reinterpret_cast<uint32_t*>(&v01);
+            pk[(c + u) / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
           }
-          const int chunk = (h * 32 + c) >> 3;
-          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
+        tmem_st_32x32b_x16(tmem_base + lane_field + s * BN + h * 16, pk);
       }
       {
         float a, b;
         unpack_f2(add_f2(sum2a, sum2b), a, b);
         l_sum = l_sum * alpha + (a + b);
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[s]);
     }
     if (ok) {
-      ok = mbar_wait(pv_done, (nb - 1) & 1, abort_flag, p.status, 30, nb);
+      // not pv_done: without a wait in every block its phase may be two behind here, which a parity cannot tell
+      ok = mbar_wait(o_done, 0, abort_flag, p.status, 30, nb);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {

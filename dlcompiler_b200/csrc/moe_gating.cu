@@ -43,28 +43,66 @@ struct GatingParams {
   float scale;
 };
 
-// sigmoid evaluated by a FIXED sequence of correctly-rounded fp32 operations
-// (no fused multiply-add, no approximate transcendental), so that the CPU checker,
-// which performs the same sequence with IEEE fp32 tensor ops, gets bit-identical
-// scores and therefore bit-identical expert ids even for near-ties:
-//   t = clamp(-x, -87, 88); n = rint(t * log2e); r = (t - n*LN2_HI) - n*LN2_LO
-//   e = (((((r/720 + 1/120) r + 1/24) r + 1/6) r + 1/2) r + 1) r + 1   [Horner]
-//   sigmoid = 1 / (1 + e * 2^n)
+// sigmoid evaluated by a FIXED sequence of correctly-rounded fp32 operations (fused
+// multiply-add, add, sub, an integer add on the exponent field, IEEE reciprocal; no
+// approximate transcendental), so that the CPU checker, which performs the same sequence
+// with an exact fp32 FMA, gets bit-identical scores and therefore bit-identical expert ids
+// even for near-ties:
+//   xc = clamp(x, -87, 86);  z = fma(xc, -log2e, M);  n = z - M          (M = 1.5 * 2^23)
+//   r  = fma(xc, -log2e_lo, fma(xc, -log2e_hi, -n))                        (|r| <= 0.5)
+//   p  = 2^r by a degree-5 Horner scheme of FMAs;  e = p * 2^n (n added to p's exponent bits)
+//   sigmoid = 1 / (1 + e)
 __device__ __forceinline__ float sigmoid_spec(float x) {
-  const float t = fminf(fmaxf(-x, -87.0f), 88.0f);
-  const float n = rintf(__fmul_rn(t, 1.44269502162933349609375f));
-  float r = __fsub_rn(t, __fmul_rn(n, 0.693145751953125f));
-  r = __fsub_rn(r, __fmul_rn(n, 1.428606765330187045037746429443359375e-06f));
-  float p = 1.38888892251998186111450195312e-03f;                 // 1/720
-  p = __fadd_rn(__fmul_rn(p, r), 8.33333376795053482055664062500e-03f);   // 1/120
-  p = __fadd_rn(__fmul_rn(p, r), 4.16666679084300994873046875000e-02f);   // 1/24
-  p = __fadd_rn(__fmul_rn(p, r), 1.66666671633720397949218750000e-01f);   // 1/6
-  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
-  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
-  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
-  const float two_n = __int_as_float(((int)n + 127) << 23);
-  const float e = __fmul_rn(p, two_n);
+  constexpr float kMagic = 12582912.0f;
+  constexpr float kNegLog2eHi = -1.44269502162933349609e+00f;
+  constexpr float kNegLog2eLo = -1.92596303350001107901e-08f;
+  const float xc = fminf(fmaxf(x, -87.0f), 86.0f);
+  const float z = __fmaf_rn(xc, kNegLog2eHi, kMagic);
+  const float n = __fsub_rn(z, kMagic);
+  float r = __fmaf_rn(xc, kNegLog2eHi, -n);
+  r = __fmaf_rn(xc, kNegLog2eLo, r);
+  float p = 1.32874317932873964310e-03f;
+  p = __fmaf_rn(p, r, 9.67150740325450897217e-03f);
+  p = __fmaf_rn(p, r, 5.55065572261810302734e-02f);
+  p = __fmaf_rn(p, r, 2.40222424268722534180e-01f);
+  p = __fmaf_rn(p, r, 6.93147063255310058594e-01f);
+  p = __fmaf_rn(p, r, 1.0f);
+  const float e = __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
   return __frcp_rn(__fadd_rn(1.0f, e));
+}
+
+// Order-preserving map from fp32 to unsigned: a > b  <=>  key(a) > key(b); -inf maps to
+// 0x007fffff, which leaves 0 free as "slot retired".
+__device__ __forceinline__ uint32_t score_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_score(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+constexpr uint32_t KEY_NEG_INF = 0x007fffffu;
+
+// Sorts N keys in registers, descending, with Batcher's odd-even merge network
+// (19 compare-exchanges for N = 8); every index below is a compile-time constant once unrolled.
+template <int N> __device__ __forceinline__ void sort_desc(uint32_t (&k)[N]) {
+#pragma unroll
+  for (int p = 1; p < N; p <<= 1) {
+#pragma unroll
+    for (int q = p; q >= 1; q >>= 1) {
+#pragma unroll
+      for (int j = q % p; j <= N - 1 - q; j += 2 * q) {
+#pragma unroll
+        for (int i = 0; i < q; ++i) {
+          const int lo = i + j, hi = i + j + q;
+          if (hi < N && (lo / (2 * p)) == (hi / (2 * p))) {
+            const uint32_t a = k[lo], b = k[hi];
+            k[lo] = max(a, b);
+            k[hi] = min(a, b);
+          }
+        }
+      }
+    }
+  }
 }
 
 __device__ __forceinline__ void merge_top2(float& a1, float& a2, float b1, float b2) {
@@ -80,6 +118,8 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int64_t token = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  __shared__ __align__(16) uint32_t sm_key[8][32 * VPL];   // per warp: every expert's selection key, by expert index
+  __shared__ __align__(16) float sm_s[8][32 * VPL];        // per warp: every expert's un-biased score
   if (token >= p.tokens) return;  // whole warp leaves together
 
   const int E = p.experts;
@@ -145,12 +185,33 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
   }
 
-  // ---- group selection ----
+  // ---- keys: the originals go to shared memory for the final index look-up, a sorted copy stays in registers
+  uint32_t key[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) key[v] = score_key(c[v]);
+  uint32_t* wkeys = sm_key[threadIdx.x >> 5];
+  float* wscores = sm_s[threadIdx.x >> 5];
+  if constexpr (VPL >= 4) {
+#pragma unroll
+    for (int v = 0; v < VPL; v += 4) {
+      *reinterpret_cast<uint4*>(wkeys + e0 + v) = make_uint4(key[v], key[v + 1], key[v + 2], key[v + 3]);
+      *reinterpret_cast<float4*>(wscores + e0 + v) = make_float4(s[v], s[v + 1], s[v + 2], s[v + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      wkeys[e0 + v] = key[v];
+      wscores[e0 + v] = s[v];
+    }
+  }
+  sort_desc<VPL>(key);
+
+  // ---- group selection: a group's score is the sum of its two best choices ----
   if (p.n_group > 1) {
     const int lanes_per_group = (E / p.n_group) / VPL;  // power of two, checked on the host
-    float t1 = -CUDART_INF_F, t2 = -CUDART_INF_F;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) merge_top2(t1, t2, c[v], -CUDART_INF_F);
+    float t1 = key_score(key[0]);
+    float t2 = -CUDART_INF_F;
+    if constexpr (VPL >= 2) t2 = key_score(key[1]);
     for (int o = 1; o < lanes_per_group; o <<= 1) {
       const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
       const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
@@ -166,62 +227,69 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     const bool keep = (my_group < p.n_group) && (rank < p.topk_group);
     if (!keep) {
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) c[v] = -CUDART_INF_F;
+      for (int v = 0; v < VPL; ++v) key[v] = KEY_NEG_INF;
     }
   }
 
-  // ---- top-k: k rounds of warp arg-max (ties -> lower expert index) ----
-  // Scores become order-preserving unsigned keys so that one hardware warp reduction
-  // (redux.sync) finds the maximum; a ballot picks the lowest lane (= lowest expert index) among equals.
-  // Each lane caches its local best; only the winning lane rescans after a round.
-  uint32_t key[VPL];
+  // ---- top-k: k rounds over the heads of the sorted per-lane lists (ties -> lower expert index) ----
+  // One hardware warp reduction (redux.sync) finds the maximum head; a ballot picks the lowest lane
+  // among equals (lanes hold ascending expert ranges, equal keys inside a lane leave in index order);
+  // the winning lane pops its head.  Round k's winner is remembered by lane k as (lane, key, how many
+  // equal keys of that lane left before it) and turned into an expert index after the loop.
+  int my_owner = 0, my_dup = 0;
+  uint32_t my_key = 0;
+  int prev_owner = -1, dup = 0;
+  uint32_t prev_key = 0;
+  for (int k = 0; k < p.top_k; ++k) {
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, key[0]);
+    const int owner = __ffs(__ballot_sync(0xffffffffu, key[0] == wmax)) - 1;
+    dup = (owner == prev_owner && wmax == prev_key) ? dup + 1 : 0;
+    prev_owner = owner;
+    prev_key = wmax;
+    if (lane == k) {
+      my_owner = owner;
+      my_key = wmax;
+      my_dup = dup;
+    }
+    if (lane == owner) {
 #pragma unroll
-  for (int v = 0; v < VPL; ++v) {
-    const uint32_t b = __float_as_uint(c[v]);
-    key[v] = (b & 0x80000000u) ? ~b : (b | 0x80000000u);      // -inf maps to 0x007fffff: below every finite score
-  }
-  uint32_t lbest = 0;
-  int lidx = 0;
-  float lbest_s = 0.f;          // un-biased score of the lane's current best
-#pragma unroll
-  for (int v = 0; v < VPL; ++v) {
-    if (key[v] > lbest) {   // strict: the lower index wins a tie inside the lane
-      lbest = key[v];
-      lidx = v;
-      lbest_s = s[v];
+      for (int v = 0; v + 1 < VPL; ++v) key[v] = key[v + 1];
+      key[VPL - 1] = 0;
     }
   }
-  float wsum = 0.f;
-  float my_w = 0.f;   // lane i < K keeps weight i
-  int my_id = 0;
-  for (int k = 0; k < p.top_k; ++k) {
-    const uint32_t wmax = __reduce_max_sync(0xffffffffu, lbest);
-    // lanes hold ascending expert ranges, so the lowest lane with the maximum holds the lowest index
-    const int owner = __ffs(__ballot_sync(0xffffffffu, lbest == wmax)) - 1;
-    const int best_e = owner * VPL + __shfl_sync(0xffffffffu, lidx, owner);
-    const float best_s = __shfl_sync(0xffffffffu, lbest_s, owner);
-    if (lane == owner) {
-      // retire the winner and rescan this lane only
-      const int gone = lidx;
-      lbest = 0;
-      lidx = 0;
-      lbest_s = 0.f;
+  __syncwarp();
+  int my_v = 0;
+  {
+    const uint32_t* ok = wkeys + my_owner * VPL;
+    uint32_t orig[VPL];
+    if constexpr (VPL >= 4) {
+#pragma unroll
+      for (int v = 0; v < VPL; v += 4) {
+        const uint4 q = *reinterpret_cast<const uint4*>(ok + v);
+        orig[v] = q.x; orig[v + 1] = q.y; orig[v + 2] = q.z; orig[v + 3] = q.w;
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) orig[v] = ok[v];
+    }
+#pragma unroll
+    for (int v = VPL - 1; v >= 0; --v) my_v = (orig[v] == my_key) ? v : my_v;
+    if (__any_sync(0xffffffffu, my_dup > 0)) {     // equal scores inside one lane: take the (dup+1)-th match
+      int seen = 0, pick = my_v;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
-        if (v == gone) key[v] = 0;
-        if (key[v] > lbest) {
-          lbest = key[v];
-          lidx = v;
-          lbest_s = s[v];
-        }
+        const bool m = orig[v] == my_key;
+        if (m && seen == my_dup) pick = v;
+        seen += m;
       }
-    }
-    wsum += best_s;
-    if (lane == k) {
-      my_w = best_s;
-      my_id = best_e;
+      my_v = pick;
     }
   }
+  const int my_id = my_owner * VPL + my_v;
+  float my_w = (lane < p.top_k) ? wscores[my_id] : 0.f;
+  float wsum = my_w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
   if (lane < p.top_k) {
     float w = my_w;
     if (p.renormalize) w = w / (wsum + 1e-20f);

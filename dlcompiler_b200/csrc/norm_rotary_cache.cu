@@ -186,16 +186,20 @@ struct RotaryParams {
 // Vector path: 16-bit types, half a head a multiple of 8 elements, 16-byte aligned rows.  One thread
 // rotates 8 lower-half and the matching 8 upper-half elements (two 128-bit loads, two stores).
 template <typename T> __global__ void __launch_bounds__(256) rotary_vec_kernel(const RotaryParams p) {
-  using T2 = typename Elem<T>::T2;
-  const int64_t t = blockIdx.x;
+  constexpr int TOKENS_PER_CTA = 4;              // enough work per CTA to amortise its launch
   const int half = p.dim >> 1;
   const int hv = half >> 3;                      // vectors per half head
-  const uint4* cs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.cos) + t * p.dim);
-  const uint4* sn = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.sin) + t * p.dim);
-  const int total = (p.hq + p.hk) * hv;
-  for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
-    const int h = idx / hv;
-    const int i = idx - h * hv;
+  const int per_token = (p.hq + p.hk) * hv;
+  const int64_t t0 = (int64_t)blockIdx.x * TOKENS_PER_CTA;
+  const int ntok = (int)min((int64_t)TOKENS_PER_CTA, p.tokens - t0);
+  for (int idx = threadIdx.x; idx < ntok * per_token; idx += blockDim.x) {
+    const int tl = idx / per_token;
+    const int rem = idx - tl * per_token;
+    const int64_t t = t0 + tl;
+    const int h = rem / hv;
+    const int i = rem - h * hv;
+    const uint4* cs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.cos) + t * p.dim);
+    const uint4* sn = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.sin) + t * p.dim);
     const T* src;
     T* dst;
     if (h < p.hq) {
@@ -378,10 +382,9 @@ extern "C" int dlb_apply_rotary(const void* q, const void* k, const void* cos, c
                    q_stride_t % 8 == 0 && q_stride_h % 8 == 0 && k_stride_t % 8 == 0 && k_stride_h % 8 == 0 &&
                    qo_stride_t % 8 == 0 && qo_stride_h % 8 == 0 && ko_stride_t % 8 == 0 && ko_stride_h % 8 == 0;
   if (vec) {
-    const int work = (hq + hk) * (dim / 16);
-    const int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
-    if (dtype == DLB_DTYPE_BF16) rotary_vec_kernel<__nv_bfloat16><<<(unsigned)tokens, threads, 0, s>>>(p);
-    else rotary_vec_kernel<__half><<<(unsigned)tokens, threads, 0, s>>>(p);
+    const unsigned blocks = (unsigned)((tokens + 3) / 4);     // TOKENS_PER_CTA = 4
+    if (dtype == DLB_DTYPE_BF16) rotary_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(p);
+    else rotary_vec_kernel<__half><<<blocks, 256, 0, s>>>(p);
     DLB_CUDA_LAUNCH_CHECK();
     return DLB_OK;
   }

@@ -56,27 +56,54 @@ def _stable_topk(scores: torch.Tensor, k: int):
     return vals[..., :k], idx[..., :k]
 
 
+def fma32(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> torch.Tensor:
+    """Correctly rounded fp32 fused multiply-add a*b+c (one rounding), as `fmaf` / the GPU's FFMA
+    compute it.  The product of two fp32 numbers is exact in fp64; the fp64 sum is then rounded
+    TO ODD (Knuth's two-sum gives the exact error of the addition, which supplies the sticky bit),
+    so that the final rounding to fp32 cannot double-round.  Finite, non-overflowing operands only.
+    """
+    f64 = torch.float64
+    p = a.to(f64) * b.to(f64)
+    c64 = c.to(f64).expand_as(p)
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)                 # exact: p + c64 == s + err
+    bits = s.contiguous().view(torch.int64)
+    inexact_even = (err != 0) & ((bits & 1) == 0)
+    grows = (err > 0) == (s > 0)                      # the exact sum lies beyond s, away from zero
+    odd = torch.where(grows, bits | 1, bits - 1)      # truncate toward zero, then set the sticky bit
+    bits = torch.where(inexact_even, odd, bits)
+    return bits.view(f64).to(torch.float32)
+
+
+# 2^r on [-0.5, 0.5], degree 5 with the constant term fixed at 1 (relative error 1e-7); highest first
+_EXP2_COEF = (1.3287431793287396e-03, 9.671507403254509e-03, 5.550655722618103e-02,
+              2.4022242426872253e-01, 6.931470632553101e-01, 1.0)
+_NEG_LOG2E_HI = -1.4426950216293335          # fp32 nearest to -log2(e)
+_NEG_LOG2E_LO = -1.925963033500011e-08           # -log2(e) - _NEG_LOG2E_HI, to fp32
+_RINT_MAGIC = 12582912.0                     # 1.5 * 2^23: adding it rounds to an integer
+
+
 def sigmoid_spec(x: torch.Tensor) -> torch.Tensor:
-    """sigmoid as a fixed sequence of correctly-rounded fp32 operations (mul, add, sub, rint,
-    reciprocal; no fused multiply-add).  The CUDA router evaluates exactly this sequence, so both
-    sides produce bit-identical scores and near-ties cannot flip an expert id.  Accurate to
-    about 2 ulp of the true sigmoid:
-        t = clamp(-x, -87, 88); n = rint(t*log2e); r = (t - n*LN2_HI) - n*LN2_LO
-        e = Horner(1, 1, 1/2, 1/6, 1/24, 1/120, 1/720)(r) * 2^n;  sigmoid = 1 / (1 + e)
+    """sigmoid as a fixed sequence of correctly-rounded fp32 operations (fused multiply-add, add,
+    sub, integer add on the exponent, reciprocal).  The CUDA router evaluates exactly this
+    sequence, so both sides produce bit-identical scores and near-ties cannot flip an expert id.
+    Accurate to about 3e-7 relative:
+        xc = clamp(x, -87, 86);  z = fma(xc, -log2e, M);  n = z - M           (M = 1.5 * 2^23)
+        r = fma(xc, -log2e_lo, fma(xc, -log2e_hi, -n))                          (|r| <= 0.5)
+        p = Horner_fma(r);  e = p * 2^n  (n added to the exponent bits);  sigmoid = 1 / (1 + e)
     """
     f = torch.float32
-    x = x.to(f)
     c = lambda v: torch.tensor(v, dtype=torch.float64).to(f)          # nearest fp32 constant
-    t = torch.clamp(-x, -87.0, 88.0)
-    n = torch.round(t * c(1.44269502162933349609375))
-    r = t - n * c(0.693145751953125)
-    r = r - n * c(1.428606765330187045037746429443359375e-06)
-    p = c(1.38888892251998186111450195312e-03).expand_as(r)
-    for coef in (8.33333376795053482055664062500e-03, 4.16666679084300994873046875000e-02,
-                 1.66666671633720397949218750000e-01, 0.5, 1.0, 1.0):
-        p = p * r + c(coef)          # two roundings: fp32 mul, then fp32 add
-    two_n = ((n.to(torch.int32) + 127) << 23).view(f)
-    e = p * two_n
+    xc = torch.clamp(x.to(f), -87.0, 86.0)
+    z = fma32(xc, c(_NEG_LOG2E_HI), c(_RINT_MAGIC))
+    n = z - c(_RINT_MAGIC)
+    r = fma32(xc, c(_NEG_LOG2E_HI), -n)
+    r = fma32(xc, c(_NEG_LOG2E_LO), r)
+    p = c(_EXP2_COEF[0]).expand_as(r)
+    for coef in _EXP2_COEF[1:]:
+        p = fma32(p, r, c(coef))
+    e = (p.contiguous().view(torch.int32) + (z.contiguous().view(torch.int32) << 23)).view(f)
     return torch.reciprocal(1.0 + e)
 
 

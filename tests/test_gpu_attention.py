@@ -79,6 +79,10 @@ def test_prefill_config_sample_and_properties(cuda_device):
     ref = oracle.context_attention(d["q"][s0:s0 + n, 31:32], d["k"][s0:s0 + n, 7:8], d["v"][s0:s0 + n, 7:8],
                                    torch.tensor([0]), torch.tensor([n]))
     torch.testing.assert_close(out[s0 + 8000:s0 + n, 31:32].float(), ref[8000:].float(), rtol=RTOL, atol=ATOL)
+    # determinism: the same inputs give the same bits (catches a softmax warp racing ahead of the MMAs)
+    for _ in range(2):
+        again, _ = _run_prefill(cuda_device, d)
+        assert torch.equal(again, out)
     # causality: changing the last 100 keys/values of a sequence leaves earlier rows bit-identical
     d2 = dict(d)
     d2["k"] = d["k"].clone()

@@ -70,6 +70,46 @@ def test_sigmoid_spec_accuracy_and_range():
     assert torch.isfinite(edge).all() and edge[2] == 0.5 and edge[-1] == 1.0 and edge[0] >= 0
 
 
+def test_fma32_is_the_correctly_rounded_fused_multiply_add():
+    """The oracle's fp32 FMA against C's fmaf (compiled here with gcc), including sums that sit a
+    hair beside an fp32 rounding midpoint, where rounding to fp64 first would round twice."""
+    import ctypes, shutil, subprocess, tempfile, os
+    import numpy as np
+    import pytest
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    d = tempfile.mkdtemp()
+    with open(os.path.join(d, "f.c"), "w") as fh:
+        fh.write("#include <math.h>\nvoid f(const float*a,const float*b,const float*c,float*o,long n)"
+                 "{for(long i=0;i<n;i++)o[i]=fmaf(a[i],b[i],c[i]);}\n")
+    subprocess.check_call(["gcc", "-O2", "-shared", "-fPIC", "-o", os.path.join(d, "f.so"), os.path.join(d, "f.c"), "-lm"])
+    lib = ctypes.CDLL(os.path.join(d, "f.so"))
+
+    def same(a, b, c):
+        out = np.empty_like(a)
+        vp = lambda x: x.ctypes.data_as(ctypes.c_void_p)
+        lib.f(vp(a), vp(b), vp(c), vp(out), ctypes.c_long(a.size))
+        mine = oracle.fma32(torch.from_numpy(a), torch.from_numpy(b), torch.from_numpy(c)).numpy()
+        return np.array_equal(mine.view(np.int32), out.view(np.int32))
+
+    g = np.random.default_rng(0)
+    n = 1 << 20
+    a, b, c = (g.standard_normal(n).astype(np.float32) for _ in range(3))
+    assert same(a, b, c)
+    wide = lambda: (g.standard_normal(n) * 10.0 ** g.uniform(-8, 8, n)).astype(np.float32)
+    assert same(wide(), wide(), wide())
+    a = wide()
+    assert same(a, b, (-(a.astype(np.float64) * b.astype(np.float64))).astype(np.float32))      # cancellation
+    # a*b = 2^-24 * (1 -/+ 2^-40): c + a*b lies 2^-64 below / above the midpoint of c's ulp
+    k = np.arange(1, 4097, dtype=np.float64)
+    cc = (1.0 + k * 2.0 ** -23).astype(np.float32)
+    a1 = np.full(cc.shape, 2.0 ** -12 * (1 + 2.0 ** -20), np.float32)
+    b_lo = np.full(cc.shape, 2.0 ** -12 * (1 - 2.0 ** -20), np.float32)
+    assert same(a1, b_lo, cc) and same(a1, -b_lo, -cc)
+    b_hi = np.full(cc.shape, 2.0 ** -12 * (1 + 2.0 ** -20), np.float32)
+    assert same(a1, b_hi, cc) and same(-a1, b_hi, -cc)
+
+
 def test_gating_tie_break_is_lowest_index():
     logits = torch.zeros(1, 64)
     ids, w = oracle.grouped_topk_gating(logits, None, 4, 4, 2, 1.0, True, "sigmoid")
