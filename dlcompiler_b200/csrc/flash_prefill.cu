@@ -395,7 +395,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-#pragma unroll
         uint32_t pk[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 8) {

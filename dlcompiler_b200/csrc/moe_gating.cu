@@ -41,17 +41,20 @@ struct GatingParams {
   int scoring;
   int renormalize;
   float scale;
+  int lanes_per_group = 1;        // filled by launch_gating
+  int lanes_per_group_log2 = 0;
 };
 
 // sigmoid evaluated by a FIXED sequence of correctly-rounded fp32 operations (fused
-// multiply-add, add, sub, an integer add on the exponent field, IEEE reciprocal; no
+// multiply-add, add, sub, integer add/sub on bit patterns; no division, no
 // approximate transcendental), so that the CPU checker, which performs the same sequence
 // with an exact fp32 FMA, gets bit-identical scores and therefore bit-identical expert ids
 // even for near-ties:
 //   xc = clamp(x, -87, 86);  z = fma(xc, -log2e, M);  n = z - M          (M = 1.5 * 2^23)
 //   r  = fma(xc, -log2e_lo, fma(xc, -log2e_hi, -n))                        (|r| <= 0.5)
 //   p  = 2^r by a degree-5 Horner scheme of FMAs;  e = p * 2^n (n added to p's exponent bits)
-//   sigmoid = 1 / (1 + e)
+//   d  = 1 + e;  y = bits^-1(0x7EF311C7 - bits(d));  three Newton steps y = fma(y, fma(-d, y, 1), y)
+//   sigmoid = y   (no division, no branch)
 __device__ __forceinline__ float sigmoid_spec(float x) {
   constexpr float kMagic = 12582912.0f;
   constexpr float kNegLog2eHi = -1.44269502162933349609e+00f;
@@ -68,17 +71,21 @@ __device__ __forceinline__ float sigmoid_spec(float x) {
   p = __fmaf_rn(p, r, 6.93147063255310058594e-01f);
   p = __fmaf_rn(p, r, 1.0f);
   const float e = __int_as_float(__float_as_int(p) + (__float_as_int(z) << 23));
-  return __frcp_rn(__fadd_rn(1.0f, e));
+  const float d = __fadd_rn(1.0f, e);
+  float y = __int_as_float(0x7EF311C7 - __float_as_int(d));   // 5 % first guess of 1/d
+#pragma unroll
+  for (int it = 0; it < 3; ++it) y = __fmaf_rn(y, __fmaf_rn(-d, y, 1.0f), y);   // 5e-2 -> 2.5e-3 -> 6e-6 -> rounding
+  return y;
 }
 
 // Order-preserving map from fp32 to unsigned: a > b  <=>  key(a) > key(b); -inf maps to
 // 0x007fffff, which leaves 0 free as "slot retired".
 __device__ __forceinline__ uint32_t score_key(float v) {
   const uint32_t b = __float_as_uint(v);
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);     // negative: all bits flip; else only the sign bit
 }
 __device__ __forceinline__ float key_score(uint32_t k) {
-  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+  return __uint_as_float(k ^ ((uint32_t)((int32_t)~k >> 31) | 0x80000000u));
 }
 constexpr uint32_t KEY_NEG_INF = 0x007fffffu;
 
@@ -113,7 +120,39 @@ __device__ __forceinline__ void merge_top2(float& a1, float& a2, float b1, float
   a2 = lo;
 }
 
-template <int VPL>
+// k rounds over the heads of the sorted per-lane lists.  One hardware warp reduction (redux.sync) finds
+// the maximum head; a ballot picks the lowest lane among equals (lanes hold ascending expert ranges);
+// the winning lane pops its head (predicated moves, no branch).  Lane k remembers round k's winner as
+// (lane, key) and, when TRACK_DUP, how many equal keys of that lane left before it: equal keys inside
+// one lane leave in index order, and such rounds are consecutive.
+template <int VPL, bool TRACK_DUP>
+__device__ __forceinline__ void topk_rounds(uint32_t (&key)[VPL], int top_k, int lane, int& my_owner,
+                                            uint32_t& my_key, int& my_dup) {
+  int prev_owner = -1, dup = 0;
+  uint32_t prev_key = 0;
+#pragma unroll 2
+  for (int k = 0; k < top_k; ++k) {
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, key[0]);
+    const int owner = __ffs(__ballot_sync(0xffffffffu, key[0] == wmax)) - 1;
+    const bool rec = lane == k;
+    my_owner = rec ? owner : my_owner;
+    my_key = rec ? wmax : my_key;
+    if constexpr (TRACK_DUP) {
+      dup = (owner == prev_owner && wmax == prev_key) ? dup + 1 : 0;
+      prev_owner = owner;
+      prev_key = wmax;
+      my_dup = rec ? dup : my_dup;
+    }
+    const bool pop = lane == owner;
+#pragma unroll
+    for (int v = 0; v + 1 < VPL; ++v) key[v] = pop ? key[v + 1] : key[v];
+    key[VPL - 1] = pop ? 0u : key[VPL - 1];
+  }
+}
+
+// One warp per token, VPL experts per lane (lane l holds experts l*VPL ..).  FULL: experts == 32 * VPL
+// and 16-byte aligned rows and bias, so no bounds checks and only vector loads.
+template <int VPL, bool FULL>
 __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
@@ -125,6 +164,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   const int E = p.experts;
   const int e0 = lane * VPL;
   const float* row = p.logits + token * p.ld;
+  auto valid = [&](int v) { return FULL || e0 + v < E; };
 
   float s[VPL];  // un-biased score (sigmoid or softmax probability)
   float c[VPL];  // selection score
@@ -132,7 +172,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   if constexpr (VPL >= 4) {
 #pragma unroll
     for (int v = 0; v < VPL; v += 4) {
-      if (e0 + v + 3 < E) {
+      if (FULL || e0 + v + 3 < E) {
         const float4 x = __ldg(reinterpret_cast<const float4*>(row + e0 + v));
         s[v] = x.x; s[v + 1] = x.y; s[v + 2] = x.z; s[v + 3] = x.w;
       } else {
@@ -142,13 +182,13 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
   } else {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? __ldg(row + e0 + v) : -CUDART_INF_F;
+    for (int v = 0; v < VPL; ++v) s[v] = valid(v) ? __ldg(row + e0 + v) : -CUDART_INF_F;
   }
 
   // ---- scoring ----
   if (p.scoring == DLB_SCORE_SIGMOID) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? sigmoid_spec(s[v]) : -CUDART_INF_F;
+    for (int v = 0; v < VPL; ++v) s[v] = valid(v) ? sigmoid_spec(s[v]) : -CUDART_INF_F;
   } else {
     // softmax is monotone in the logit: without a bias the selection runs on the raw logits,
     // which keeps the chosen ids independent of how exp() rounds
@@ -164,24 +204,35 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     float sum = 0.f;
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      s[v] = (e0 + v < E) ? expf(s[v] - m) : 0.f;
+      s[v] = valid(v) ? expf(s[v] - m) : 0.f;
       sum += s[v];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) s[v] = (e0 + v < E) ? s[v] / sum : -CUDART_INF_F;
+    for (int v = 0; v < VPL; ++v) s[v] = valid(v) ? s[v] / sum : -CUDART_INF_F;
   }
   if (p.probs != nullptr) {
 #pragma unroll
     for (int v = 0; v < VPL; ++v)
-      if (e0 + v < E) p.probs[token * E + e0 + v] = s[v];
+      if (valid(v)) p.probs[token * E + e0 + v] = s[v];
   }
   if (p.scoring == DLB_SCORE_SIGMOID || p.bias != nullptr) {
+    if (p.bias == nullptr) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      const bool valid = e0 + v < E;
-      c[v] = valid ? (p.bias != nullptr ? __fadd_rn(s[v], __ldg(p.bias + e0 + v)) : s[v]) : -CUDART_INF_F;
+      for (int v = 0; v < VPL; ++v) c[v] = s[v];
+    } else if constexpr (FULL && VPL >= 4) {
+#pragma unroll
+      for (int v = 0; v < VPL; v += 4) {
+        const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + e0 + v));
+        c[v] = __fadd_rn(s[v], bv.x);
+        c[v + 1] = __fadd_rn(s[v + 1], bv.y);
+        c[v + 2] = __fadd_rn(s[v + 2], bv.z);
+        c[v + 3] = __fadd_rn(s[v + 3], bv.w);
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) c[v] = valid(v) ? __fadd_rn(s[v], __ldg(p.bias + e0 + v)) : -CUDART_INF_F;
     }
   }
 
@@ -208,55 +259,42 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 
   // ---- group selection: a group's score is the sum of its two best choices ----
   if (p.n_group > 1) {
-    const int lanes_per_group = (E / p.n_group) / VPL;  // power of two, checked on the host
+    const int lpg = p.lanes_per_group, lg = p.lanes_per_group_log2;   // a group spans 2^lg lanes
     float t1 = key_score(key[0]);
     float t2 = -CUDART_INF_F;
     if constexpr (VPL >= 2) t2 = key_score(key[1]);
-    for (int o = 1; o < lanes_per_group; o <<= 1) {
+    for (int o = 1; o < lpg; o <<= 1) {
       const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
       const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
       merge_top2(t1, t2, o1, o2);
     }
-    const int my_group = lane / lanes_per_group;
+    const int my_group = lane >> lg;
     const float my_score = (my_group < p.n_group) ? __fadd_rn(t1, t2) : -CUDART_INF_F;
+    // rank = groups that beat mine (ties: lower index).  The lanes of a group share the comparisons:
+    // each takes a slice of the groups, then the partial counts are summed inside the group.
+    const int per = (p.n_group + lpg - 1) >> lg;
+    const int g0 = (lane & (lpg - 1)) * per;
     int rank = 0;
-    for (int g = 0; g < p.n_group; ++g) {
-      const float gs = __shfl_sync(0xffffffffu, my_score, g * lanes_per_group);
-      rank += (gs > my_score) || (gs == my_score && g < my_group);
+    for (int i = 0; i < per; ++i) {
+      const int g = g0 + i;
+      const float gs = __shfl_sync(0xffffffffu, my_score, (g << lg) & 31);
+      rank += (g < p.n_group) && ((gs > my_score) || (gs == my_score && g < my_group));
     }
+    for (int o = 1; o < lpg; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
     const bool keep = (my_group < p.n_group) && (rank < p.topk_group);
-    if (!keep) {
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) key[v] = KEY_NEG_INF;
-    }
+    for (int v = 0; v < VPL; ++v) key[v] = keep ? key[v] : KEY_NEG_INF;
   }
 
-  // ---- top-k: k rounds over the heads of the sorted per-lane lists (ties -> lower expert index) ----
-  // One hardware warp reduction (redux.sync) finds the maximum head; a ballot picks the lowest lane
-  // among equals (lanes hold ascending expert ranges, equal keys inside a lane leave in index order);
-  // the winning lane pops its head.  Round k's winner is remembered by lane k as (lane, key, how many
-  // equal keys of that lane left before it) and turned into an expert index after the loop.
+  // ---- top-k (ties -> lower expert index); equal finite keys inside one lane need the slower bookkeeping ----
+  bool lane_dup = false;
+#pragma unroll
+  for (int v = 0; v + 1 < VPL; ++v) lane_dup |= (key[v] == key[v + 1]) && (key[v] > KEY_NEG_INF);
+  const bool any_dup = __any_sync(0xffffffffu, lane_dup);
   int my_owner = 0, my_dup = 0;
   uint32_t my_key = 0;
-  int prev_owner = -1, dup = 0;
-  uint32_t prev_key = 0;
-  for (int k = 0; k < p.top_k; ++k) {
-    const uint32_t wmax = __reduce_max_sync(0xffffffffu, key[0]);
-    const int owner = __ffs(__ballot_sync(0xffffffffu, key[0] == wmax)) - 1;
-    dup = (owner == prev_owner && wmax == prev_key) ? dup + 1 : 0;
-    prev_owner = owner;
-    prev_key = wmax;
-    if (lane == k) {
-      my_owner = owner;
-      my_key = wmax;
-      my_dup = dup;
-    }
-    if (lane == owner) {
-#pragma unroll
-      for (int v = 0; v + 1 < VPL; ++v) key[v] = key[v + 1];
-      key[VPL - 1] = 0;
-    }
-  }
+  if (!any_dup) topk_rounds<VPL, false>(key, p.top_k, lane, my_owner, my_key, my_dup);
+  else topk_rounds<VPL, true>(key, p.top_k, lane, my_owner, my_key, my_dup);
   __syncwarp();
   int my_v = 0;
   {
@@ -274,7 +312,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
 #pragma unroll
     for (int v = VPL - 1; v >= 0; --v) my_v = (orig[v] == my_key) ? v : my_v;
-    if (__any_sync(0xffffffffu, my_dup > 0)) {     // equal scores inside one lane: take the (dup+1)-th match
+    if (any_dup) {     // take the (dup+1)-th match
       int seen = 0, pick = my_v;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
@@ -286,13 +324,13 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
   }
   const int my_id = my_owner * VPL + my_v;
-  float my_w = (lane < p.top_k) ? wscores[my_id] : 0.f;
+  const float my_w = (lane < p.top_k) ? wscores[my_id] : 0.f;
   float wsum = my_w;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
   if (lane < p.top_k) {
     float w = my_w;
-    if (p.renormalize) w = w / (wsum + 1e-20f);
+    if (p.renormalize) w = __fdividef(w, wsum + 1e-20f);
     w *= p.scale;
     p.ids[token * p.top_k + lane] = my_id;
     p.weights[token * p.top_k + lane] = w;
@@ -300,19 +338,38 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 }
 
 // Launch the one-warp-per-token router for prepared parameters.
-static int launch_gating(const GatingParams& p, void* stream) {
+static int launch_gating(const GatingParams& p_in, void* stream) {
+  GatingParams p = p_in;
   int vpl = 1;
   while (vpl * 32 < p.experts) vpl <<= 1;
+  p.lanes_per_group = 1;
+  p.lanes_per_group_log2 = 0;
+  if (p.n_group > 1) {
+    p.lanes_per_group = (p.experts / p.n_group) / vpl;     // power of two, checked by the caller
+    while ((1 << p.lanes_per_group_log2) < p.lanes_per_group) ++p.lanes_per_group_log2;
+  }
+  const bool full = p.experts == 32 * vpl && ((uintptr_t)p.logits & 15) == 0 && (p.ld % 4) == 0 &&
+                    ((uintptr_t)p.bias & 15) == 0;
   const int warps = 8;
   const int64_t blocks = (p.tokens + warps - 1) / warps;
   DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gating: too many tokens");
   cudaStream_t s = (cudaStream_t)stream;
+  const unsigned g = (unsigned)blocks, t = warps * 32;
   switch (vpl) {
-    case 1: grouped_topk_kernel<1><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 2: grouped_topk_kernel<2><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 4: grouped_topk_kernel<4><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    case 8: grouped_topk_kernel<8><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
-    default: grouped_topk_kernel<16><<<(unsigned)blocks, warps * 32, 0, s>>>(p); break;
+    case 1: grouped_topk_kernel<1, false><<<g, t, 0, s>>>(p); break;
+    case 2: grouped_topk_kernel<2, false><<<g, t, 0, s>>>(p); break;
+    case 4:
+      if (full) grouped_topk_kernel<4, true><<<g, t, 0, s>>>(p);
+      else grouped_topk_kernel<4, false><<<g, t, 0, s>>>(p);
+      break;
+    case 8:
+      if (full) grouped_topk_kernel<8, true><<<g, t, 0, s>>>(p);
+      else grouped_topk_kernel<8, false><<<g, t, 0, s>>>(p);
+      break;
+    default:
+      if (full) grouped_topk_kernel<16, true><<<g, t, 0, s>>>(p);
+      else grouped_topk_kernel<16, false><<<g, t, 0, s>>>(p);
+      break;
   }
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;

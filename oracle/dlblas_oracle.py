@@ -82,16 +82,18 @@ _EXP2_COEF = (1.3287431793287396e-03, 9.671507403254509e-03, 5.550655722618103e-
 _NEG_LOG2E_HI = -1.4426950216293335          # fp32 nearest to -log2(e)
 _NEG_LOG2E_LO = -1.925963033500011e-08           # -log2(e) - _NEG_LOG2E_HI, to fp32
 _RINT_MAGIC = 12582912.0                     # 1.5 * 2^23: adding it rounds to an integer
+_RCP_MAGIC = 0x7EF311C7                      # bits(1/d) ~ _RCP_MAGIC - bits(d)
 
 
 def sigmoid_spec(x: torch.Tensor) -> torch.Tensor:
     """sigmoid as a fixed sequence of correctly-rounded fp32 operations (fused multiply-add, add,
-    sub, integer add on the exponent, reciprocal).  The CUDA router evaluates exactly this
+    sub, integer add/sub on the bit patterns; no division).  The CUDA router evaluates exactly this
     sequence, so both sides produce bit-identical scores and near-ties cannot flip an expert id.
     Accurate to about 3e-7 relative:
         xc = clamp(x, -87, 86);  z = fma(xc, -log2e, M);  n = z - M           (M = 1.5 * 2^23)
         r = fma(xc, -log2e_lo, fma(xc, -log2e_hi, -n))                          (|r| <= 0.5)
-        p = Horner_fma(r);  e = p * 2^n  (n added to the exponent bits);  sigmoid = 1 / (1 + e)
+        p = Horner_fma(r);  e = p * 2^n  (n added to the exponent bits);  d = 1 + e
+        y = bits^-1(0x7EF311C7 - bits(d));  three times  y = fma(y, fma(-d, y, 1), y);  sigmoid = y
     """
     f = torch.float32
     c = lambda v: torch.tensor(v, dtype=torch.float64).to(f)          # nearest fp32 constant
@@ -104,7 +106,11 @@ def sigmoid_spec(x: torch.Tensor) -> torch.Tensor:
     for coef in _EXP2_COEF[1:]:
         p = fma32(p, r, c(coef))
     e = (p.contiguous().view(torch.int32) + (z.contiguous().view(torch.int32) << 23)).view(f)
-    return torch.reciprocal(1.0 + e)
+    d = 1.0 + e
+    y = (_RCP_MAGIC - d.contiguous().view(torch.int32)).view(f)       # 5 % first guess of 1/d from the bits
+    for _ in range(3):                                                # Newton: error 5e-2 -> 2.5e-3 -> 6e-6 -> rounding
+        y = fma32(y, fma32(-d, y, c(1.0)), y)
+    return y
 
 
 def grouped_topk_gating(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, n_group: int = 1,

@@ -102,6 +102,18 @@ def test_gating_ties_go_to_lower_index(cuda_device):
     torch.testing.assert_close(w2.cpu(), torch.full((2, 2), 0.125))
 
 
+@pytest.mark.parametrize("E,ng,tg,k", [(256, 8, 4, 8), (128, 1, 1, 6), (512, 16, 4, 8)])
+def test_gating_many_equal_scores(cuda_device, E, ng, tg, k):
+    """Logits from five distinct values: equal scores inside lanes, across lanes and across groups."""
+    g = torch.Generator().manual_seed(E)
+    logits = torch.randint(-2, 3, (96, E), generator=g).float()
+    bias = torch.randint(0, 2, (E,), generator=g).float() * 0.25
+    ids, w = grouped_topk_gating(logits.to(cuda_device), bias.to(cuda_device), k, ng, tg, 1.0, True, "sigmoid")
+    rid, rw = oracle.grouped_topk_gating(logits, bias, k, ng, tg, 1.0, True, "sigmoid")
+    assert torch.equal(ids.cpu(), rid)
+    torch.testing.assert_close(w.cpu(), rw, rtol=1e-5, atol=1e-6)
+
+
 def test_gating_is_deterministic(cuda_device):
     wl = W.GatingWorkload(tokens=4096)
     d = wl.make()
