@@ -266,6 +266,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
+      const uint64_t desc0 = make_smem_desc(smem_u32(smem), 16, 1024, 2);   // stage 0, A operand
+      const uint32_t desc_lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++tile_iter) {
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_ph = (tile_iter >> 1) & 1;
@@ -277,15 +279,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, 3, tile)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
-          const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024, 2);
-          const uint64_t b_desc = make_smem_desc(b_addr, 16, 1024, 2);
+          // descriptors: only the 14-bit address field (bytes >> 4) in the low word moves
+          const uint32_t a_lo = desc_lo0 + (uint32_t)s * (STAGE_BYTES >> 4);
+          const uint32_t b_lo = a_lo + (A_BYTES >> 4);
+          if (kb == 0) umma_ss_lohi<0>(d_tmem, a_lo, desc_hi, b_lo, desc_hi, (uint32_t)p.idesc);
+          else umma_ss_lohi<1>(d_tmem, a_lo, desc_hi, b_lo, desc_hi, (uint32_t)p.idesc);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          for (int kk = 1; kk < BK / UMMA_K; ++kk) {
             // advance 32 bytes (16 elements) along K inside the 128-byte swizzle row
-            umma_ss_f16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), (uint32_t)p.idesc,
-                        (kb | kk) != 0 ? 1u : 0u);
+            umma_ss_lohi<1>(d_tmem, a_lo + kk * 2, desc_hi, b_lo + kk * 2, desc_hi, (uint32_t)p.idesc);
           }
           umma_commit(&empty_bar[s]);   // stage reusable once these MMAs have read it
         }
