@@ -27,10 +27,6 @@
 // resident CTAs share K/V through L2 and the tail of each group is short.
 #include <math_constants.h>
 
-#include <algorithm>
-#include <atomic>
-#include <mutex>
-
 #include "common.cuh"
 
 namespace dlb {
@@ -201,15 +197,12 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_CTRL);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;     // [2]
-  uint64_t* k_empty = bars + 3;    // [2]
   uint64_t* v_full = bars + 5;     // [2]
-  uint64_t* v_empty = bars + 7;    // [2]
   uint64_t* s_full = bars + 9;     // [2]
   // p_full is per S/P buffer: a fast softmax warp may finish block j+1 before a slow one finishes
   // block j, and its arrival must not count toward block j's phase
   uint64_t* p_full = bars + 11;    // [2]
-  uint64_t* pv_done = bars + 13;   // one phase per P.V; waited on only before O is rescaled
-  uint64_t* o_done = bars + 14;    // the last P.V retired: O is final
+  uint64_t* pv_done = bars + 13;   // [2] P.V of the block in S/P buffer s retired: V stage s reusable, O updated
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -220,14 +213,11 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&pv_done[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
     }
-    mbar_init(pv_done, 1);
-    mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -254,12 +244,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int row = start + j * BN;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, 21, j)) break;
+        // K stage s is free once the Q K^T of block j - 2 has retired (s_full), V stage s once its P V has
+        // (pv_done): no separate "empty" commits, every commit costs the single issuing thread ~100 clocks
+        if (!mbar_wait(&s_full[s], ph ^ 1, abort_flag, p.status, 21, j)) break;
         uint8_t* kd = smem + OFF_K + s * KV_BYTES;
         mbar_arrive_expect_tx(&k_full[s], KV_BYTES);
 #pragma unroll
         for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
+        if (!mbar_wait(&pv_done[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
         uint8_t* vd = smem + OFF_V + s * KV_BYTES;
         mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
 #pragma unroll
@@ -294,15 +286,20 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             else umma_ss_lohi<1>(tmem_base + s * BN, q_lo0 + off, kq_hi, k_lo + koff, kq_hi, p.idesc_qk);
           }
           umma_commit(&s_full[s]);
-          umma_commit(&k_empty[s]);
         }
         if (j > 0) {
           // O += P_{j-1} V_{j-1}
           const int jj = j - 1;
           const int s = jj & 1;
           const uint32_t ph = (jj >> 1) & 1;
-          if (!mbar_wait(&p_full[s], ph, abort_flag, p.status, 26, jj)) { ok = false; break; }
-          if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, 27, jj)) { ok = false; break; }
+          {
+            // poll both barriers at once (their latencies overlap); wait in turn only if one is not ready
+            const bool r1 = mbar_try_wait(&p_full[s], ph), r2 = mbar_try_wait(&v_full[s], ph);
+            if (!(r1 && r2)) {
+              if (!mbar_wait(&p_full[s], ph, abort_flag, p.status, 26, jj)) { ok = false; break; }
+              if (!mbar_wait(&v_full[s], ph, abort_flag, p.status, 27, jj)) { ok = false; break; }
+            }
+          }
           tc_fence_after_sync();
           const uint32_t v_lo = v_lo0 + (uint32_t)s * (KV_BYTES >> 4);
           // A = P_{jj} from TMEM (16-bit pairs in the first 32 columns of S buffer s), 8 columns per K16 step
@@ -311,9 +308,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int ks = 1; ks < BN / 16; ++ks)
             umma_ts_lohi<1>(tmem_o, tmem_base + s * BN + ks * 8, v_lo + ks * (16 * 128 >> 4), v_hi, p.idesc_pv);
-          umma_commit(pv_done);
-          umma_commit(&v_empty[s]);
-          if (jj == nb - 1) umma_commit(o_done);
+          umma_commit(&pv_done[s]);
         }
       }
     }
@@ -378,7 +373,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       // O may be rescaled only once P_{j-1} V_{j-1} has retired.  (P_{j-2} V_{j-2} retired before S_j was
       // signalled, so the barrier is never more than one phase behind and the parity wait is exact.)
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
-        ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, 29, j);
+        ok = mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, 29, j);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -449,8 +444,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_arrive(&p_full[s]);
     }
     if (ok) {
-      // not pv_done: without a wait in every block its phase may be two behind here, which a parity cannot tell
-      ok = mbar_wait(o_done, 0, abort_flag, p.status, 30, nb);
+      // the last P.V (the one before it in the same buffer, block nb - 3, retired before S of block nb - 1
+      // was signalled, so the parity is exact)
+      ok = mbar_wait(&pv_done[(nb - 1) & 1], ((nb - 1) >> 1) & 1, abort_flag, p.status, 30, nb);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -491,499 +487,6 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
 }
 
-// =====================================================================================
-// Head size 128: persistent kernel, one CTA per SM, Q as a TMEM operand.
-//
-// Why a second shape: with two CTAs per SM (256 TMEM columns each) there is no room for Q in TMEM,
-// S = Q K^T re-reads the whole 32 KiB Q tile from shared memory for every 64-key block, and the
-// tensor pipe (shared by both CTAs) stalls on operand fetch.  Here one CTA owns all 512 columns:
-//   Q [0,64)   S0..S3 [64,320) (64 keys each)   O [320,448)
-// Q is copied once per tile into TMEM and is the A operand of Q K^T; S is a ring of four buffers, so
-// Q K^T runs three blocks ahead of the softmax; P overwrites the first 32 columns of its S buffer
-// and is the A operand of P V.
-// 352 threads: warps 0-7 softmax, warp 8 scheduler + TMA producer, warp 9 issues the Q K^T MMAs,
-// warp 10 the P V MMAs.  Two issuing threads because a lone thread is the bottleneck otherwise: around
-// every tcgen05.mma it also executes waits and commits, measured at ~90 and ~100 clocks each, which put
-// one thread at ~1750 clocks per 64-key block against ~620 clocks of tensor work.  For the same reason
-// a K stage is released by the S buffer's own "full" commit and a V stage by the P V commit (no
-// separate "empty" commits).  Softmax warp w
-// owns TMEM quadrant w & 3 (32 query rows, one per thread) and the blocks of parity w >> 2: the two
-// warps of a quadrant alternate blocks, so on every scheduler one warp is in its exponentials while
-// the other loads scores and reduces the row max.  The running reference max of a row is handed from
-// block to block through shared memory (it is known right after the max reduction, long before the
-// block's exponentials finish); each warp keeps its own partial row sum.
-// CTAs are persistent: the scheduler claims (sequence, kv head, tile, q head) work items from a global
-// counter in the same L2-friendly order as the 64-key kernel, publishes them through a two-slot ring,
-// and loads the next tile's Q while the current tile is still in its main loop.
-namespace fpw {
-constexpr int BM = 128, BN = 64, HD = 128;
-constexpr int THREADS = 352;
-constexpr int WARP_TMA = 8, WARP_QK = 9, WARP_PV = 10;
-constexpr int Q_BOX = BM * 128;             // one 64-wide (128 B) column box of the Q tile
-constexpr int KV_BOX = BN * 128;            // one 64-wide column box of a K or V tile
-constexpr int Q_BYTES = 2 * Q_BOX, KV_BYTES = 2 * KV_BOX;
-constexpr int S_BUFS = 4;                   // S ring; K and V rings have the same depth and index
-constexpr int K_STAGES = S_BUFS, V_STAGES = S_BUFS;
-constexpr int K_AHEAD = 2;                  // K loads run this many blocks ahead of V loads
-constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + Q_BYTES;
-constexpr int OFF_V = OFF_K + K_STAGES * KV_BYTES;
-constexpr int OFF_MST = OFF_V + V_STAGES * KV_BYTES;     // float [2 slots][128 rows] reference max after a block
-constexpr int OFF_XL = OFF_MST + 1024;                   // float [2 warp sets][128 rows] partial row sums
-constexpr int OFF_REC = OFF_XL + 1024;                   // int [2 slots][8] work items
-constexpr int OFF_CTRL = OFF_REC + 64;
-constexpr int SMEM_BYTES = OFF_CTRL + 384;
-constexpr int TM_Q = 0, TM_S = 64, TM_O = 320, TMEM_COLS = 512;
-constexpr float RESCALE_THRESHOLD = 8.0f;
-constexpr int COUNTER_SLOTS = 64;
-}  // namespace fpw
-
-// One work counter per launch in flight (slots are handed out round-robin by the host and zeroed on
-// the launch's stream before the kernel starts).
-static __device__ unsigned int g_prefill_tile_counter[fpw::COUNTER_SLOTS];
-
-struct WideParams {
-  PrefillParams base;
-  unsigned int* tile_counter;
-  int total_items;
-};
-
-template <typename T>
-__global__ void __launch_bounds__(fpw::THREADS, 1)
-flash_prefill_wide_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                          const __grid_constant__ CUtensorMap tmap_v, const WideParams wp) {
-  using namespace fpw;
-  const PrefillParams& p = wp.base;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  if ((smem_u32(smem) & 1023u) != 0) {
-    if (threadIdx.x == 0 && p.status != nullptr && atomicCAS(p.status, 0, 2) == 0) p.status[1] = 40;
-    return;
-  }
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_CTRL);
-  uint64_t* q_full = bars + 0;      // Q tile landed in shared memory (TMA)
-  uint64_t* q_ready = bars + 1;     // Q copied to TMEM by the 256 softmax threads: MMAs may start, Q smem is free
-  uint64_t* k_full = bars + 2;      // [4]
-  uint64_t* v_full = bars + 6;      // [4]
-  uint64_t* s_full = bars + 10;     // [4] Q K^T of the block retired: S readable, K stage reusable
-  uint64_t* p_full = bars + 14;     // [4] 128 arrivals (the four warps that own the block)
-  uint64_t* pv_done = bars + 18;    // [4] P V of the block retired: S buffer and V stage reusable, O updated
-  uint64_t* o_free = bars + 22;     // one phase per tile: 256 threads have read O
-  uint64_t* rec_full = bars + 23;   // [2]
-  uint64_t* rec_empty = bars + 25;  // [2] 10 arrivals (two MMA threads + 8 softmax warps)
-  uint64_t* m_full = bars + 27;     // [4 quadrants][2 slots] 32 arrivals: reference max after a block posted
-  uint64_t* l_full = bars + 35;     // [4 quadrants] 64 arrivals: both warps posted their row sum
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 39);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* mst = reinterpret_cast<float*>(smem + OFF_MST);
-  float* xl = reinterpret_cast<float*>(smem + OFF_XL);
-  volatile int* recs = reinterpret_cast<volatile int*>(smem + OFF_REC);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_ready, 256);
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
-      mbar_init(&pv_done[i], 1);
-      mbar_init(&l_full[i], 64);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&rec_full[i], 1);
-      mbar_init(&rec_empty[i], 10);
-    }
-    mbar_init(o_free, 256);
-    for (int i = 0; i < 8; ++i) mbar_init(&m_full[i], 32);
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == WARP_QK) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == WARP_TMA) {
-    // ------------------------------ scheduler + TMA producer ------------------------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-      uint32_t g = 0;
-      for (int t = 0;; ++t) {
-        // claim the next non-empty work item (same order as the 64-key kernel's block index)
-        int head = 0, kvh = 0, q0 = 0, seq_len = 0, start = 0, kv_end = 0, nb = 0;
-        for (;;) {
-          const unsigned idx = atomicAdd(wp.tile_counter, 1u);
-          if (idx >= (unsigned)wp.total_items) { nb = 0; break; }
-          int x = (int)idx;
-          const int hig = x % p.group;
-          x /= p.group;
-          const int tile = p.max_tiles - 1 - x % p.max_tiles;
-          x /= p.max_tiles;
-          kvh = x % p.hkv;
-          const int seq = x / p.hkv;
-          head = kvh * p.group + hig;
-          seq_len = p.b_seq_len[seq];
-          q0 = tile * BM;
-          if (q0 >= seq_len) continue;
-          start = p.b_start_loc[seq];
-          kv_end = p.causal ? min(seq_len, q0 + BM) : seq_len;
-          nb = (kv_end + BN - 1) / BN;
-          break;
-        }
-        const int slot = t & 1;
-        if (!mbar_wait(&rec_empty[slot], ((t >> 1) & 1) ^ 1, abort_flag, p.status, 41, t)) break;
-        volatile int* r = recs + slot * 8;
-        r[0] = start; r[1] = head; r[2] = kvh; r[3] = q0; r[4] = seq_len; r[5] = kv_end; r[6] = nb;
-        mbar_arrive(&rec_full[slot]);
-        if (nb == 0) break;
-        // Q: its shared-memory tile is free once the previous tile's copy to TMEM is complete
-        if (!mbar_wait(q_ready, (t & 1) ^ 1, abort_flag, p.status, 42, t)) break;
-        mbar_arrive_expect_tx(q_full, Q_BYTES);
-#pragma unroll
-        for (int bx = 0; bx < 2; ++bx) tma_load_3d(smem + OFF_Q + bx * Q_BOX, &tmap_q, q_full, bx * 64, head, start + q0);
-        // K runs K_AHEAD blocks ahead of V, like the MMAs that consume them.  Stage gi % 4 of K is free
-        // once the Q K^T of block gi - 4 has retired (s_full), of V once its P V has (pv_done).
-        bool ok = true;
-        auto load_k = [&](int j) -> bool {
-          const uint32_t gi = g + j;
-          const int st = gi % K_STAGES;
-          if (!mbar_wait(&s_full[st], ((gi / K_STAGES) & 1) ^ 1, abort_flag, p.status, 43, j)) return false;
-          uint8_t* kd = smem + OFF_K + st * KV_BYTES;
-          mbar_arrive_expect_tx(&k_full[st], KV_BYTES);
-#pragma unroll
-          for (int bx = 0; bx < 2; ++bx)
-            tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[st], bx * 64, kvh, start + j * BN);
-          return true;
-        };
-        for (int j = 0; ok && j < min(nb, K_AHEAD); ++j) ok = load_k(j);
-        for (int j = 0; ok && j < nb; ++j) {
-          const uint32_t gi = g + j;
-          const int st = gi % V_STAGES;
-          if (!mbar_wait(&pv_done[st], ((gi / V_STAGES) & 1) ^ 1, abort_flag, p.status, 44, j)) { ok = false; break; }
-          uint8_t* vd = smem + OFF_V + st * KV_BYTES;
-          mbar_arrive_expect_tx(&v_full[st], KV_BYTES);
-#pragma unroll
-          for (int bx = 0; bx < 2; ++bx)
-            tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[st], bx * 64, kvh, start + j * BN);
-          if (j + K_AHEAD < nb) ok = load_k(j + K_AHEAD);
-        }
-        if (!ok) break;
-        g += nb;
-      }
-    }
-  } else if (warp == WARP_QK) {
-    // ------------------------------ Q K^T issuer ------------------------------
-    if (lane == 0) {
-      uint32_t g = 0;
-      bool ok = true;
-      // descriptors as (low, high) words: only the address field (bytes >> 4) in the low word moves
-      const uint64_t k_d0 = make_smem_desc(smem_u32(smem + OFF_K), 16, 1024, 2);
-      const uint32_t k_lo0 = (uint32_t)k_d0, k_hi = (uint32_t)(k_d0 >> 32);
-      for (int t = 0; ok; ++t) {
-        const int slot = t & 1;
-        if (!mbar_wait(&rec_full[slot], (t >> 1) & 1, abort_flag, p.status, 45, t)) break;
-        const int nb = recs[slot * 8 + 6];
-        mbar_arrive(&rec_empty[slot]);
-        if (nb == 0) break;
-        if (!mbar_wait(q_ready, t & 1, abort_flag, p.status, 46, t)) break;
-        for (int j = 0; j < nb; ++j) {
-          // S_j = Q K_j^T into S buffer gi % 4, Q from TMEM (8 columns per K16 step).  The buffer last held
-          // P of block gi - 4: wait until the other thread's P V of that block has retired.
-          const uint32_t gi = g + j;
-          const int sb = gi % S_BUFS;
-          const uint32_t par = (gi / S_BUFS) & 1;
-          const bool r1 = mbar_try_wait(&k_full[sb], par), r2 = mbar_try_wait(&pv_done[sb], par ^ 1);
-          if (!(r1 && r2)) {
-            if (!mbar_wait(&k_full[sb], par, abort_flag, p.status, 47, j)) { ok = false; break; }
-            if (!mbar_wait(&pv_done[sb], par ^ 1, abort_flag, p.status, 59, j)) { ok = false; break; }
-          }
-          tc_fence_after_sync();
-          const uint32_t k_lo = k_lo0 + (uint32_t)sb * (KV_BYTES >> 4);
-          const uint32_t s_tm = tmem_base + TM_S + sb * BN;
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t koff = (uint32_t)(((ks >> 2) * KV_BOX + (ks & 3) * 32) >> 4);
-            if (ks == 0) umma_ts_lohi<0>(s_tm, tmem_base + TM_Q, k_lo + koff, k_hi, p.idesc_qk);
-            else umma_ts_lohi<1>(s_tm, tmem_base + TM_Q + ks * 8, k_lo + koff, k_hi, p.idesc_qk);
-          }
-          umma_commit(&s_full[sb]);
-        }
-        g += nb;
-      }
-    }
-  } else if (warp == WARP_PV) {
-    // ------------------------------ P V issuer ------------------------------
-    if (lane == 0) {
-      uint32_t g = 0;
-      bool ok = true;
-      const uint64_t v_d0 = make_smem_desc(smem_u32(smem + OFF_V), p.v_lbo, p.v_sbo, 2);
-      const uint32_t v_lo0 = (uint32_t)v_d0, v_hi = (uint32_t)(v_d0 >> 32);
-      for (int t = 0; ok; ++t) {
-        const int slot = t & 1;
-        if (!mbar_wait(&rec_full[slot], (t >> 1) & 1, abort_flag, p.status, 60, t)) break;
-        const int nb = recs[slot * 8 + 6];
-        mbar_arrive(&rec_empty[slot]);
-        if (nb == 0) break;
-        // the previous tile's O must have been read before this tile's first P V overwrites it
-        if (t > 0 && !mbar_wait(o_free, (t - 1) & 1, abort_flag, p.status, 50, t)) break;
-        for (int j = 0; j < nb; ++j) {
-          // O += P_j V_j, P from the first 32 columns of its S buffer
-          const uint32_t gi = g + j;
-          const int sb = gi % S_BUFS;
-          const uint32_t par = (gi / S_BUFS) & 1;
-          const bool r1 = mbar_try_wait(&p_full[sb], par), r2 = mbar_try_wait(&v_full[sb], par);
-          if (!(r1 && r2)) {
-            if (!mbar_wait(&p_full[sb], par, abort_flag, p.status, 48, j)) { ok = false; break; }
-            if (!mbar_wait(&v_full[sb], par, abort_flag, p.status, 49, j)) { ok = false; break; }
-          }
-          tc_fence_after_sync();
-          const uint32_t v_lo = v_lo0 + (uint32_t)sb * (KV_BYTES >> 4);
-          const uint32_t p_tm = tmem_base + TM_S + sb * BN;
-          if (j == 0) umma_ts_lohi<0>(tmem_base + TM_O, p_tm, v_lo, v_hi, p.idesc_pv);
-          else umma_ts_lohi<1>(tmem_base + TM_O, p_tm, v_lo, v_hi, p.idesc_pv);
-#pragma unroll
-          for (int ks = 1; ks < BN / 16; ++ks)
-            umma_ts_lohi<1>(tmem_base + TM_O, p_tm + ks * 8, v_lo + ks * (16 * 128 >> 4), v_hi, p.idesc_pv);
-          umma_commit(&pv_done[sb]);
-        }
-        g += nb;
-      }
-    }
-  } else {
-    // ------------------------------ softmax / correction / epilogue ------------------------------
-    const int quad = warp & 3, wset = warp >> 2;   // wset 0 owns the even blocks of a tile, wset 1 the odd ones
-    const int row = quad * 32 + lane;              // query row inside the tile == TMEM lane
-    const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
-    uint32_t g = 0;
-    uint32_t m_uses0 = 0, m_uses1 = 0;             // completed phases of m_full[quad][slot] before this tile
-    bool ok = true;
-    for (int t = 0; ok; ++t) {
-      const int slot = t & 1;
-      ok = mbar_wait(&rec_full[slot], (t >> 1) & 1, abort_flag, p.status, 51, t);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const int start = recs[slot * 8 + 0], head = recs[slot * 8 + 1], q0 = recs[slot * 8 + 3];
-      const int seq_len = recs[slot * 8 + 4], kv_end = recs[slot * 8 + 5], nb = recs[slot * 8 + 6];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&rec_empty[slot]);
-      if (nb == 0) break;
-      // ---- Q: shared memory (128 B swizzle) -> TMEM; this warp copies column box wset of its 32 rows ----
-      ok = mbar_wait(q_full, t & 1, abort_flag, p.status, 52, t);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      {
-        const uint8_t* qrow = smem + OFF_Q + wset * Q_BOX + row * 128;
-        uint32_t qr[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = *reinterpret_cast<const uint4*>(qrow + ((c ^ (row & 7)) << 4));
-          qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
-        }
-        tmem_st_32x32b_x32(tmem_base + lane_field + TM_Q + wset * 32, qr);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(q_ready);
-      }
-      const int q_pos = q0 + row;
-      float m_own = -CUDART_INF_F;   // reference max this warp's row sum is relative to
-      float l_sum = 0.f;
-      for (int j = wset; j < nb; j += 2) {
-        const uint32_t gi = g + j;
-        const int sb = gi % S_BUFS;
-        ok = mbar_wait(&s_full[sb], (gi / S_BUFS) & 1, abort_flag, p.status, 53, j);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        uint32_t sr[2][32];
-        const uint32_t s_addr = tmem_base + lane_field + TM_S + sb * BN;
-        tmem_ld_32x32b_x32(s_addr, sr[0]);
-        tmem_ld_32x32b_x32(s_addr + 32, sr[1]);
-        tmem_wait_ld();
-        const int key0 = j * BN;
-        const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0);
-        if (need_mask) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int key = key0 + h * 32 + c;
-              const bool visible = key < kv_end && (!p.causal || key <= q_pos);
-              if (!visible) sr[h][c] = 0xff800000u;   // -inf
-            }
-          }
-        }
-        float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              mx4[u] = max3(mx4[u], __uint_as_float(sr[h][c + 2 * u]), __uint_as_float(sr[h][c + 2 * u + 1]));
-          }
-        }
-        const float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * p.scale_log2;
-        // reference max after the previous block (the partner warp's), then this block's decision,
-        // posted at once for the next block
-        float m_prev = -CUDART_INF_F;
-        if (j > 0) {
-          const int ps = (j - 1) & 1;
-          ok = mbar_wait(&m_full[quad * 2 + ps], ((ps ? m_uses1 : m_uses0) + ((j - 1) >> 1)) & 1, abort_flag,
-                         p.status, 54, j);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          m_prev = mst[ps * 128 + row];
-        }
-        float m_ref = m_prev;
-        float alpha = 1.f;
-        bool rescale = false;
-        if (m_prev == -CUDART_INF_F) {
-          m_ref = mx;                       // nothing accumulated yet
-        } else if (mx - m_prev > RESCALE_THRESHOLD) {
-          alpha = fast_exp2(m_prev - mx);
-          m_ref = mx;
-          rescale = true;
-        }
-        mst[(j & 1) * 128 + row] = m_ref;
-        mbar_arrive(&m_full[quad * 2 + (j & 1)]);
-        // this warp's row sum follows the reference max (the partner may have moved it too)
-        if (m_own != m_ref) {
-          l_sum *= fast_exp2(m_own - m_ref);   // m_own = -inf: l_sum is 0 and stays 0
-          m_own = m_ref;
-        }
-        // O (all 128 columns of this row) is rescaled by the thread that moved the max, once the
-        // previous block's P.V has retired; no later P.V can start before this block's P is posted
-        if (__any_sync(0xffffffffu, rescale)) {
-          const uint32_t gp = gi - 1;
-          ok = mbar_wait(&pv_done[gp % S_BUFS], (gp / S_BUFS) & 1, abort_flag, p.status, 55, j);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after_sync();
-#pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t o[32];
-            const uint32_t o_addr = tmem_base + lane_field + TM_O + c * 32;
-            tmem_ld_32x32b_x32(o_addr, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32b_x32(o_addr, o);
-          }
-          tmem_wait_st();
-        }
-        const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
-        const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
-        const uint64_t negm2 = pack_f2(neg_m, neg_m);
-        uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const uint64_t a01 =
-                fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2);
-            const uint64_t a23 =
-                fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2);
-            float x0, x1, x2, x3;
-            unpack_f2(a01, x0, x1);
-            unpack_f2(a23, x2, x3);
-            const float e0 = fast_exp2(x0), e1 = fast_exp2(x1), e2 = fast_exp2(x2), e3 = fast_exp2(x3);
-            sum2a = add_f2(sum2a, pack_f2(e0, e1));
-            sum2b = add_f2(sum2b, pack_f2(e2, e3));
-            typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
-            typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
-            pk[c / 2] = *reinterpret_cast<uint32_t*>(&v01);
-            pk[c / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
-          }
-          tmem_st_32x32b_x16(s_addr + h * 16, pk);   // P (16-bit pairs) over the first 32 columns of this S buffer
-        }
-        {
-          float a, b;
-          unpack_f2(add_f2(sum2a, sum2b), a, b);
-          l_sum += a + b;
-        }
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(&p_full[sb]);
-      }
-      if (!ok) break;
-      // ---- epilogue: final reference max = the last block's; combine the two warps' row sums ----
-      float m_fin;
-      {
-        const int ls = (nb - 1) & 1;
-        ok = mbar_wait(&m_full[quad * 2 + ls], ((ls ? m_uses1 : m_uses0) + ((nb - 1) >> 1)) & 1, abort_flag,
-                       p.status, 58, t);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        m_fin = mst[ls * 128 + row];
-      }
-      m_uses0 += (uint32_t)(nb + 1) >> 1;
-      m_uses1 += (uint32_t)nb >> 1;
-      if (m_own != m_fin) l_sum *= fast_exp2(m_own - m_fin);
-      {
-        const uint32_t gl = g + nb - 1;   // the last block's P V
-        ok = mbar_wait(&pv_done[gl % S_BUFS], (gl / S_BUFS) & 1, abort_flag, p.status, 57, t);
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      // (after the last P V: this tile's first P V waited for every thread's o_free of the previous tile, so
-      // the partner's read of the previous tile's sums is behind us)
-      xl[wset * 128 + row] = l_sum;
-      mbar_arrive(&l_full[quad]);
-      ok = mbar_wait(&l_full[quad], t & 1, abort_flag, p.status, 56, t);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const float l_tot = l_sum + xl[(wset ^ 1) * 128 + row];
-      const float inv_l = 1.f / l_tot;
-      const bool row_ok = q_pos < seq_len;
-      T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(start + q_pos) * p.o_stride_t + (int64_t)head * p.o_stride_h +
-                wset * 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_field + TM_O + wset * 64 + c * 32, o);
-        tmem_wait_ld();
-        if (row_ok) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              typename Elem<T>::T2 v2 = Elem<T>::from_f2(__uint_as_float(o[v * 8 + 2 * i]) * inv_l,
-                                                         __uint_as_float(o[v * 8 + 2 * i + 1]) * inv_l);
-              w[i] = *reinterpret_cast<uint32_t*>(&v2);
-            }
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(o_free);
-      if (row_ok && wset == 0 && p.lse != nullptr) {
-        p.lse[(int64_t)head * p.total_tokens + start + q_pos] = m_fin * 0.6931471805599453f + __logf(l_tot);
-      }
-      g += nb;
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == WARP_QK) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, fpw::TMEM_COLS);
-  }
-}
-
 template <typename T, int D>
 static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
                           unsigned grid, cudaStream_t stream) {
@@ -995,60 +498,6 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     return (int)e;
   }
   kern<<<grid, fp::THREADS, SMEM, stream>>>(tq, tk, tv, p);
-  return DLB_OK;
-}
-
-// Device address of work-counter slot `slot` on the current device (the symbol's host-side name is
-// only a handle; the address comes from the runtime and is cached per device).
-static int prefill_counter_address(int slot, unsigned int** out) {
-  static unsigned int* cache[64] = {nullptr};
-  static std::mutex mu;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) {
-    set_last_error("flash_prefill: cudaGetDevice: %s", cudaGetErrorString(e));
-    return (int)e;
-  }
-  DLB_CHECK_ARG(dev >= 0 && dev < 64, DLB_ERR_UNSUPPORTED, "flash_prefill: device ordinal %d", dev);
-  std::lock_guard<std::mutex> lock(mu);
-  if (cache[dev] == nullptr) {
-    unsigned int* ptr = nullptr;
-    e = cudaGetSymbolAddress((void**)&ptr, g_prefill_tile_counter);
-    if (e != cudaSuccess || ptr == nullptr) {
-      set_last_error("flash_prefill: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-      return e != cudaSuccess ? (int)e : DLB_ERR_DRIVER;
-    }
-    cache[dev] = ptr;
-  }
-  *out = cache[dev] + slot;
-  return DLB_OK;
-}
-
-template <typename T>
-static int launch_prefill_wide(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                               const PrefillParams& p, int64_t items, cudaStream_t stream) {
-  static std::atomic<unsigned> next_slot{0};
-  WideParams wp;
-  wp.base = p;
-  wp.total_items = (int)items;
-  const int slot = (int)(next_slot.fetch_add(1) % fpw::COUNTER_SLOTS);
-  int rc = prefill_counter_address(slot, &wp.tile_counter);
-  if (rc != DLB_OK) return rc;
-  cudaError_t e = cudaMemsetAsync(wp.tile_counter, 0, sizeof(unsigned int), stream);
-  if (e != cudaSuccess) {
-    set_last_error("flash_prefill: counter reset: %s", cudaGetErrorString(e));
-    return (int)e;
-  }
-  auto kern = flash_prefill_wide_kernel<T>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fpw::SMEM_BYTES);
-  if (e != cudaSuccess) {
-    set_last_error("flash_prefill: smem attribute: %s", cudaGetErrorString(e));
-    return (int)e;
-  }
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const int64_t ctas = std::min<int64_t>(items, sm_count(dev));
-  kern<<<(unsigned)ctas, fpw::THREADS, fpw::SMEM_BYTES, stream>>>(tq, tk, tv, wp);
   return DLB_OK;
 }
 
@@ -1078,9 +527,7 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   const int64_t grid = max_tiles * batch * hq;
   DLB_CHECK_ARG(grid <= 0x7fffffffLL && total_tokens < (1LL << 31), DLB_ERR_TOO_LARGE, "flash_prefill: grid too large");
 
-  // head size 128 runs the persistent 128-key-block kernel, head size 64 the 64-key-block kernel
-  const bool wide = D == 128;
-  const int kv_box = BN;   // both kernels use 64-key K/V tiles
+  const int kv_box = BN;
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_tokens(&tq, q, D, hq, total_tokens, q_stride_h, q_stride_t, BM);
   if (rc != DLB_OK) return rc;
@@ -1117,11 +564,11 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   cudaStream_t s = (cudaStream_t)stream;
   int rc2;
   if (dtype == DLB_DTYPE_BF16) {
-    rc2 = wide ? launch_prefill_wide<__nv_bfloat16>(tq, tk, tv, p, grid, s)
-               : launch_prefill<__nv_bfloat16, 64>(tq, tk, tv, p, (unsigned)grid, s);
+    rc2 = D == 128 ? launch_prefill<__nv_bfloat16, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__nv_bfloat16, 64>(tq, tk, tv, p, (unsigned)grid, s);
   } else {
-    rc2 = wide ? launch_prefill_wide<__half>(tq, tk, tv, p, grid, s)
-               : launch_prefill<__half, 64>(tq, tk, tv, p, (unsigned)grid, s);
+    rc2 = D == 128 ? launch_prefill<__half, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__half, 64>(tq, tk, tv, p, (unsigned)grid, s);
   }
   if (rc2 != DLB_OK) return rc2;
   DLB_CUDA_LAUNCH_CHECK();
