@@ -119,7 +119,22 @@ struct DecodeParams {
   int table_is_int64, lens_is_int64;
   float sm_scale, softcap;   // softcap <= 0: none
   int* status;
+  // gather path (pages smaller than 8 tokens): plain pointers and element strides of the caches
+  int gather;
+  const void* k_cache;
+  const void* v_cache;
+  int64_t k_stride_page, k_stride_slot, k_stride_head;
+  int64_t v_stride_page, v_stride_slot, v_stride_head;
 };
+
+// 16-byte asynchronous copy global -> shared (bypassing L1), and "arrive on this mbarrier once all of
+// this thread's earlier cp.async copies have landed" (the arrival is one of the barrier's expected count).
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 __device__ __forceinline__ int load_index(const void* p, int64_t i, int is64) {
   return is64 ? (int)reinterpret_cast<const int64_t*>(p)[i] : reinterpret_cast<const int32_t*>(p)[i];
@@ -176,7 +191,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], p.gather ? 32 : 1);   // gather: one arrival per producer lane
       mbar_init(&empty_bar[s], CONSUMER_WARPS);
     }
     *abort_flag = 0;
@@ -204,9 +219,67 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
     }
+    if (p.gather) {
+      // Pages of fewer than 8 tokens (token-granular caches: page size 1) would need one TMA box of
+      // 128 bytes per token and column half, and the copy engine's operation rate, not bandwidth, becomes
+      // the limit (measured 0.96 TB/s at page size 1).  Instead the 32 lanes gather 16-byte chunks with
+      // cp.async straight into the same 128-byte-swizzled tile layout: 16 lanes per token row, two rows
+      // per pass, the page of a row looked up by its 16 lanes together.
+      const T* kc = reinterpret_cast<const T*>(p.k_cache);
+      const T* vc = reinterpret_cast<const T*>(p.v_cache);
+      constexpr int CHUNKS = D / 8;                 // 16-byte chunks per token row
+      constexpr int ROWS_PER_PASS = 32 / CHUNKS;    // 2 (D = 128) or 4 (D = 64)
+      const int c16 = lane % CHUNKS;                // chunk inside the row
+      const int sub = lane / CHUNKS;                // row inside the pass
+      const int hbox = c16 >> 3, cc = c16 & 7;      // 64-wide column box and chunk inside its 128-byte row
+      const bool one_token_pages = p.page_size == 1;
+      const T* k_lane = kc + (int64_t)kvh * p.k_stride_head + c16 * 8;   // this lane's chunk of row (page 0, slot 0)
+      const T* v_lane = vc + (int64_t)kvh * p.v_stride_head + c16 * 8;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 11, t) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        uint8_t* kdst = smem + s * STAGE_BYTES + hbox * HALF_BYTES;
+        uint8_t* vdst = kdst + KV_BYTES;
+        const int tok0 = lo + t * TILE_KEYS;
+        // the 64 rows' (page, slot) are looked up once, two rows per lane, and handed out by shuffles
+        int pg[2], sl[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int tok = tok0 + q * 32 + lane;
+          int page_slot = tok / p.page_size;
+          if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // rows past the table: any valid page
+          int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
+          if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
+          pg[q] = page;
+          sl[q] = tok % p.page_size;
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+#pragma unroll 4
+          for (int rr = sub; rr < 32; rr += ROWS_PER_PASS) {
+            const int r = q * 32 + rr;
+            const int page = __shfl_sync(0xffffffffu, pg[q], rr);
+            const uint32_t off = (uint32_t)(r * 128 + ((cc ^ (r & 7)) << 4));
+            int64_t ko = (int64_t)page * p.k_stride_page, vo = (int64_t)page * p.v_stride_page;
+            if (!one_token_pages) {   // uniform
+              const int slot = __shfl_sync(0xffffffffu, sl[q], rr);
+              ko += (int64_t)slot * p.k_stride_slot;
+              vo += (int64_t)slot * p.v_stride_slot;
+            }
+            cp_async_16(kdst + off, k_lane + ko);
+            cp_async_16(vdst + off, v_lane + vo);
+          }
+        }
+        cp_async_arrive(&full_bar[s]);
+      }
+    }
     const int keys_per_box = min(p.page_size, TILE_KEYS);
     const int boxes_per_tile = TILE_KEYS / keys_per_box;
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = 0; !p.gather && t < n_tiles; ++t) {
       const int s = t % STAGES;
       const uint32_t ph = (t / STAGES) & 1;
       int ok = 1;
@@ -557,6 +630,19 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   p.sm_scale = sm_scale;
   p.softcap = softcap;
   p.status = status;
+  // pages of fewer than 8 tokens are gathered with cp.async (needs 16-byte aligned rows)
+  const bool aligned16 = ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && k_stride_page % 8 == 0 &&
+                         k_stride_slot % 8 == 0 && k_stride_head % 8 == 0 && v_stride_page % 8 == 0 &&
+                         v_stride_slot % 8 == 0 && v_stride_head % 8 == 0;
+  p.gather = (page_size < 8 && aligned16) ? 1 : 0;
+  p.k_cache = k_cache;
+  p.v_cache = v_cache;
+  p.k_stride_page = k_stride_page;
+  p.k_stride_slot = k_stride_slot;
+  p.k_stride_head = k_stride_head;
+  p.v_stride_page = v_stride_page;
+  p.v_stride_slot = v_stride_slot;
+  p.v_stride_head = v_stride_head;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DLB_DTYPE_BF16) {
     return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(tk, tv, p, s)
