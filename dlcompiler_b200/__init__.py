@@ -18,9 +18,10 @@ from .kernels.moe_gating import grouped_topk_gating, softmax_topk
 from .kernels.paged_attention import paged_attention_fwd
 from .kernels.prefill_attention import context_attention_fwd
 from .kernels.topk_gating import topk_gating
+from .op_registry import get_op, op_registry, register_dlblas_op
 
 __all__ = [
     "DlblasError", "check_device_status", "is_built", "silu_and_mul", "fused_moe", "fused_moe_kernel_launcher",
     "get_start_end", "moe_align_block_size", "grouped_topk_gating", "softmax_topk", "paged_attention_fwd",
-    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2", "apply_rotary_pos_emb", "fill_kv_cache", "rms_norm", "add_rms_norm", "topk_gating",
+    "context_attention_fwd", "decode_attention_fwd", "flash_attention_fwd", "flash_attention_v2", "apply_rotary_pos_emb", "fill_kv_cache", "rms_norm", "add_rms_norm", "topk_gating", "get_op", "op_registry", "register_dlblas_op",
 ]

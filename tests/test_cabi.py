@@ -50,3 +50,18 @@ def test_wrappers_refuse_cpu_tensors():
 
     with pytest.raises(AssertionError):
         silu_and_mul(torch.zeros(4, 8, dtype=torch.bfloat16))
+
+
+def test_op_registry_shell_resolves_the_reference_names():
+    """`get_op(name, args)` as the reference's consumers call it (dlblas/__init__.py:13-23): known names give a
+    callable operator object, unknown names raise NameError, a wrong arity raises LookupError."""
+    import pytest
+    import dlcompiler_b200 as dl
+    assert set(dl.op_registry.get_list_op_names()) >= {"topk_gating", "flash_attention_v2", "add_rms_norm", "rms_norm"}
+    op = dl.get_op("topk_gating", (None, 2, 1.0, 2, False))
+    assert callable(op) and op.name == "topk_gating"
+    assert dl.get_op("rms_norm", (None, None, 1e-6)).n_args == 3
+    with pytest.raises(NameError):
+        dl.get_op("no_such_op", ())
+    with pytest.raises(LookupError):
+        dl.get_op("flash_attention_v2", (None,))

@@ -161,3 +161,22 @@ def test_fill_then_decode_round_trip(cuda_device):
     paged_attention_fwd(q, kc, vc, o1, *args)
     paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o2, *args)
     assert torch.equal(o1, o2)
+
+
+def test_registry_lookup_runs_the_same_kernels(cuda_device):
+    """`get_op(name, args)(*args)`, the reference's calling convention for its registered ops
+    (dlblas/__init__.py:13-23, add_rms_norm.py:103-118), gives the direct call's result."""
+    import dlcompiler_b200 as dl
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(33, 512, generator=g).to(torch.bfloat16).to(cuda_device)
+    w = torch.randn(512, generator=g).to(torch.bfloat16).to(cuda_device)
+    res = torch.randn(33, 512, generator=g).to(torch.bfloat16).to(cuda_device)
+    args = (x, w, 1e-6)
+    assert torch.equal(dl.get_op("rms_norm", args)(*args), add_rms_norm(x, w, 1e-6))
+    args = (x, w, 1e-6, res)
+    out, res_out = dl.get_op("add_rms_norm", args)(*args)
+    ref_out, ref_res = add_rms_norm(x, w, 1e-6, res)
+    assert torch.equal(out, ref_out) and torch.equal(res_out, ref_res)
+    q = torch.randn(2, 64, 4, 64, generator=g).to(torch.bfloat16).to(cuda_device)
+    args = (q, q, q)
+    assert torch.equal(dl.get_op("flash_attention_v2", args)(*args), dl.flash_attention_v2(q, q, q))
