@@ -72,6 +72,9 @@ def _register_builtin_ops() -> None:
     def _norm_call(hidden_states, weight, eps=1e-6, residual=None):
         return add_rms_norm(hidden_states, weight, eps, residual)
 
+    from .kernels.fused_rotary_and_fa import call as _rotary_fa_call
+    # (q, k, v, cos, sin): fused_rotary_and_fa.py:413
+    register_dlblas_op("fused_rotary_and_fa", 5, _rotary_fa_call)
     register_dlblas_op("add_rms_norm", 4, _norm_call)
     register_dlblas_op("rms_norm", 3, _norm_call)
 

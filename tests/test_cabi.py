@@ -57,7 +57,8 @@ def test_op_registry_shell_resolves_the_reference_names():
     callable operator object, unknown names raise NameError, a wrong arity raises LookupError."""
     import pytest
     import dlcompiler_b200 as dl
-    assert set(dl.op_registry.get_list_op_names()) >= {"topk_gating", "flash_attention_v2", "add_rms_norm", "rms_norm"}
+    assert set(dl.op_registry.get_list_op_names()) >= {"topk_gating", "flash_attention_v2", "add_rms_norm", "rms_norm",
+                                                        "fused_rotary_and_fa"}
     op = dl.get_op("topk_gating", (None, 2, 1.0, 2, False))
     assert callable(op) and op.name == "topk_gating"
     assert dl.get_op("rms_norm", (None, None, 1e-6)).n_args == 3

@@ -180,3 +180,23 @@ def test_registry_lookup_runs_the_same_kernels(cuda_device):
     q = torch.randn(2, 64, 4, 64, generator=g).to(torch.bfloat16).to(cuda_device)
     args = (q, q, q)
     assert torch.equal(dl.get_op("flash_attention_v2", args)(*args), dl.flash_attention_v2(q, q, q))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_rotary_and_fa(cuda_device, dtype):
+    """Rotary on q and k, then dense non-causal attention (fused_rotary_and_fa.py:120-182), against the
+    oracle's rotary followed by the oracle's attention."""
+    import dlcompiler_b200 as dl
+    g = torch.Generator().manual_seed(11)
+    b, s, h, d = 2, 200, 4, 128
+    q, k, v = (torch.randn(b, s, h, d, generator=g).to(dtype) for _ in range(3))
+    ang = torch.rand(b, s, d // 2, generator=g) * 6.283
+    cos = torch.cat([ang.cos(), ang.cos()], dim=-1).to(dtype)
+    sin = torch.cat([ang.sin(), ang.sin()], dim=-1).to(dtype)
+    out = dl.get_op("fused_rotary_and_fa", (q, k, v, cos, sin))(
+        q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device)).cpu()
+    qr, kr = oracle.apply_rotary_pos_emb(q.reshape(b * s, h, d), k.reshape(b * s, h, d), cos.reshape(b * s, d),
+                                         sin.reshape(b * s, d))
+    ref = oracle.context_attention(qr, kr, v.reshape(b * s, h, d), torch.arange(b) * s, torch.full((b,), s),
+                                   causal=False)
+    torch.testing.assert_close(out.reshape(b * s, h, d).float(), ref.float(), rtol=2e-2, atol=2e-2)
