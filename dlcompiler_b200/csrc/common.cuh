@@ -73,6 +73,10 @@ PFN_encodeTiled get_encode_tiled();
 // Encode a 2-D row-major tensor map (inner dimension contiguous) for 16-bit
 // elements with the 128-byte swizzle; box = box_inner x box_outer elements.
 // Returns DLB_OK or a negative status with the message set.
+// 4-D tensor map over a paged cache [pages, slots, heads, d] (element strides), box = 64 x 1 x box_slots x 1,
+// 128-byte swizzle.
+int make_tmap_cache(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t slots, int64_t pages,
+                    int64_t stride_page, int64_t stride_slot, int64_t stride_head, int box_slots);
 int make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
 
@@ -199,6 +203,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)),
       "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
 // Pull a tile into L2 ahead of the load that will bring it to shared memory.

@@ -157,7 +157,20 @@ struct PrefillParams {
   uint32_t idesc_qk, idesc_pv;
   uint32_t v_lbo, v_sbo;          // MN-major descriptor strides of the V tile
   int* status;
+  // Paged K/V (prefill over a cache that already holds kv_seq_len - seq_len earlier tokens of each
+  // sequence): tmap_k / tmap_v are then 4-D maps over [pages, slots, heads, d] and the keys of a
+  // sequence are found through its row of the block table.
+  int paged;
+  int page_size, num_pages, max_pages;
+  const void* block_table;        // [batch, max_pages] int32 or int64
+  int64_t bt_stride;
+  int table_is_int64;
+  const int32_t* kv_seq_len;      // [batch]
 };
+
+__device__ __forceinline__ int table_entry(const void* t, int64_t i, int is64) {
+  return is64 ? (int)reinterpret_cast<const int64_t*>(t)[i] : reinterpret_cast<const int32_t*>(t)[i];
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(fp::THREADS, 2)
@@ -184,7 +197,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int q0 = tile * BM;
   if (q0 >= seq_len) return;
   const int start = p.b_start_loc[seq];
-  const int kv_end = p.causal ? min(seq_len, q0 + BM) : seq_len;
+  // query row r of the tile sits at position hist + q0 + r of its sequence (hist = tokens already cached)
+  const int kv_len = p.paged ? p.kv_seq_len[seq] : seq_len;
+  const int hist = kv_len - seq_len;
+  const int kv_end = p.causal ? min(kv_len, q0 + BM + hist) : kv_len;
   const int nb = (kv_end + BN - 1) / BN;
   const int kvh = head / p.group;
 
@@ -244,18 +260,45 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int row = start + j * BN;
+        // paged: the 64 keys of block j come from 64 / min(page, 64) pages of this sequence's table
+        const int box_slots = min(p.page_size, BN);
+        const int n_sub = p.paged ? BN / box_slots : 0;
+        int pg[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
+        for (int u = 0; u < n_sub; ++u) {
+          const int tok = j * BN + u * box_slots;
+          int page_slot = tok / p.page_size;
+          if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // past the table: any valid page, masked later
+          int page = table_entry(p.block_table, (int64_t)seq * p.bt_stride + page_slot, p.table_is_int64);
+          if (tok >= kv_len || page < 0 || page >= p.num_pages) page = 0;
+          pg[u] = page;
+          sl[u] = tok % p.page_size;
+        }
         // K stage s is free once the Q K^T of block j - 2 has retired (s_full), V stage s once its P V has
         // (pv_done): no separate "empty" commits, every commit costs the single issuing thread ~100 clocks
         if (!mbar_wait(&s_full[s], ph ^ 1, abort_flag, p.status, 21, j)) break;
         uint8_t* kd = smem + OFF_K + s * KV_BYTES;
         mbar_arrive_expect_tx(&k_full[s], KV_BYTES);
+        if (p.paged) {
+          for (int u = 0; u < n_sub; ++u)
 #pragma unroll
-        for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
+            for (int bx = 0; bx < BOXES; ++bx)
+              tma_load_4d(kd + bx * KV_BOX + u * box_slots * 128, &tmap_k, &k_full[s], bx * 64, kvh, sl[u], pg[u]);
+        } else {
+#pragma unroll
+          for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
+        }
         if (!mbar_wait(&pv_done[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
         uint8_t* vd = smem + OFF_V + s * KV_BYTES;
         mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
+        if (p.paged) {
+          for (int u = 0; u < n_sub; ++u)
 #pragma unroll
-        for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[s], bx * 64, kvh, row);
+            for (int bx = 0; bx < BOXES; ++bx)
+              tma_load_4d(vd + bx * KV_BOX + u * box_slots * 128, &tmap_v, &v_full[s], bx * 64, kvh, sl[u], pg[u]);
+        } else {
+#pragma unroll
+          for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[s], bx * 64, kvh, row);
+        }
       }
     }
   } else if (warp == WARP_MMA) {
@@ -335,14 +378,14 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
       // mask (diagonal / tail blocks only), on the raw scores
       const int key0 = j * BN;
-      const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0);
+      const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0 + hist);
       if (need_mask) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = key0 + h * 32 + c;
-            const bool visible = key < kv_end && (!p.causal || key <= q_pos);
+            const bool visible = key < kv_end && (!p.causal || key <= q_pos + hist);
             if (!visible) sr[h][c] = 0xff800000u;   // -inf
           }
         }
@@ -560,6 +603,101 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   p.v_lbo = KV_BOX;
   p.v_sbo = 1024;
   p.status = status;
+  p.paged = 0;
+  p.page_size = BN;
+  p.num_pages = p.max_pages = 0;
+  p.block_table = nullptr;
+  p.bt_stride = 0;
+  p.table_is_int64 = 0;
+  p.kv_seq_len = nullptr;
+
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc2;
+  if (dtype == DLB_DTYPE_BF16) {
+    rc2 = D == 128 ? launch_prefill<__nv_bfloat16, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__nv_bfloat16, 64>(tq, tk, tv, p, (unsigned)grid, s);
+  } else {
+    rc2 = D == 128 ? launch_prefill<__half, 128>(tq, tk, tv, p, (unsigned)grid, s)
+                   : launch_prefill<__half, 64>(tq, tk, tv, p, (unsigned)grid, s);
+  }
+  if (rc2 != DLB_OK) return rc2;
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
+                                       const void* block_table, const int32_t* q_start_loc,
+                                       const int32_t* q_seq_len, const int32_t* kv_seq_len, int64_t batch,
+                                       int64_t total_q_tokens, int64_t max_q_len, int64_t hq, int64_t hkv,
+                                       int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages,
+                                       int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_page,
+                                       int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
+                                       int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
+                                       int64_t o_stride_h, int64_t bt_stride, int table_is_int64, float sm_scale,
+                                       int causal, int dtype, int32_t* status, void* stream) {
+  using namespace dlb;
+  using namespace dlb::fp;
+  DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
+                "flash_prefill_paged: dtype %d (need fp16 or bf16)", dtype);
+  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
+                "flash_prefill_paged: head_dim %lld not supported (64 or 128)", (long long)head_dim);
+  const int D = (int)head_dim;
+  DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG,
+                "flash_prefill_paged: bad head counts");
+  DLB_CHECK_ARG(total_q_tokens >= 0 && max_q_len >= 0, DLB_ERR_BAD_ARG, "flash_prefill_paged: negative size");
+  DLB_CHECK_ARG(page_size >= 16 && (page_size & (page_size - 1)) == 0, DLB_ERR_UNSUPPORTED,
+                "flash_prefill_paged: page size %lld must be a power of two >= 16", (long long)page_size);
+  DLB_CHECK_ARG(num_pages >= 1 && max_pages >= 1, DLB_ERR_BAD_ARG, "flash_prefill_paged: empty cache or table");
+  if (batch == 0 || total_q_tokens == 0 || max_q_len == 0) return DLB_OK;
+  DLB_CHECK_ARG(q && k_cache && v_cache && out && block_table && q_start_loc && q_seq_len && kv_seq_len,
+                DLB_ERR_BAD_ARG, "flash_prefill_paged: null pointer");
+  DLB_CHECK_ARG(((uintptr_t)out & 15) == 0 && o_stride_t % 8 == 0 && o_stride_h % 8 == 0, DLB_ERR_ALIGNMENT,
+                "flash_prefill_paged: output must be 16-byte aligned with strides that are multiples of 8");
+  const int64_t max_tiles = (max_q_len + BM - 1) / BM;
+  const int64_t grid = max_tiles * batch * hq;
+  DLB_CHECK_ARG(grid <= 0x7fffffffLL && total_q_tokens < (1LL << 31), DLB_ERR_TOO_LARGE,
+                "flash_prefill_paged: grid too large");
+
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_tokens(&tq, q, D, hq, total_q_tokens, q_stride_h, q_stride_t, BM);
+  if (rc != DLB_OK) return rc;
+  const int box_slots = (int)(page_size < BN ? page_size : BN);
+  rc = make_tmap_cache(&tk, k_cache, D, hkv, page_size, num_pages, k_stride_page, k_stride_slot, k_stride_head,
+                       box_slots);
+  if (rc != DLB_OK) return rc;
+  rc = make_tmap_cache(&tv, v_cache, D, hkv, page_size, num_pages, v_stride_page, v_stride_slot, v_stride_head,
+                       box_slots);
+  if (rc != DLB_OK) return rc;
+
+  const uint32_t fmt = dtype == DLB_DTYPE_BF16 ? 1u : 0u;
+  PrefillParams p;
+  p.out = out;
+  p.lse = lse;
+  p.b_start_loc = q_start_loc;
+  p.b_seq_len = q_seq_len;
+  p.o_stride_t = o_stride_t;
+  p.o_stride_h = o_stride_h;
+  p.total_tokens = total_q_tokens;
+  p.batch = (int)batch;
+  p.hq = (int)hq;
+  p.hkv = (int)hkv;
+  p.group = (int)(hq / hkv);
+  p.max_tiles = (int)max_tiles;
+  p.causal = causal;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.idesc_qk = make_idesc_f16(BM, BN, fmt, 0u, 0u);
+  p.idesc_pv = make_idesc_f16(BM, D, fmt, 0u, 1u);
+  p.v_lbo = KV_BOX;
+  p.v_sbo = 1024;
+  p.status = status;
+  p.paged = 1;
+  p.page_size = (int)page_size;
+  p.num_pages = (int)num_pages;
+  p.max_pages = (int)max_pages;
+  p.block_table = block_table;
+  p.bt_stride = bt_stride;
+  p.table_is_int64 = table_is_int64;
+  p.kv_seq_len = kv_seq_len;
 
   cudaStream_t s = (cudaStream_t)stream;
   int rc2;

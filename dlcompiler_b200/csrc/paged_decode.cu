@@ -32,36 +32,6 @@ constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
 constexpr int STAGES = 3;
 }  // namespace pd
 
-// Encode a 4-D tensor map over a paged cache [pages, slots, heads, d] (element
-// strides given), box = 64 x 1 x box_slots x 1, 128-byte swizzle.
-static int make_tmap_cache(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t slots,
-                           int64_t pages, int64_t stride_page, int64_t stride_slot, int64_t stride_head,
-                           int box_slots) {
-  PFN_encodeTiled enc = get_encode_tiled();
-  DLB_CHECK_ARG(enc != nullptr, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
-  DLB_CHECK_ARG(((uintptr_t)base & 15) == 0, DLB_ERR_ALIGNMENT, "cache base is not 16-byte aligned");
-  DLB_CHECK_ARG((stride_page * 2) % 16 == 0 && (stride_slot * 2) % 16 == 0 && (stride_head * 2) % 16 == 0,
-                DLB_ERR_ALIGNMENT, "cache strides must be multiples of 16 bytes");
-  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)slots, (cuuint64_t)pages};
-  cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_slot * 2, (cuuint64_t)stride_page * 2};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_slots, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  DLB_CHECK_ARG(r == CUDA_SUCCESS, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled(cache) failed with CUresult %d", (int)r);
-  return DLB_OK;
-}
-
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1,
-                                            int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(smem_dst)),
-      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)

@@ -71,6 +71,28 @@ int make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t inner, uint64_
   return DLB_OK;
 }
 
+// Encode a 4-D tensor map over a paged cache [pages, slots, heads, d] (element
+// strides given), box = 64 x 1 x box_slots x 1, 128-byte swizzle.
+int make_tmap_cache(CUtensorMap* out, const void* base, int64_t d, int64_t heads, int64_t slots,
+                           int64_t pages, int64_t stride_page, int64_t stride_slot, int64_t stride_head,
+                           int box_slots) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  DLB_CHECK_ARG(enc != nullptr, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the driver");
+  DLB_CHECK_ARG(((uintptr_t)base & 15) == 0, DLB_ERR_ALIGNMENT, "cache base is not 16-byte aligned");
+  DLB_CHECK_ARG((stride_page * 2) % 16 == 0 && (stride_slot * 2) % 16 == 0 && (stride_head * 2) % 16 == 0,
+                DLB_ERR_ALIGNMENT, "cache strides must be multiples of 16 bytes");
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)slots, (cuuint64_t)pages};
+  cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_slot * 2, (cuuint64_t)stride_page * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_slots, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DLB_CHECK_ARG(r == CUDA_SUCCESS, DLB_ERR_DRIVER, "cuTensorMapEncodeTiled(cache) failed with CUresult %d", (int)r);
+  return DLB_OK;
+}
+
+
 }  // namespace dlb
 
 extern "C" {

@@ -35,14 +35,17 @@ def paged_attention_fwd(
     sm_scale: float = None,
     logit_softcapping: float = None,
 ):
-    """Paged attention forward, decode case (one query token per sequence).
+    """Paged attention forward.
 
-    Args follow the reference (paged_attention.py:492-519): `q` [batch, Hq, D], caches
-    `k`/`v` [num_pages, page_size, Hkv, D], `o` written in place, `block_offsets`
-    [batch, max_pages] page ids (int32 or int64), `kv_seqlens` [batch].  The KV length is
-    split in fixed-size chunks (count adapts to each sequence) and merged by log-sum-exp.
-    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power
-    of two >= 16, decode only (q_seqlens all 1).
+    Args follow the reference (paged_attention.py:492-519): caches `k`/`v` [num_pages, page_size, Hkv, D],
+    `o` written in place, `block_offsets` [batch, max_pages] page ids (int32 or int64), `kv_seqlens`
+    [batch].  Decode (`q` [batch, Hq, D], one query token per sequence, paged_attention.py:559): the KV
+    length is split in fixed-size chunks (count adapts to each sequence) and merged by log-sum-exp.
+    Prefill (`q` [total_q, Hq, D] packed by `q_start_loc` / `q_seqlens`): query i of a sequence sits at
+    position `kv_seqlens - q_seqlens + i` and attends causally to the cache, which must already hold the
+    new tokens' K/V (fill_kv_cache runs first, as in the reference's callers).
+    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power of two >= 16;
+    sliding window and soft-cap in decode only.
     """
     dev = _lib.require_cuda(q, k, v, o, block_offsets, kv_seqlens)
     if window_size is None:
@@ -57,9 +60,10 @@ def paged_attention_fwd(
     BLOCK = k.size(1)
     assert BLOCK >= 16
     is_decoding = q.shape[-3] == q_seqlens.size(0)
+    assert Lk == Lv, "the kernels need equal K and V head sizes"
     if not is_decoding:
-        raise NotImplementedError("paged prefill with history is outside this implementation (decode only)")
-    assert Lk == Lv, "decode kernel needs equal K and V head sizes"
+        return _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens, max_seqlen,
+                              window_size, sm_scale, logit_softcapping, dev)
     assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert q.stride(-1) == 1 and o.stride(-1) == 1
     assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
@@ -87,4 +91,32 @@ def paged_attention_fwd(
             chunk, max_splits, window_size, float(sm_scale), float(logit_softcapping), _lib.dtype_code(q),
             status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "paged_attention_fwd(decode)")
+    return o
+
+
+def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens, max_seqlen, window_size, sm_scale,
+                   logit_softcapping, dev):
+    """Prefill branch of paged_attention_fwd (paged_attention.py:617-671): the tcgen05 prefill kernel with
+    its K/V tiles fetched page by page."""
+    if window_size > 0 or logit_softcapping > 0:
+        raise NotImplementedError("sliding window / soft-cap are implemented for decode only")
+    assert q.dim() == 3 and o.shape == q.shape and q.stride(-1) == 1 and o.stride(-1) == 1
+    assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
+    assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
+    assert block_offsets.dtype in (torch.int32, torch.int64)
+    batch = q_seqlens.shape[0]
+    q_start = q_start_loc.to(device=dev, dtype=torch.int32).contiguous()
+    q_len = q_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+    kv_len = kv_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+    lib = _lib.load()
+    status = _lib.status_word(dev)
+    with torch.cuda.device(dev):
+        rc = lib.dlb_flash_prefill_paged(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, block_offsets.data_ptr(),
+            q_start.data_ptr(), q_len.data_ptr(), kv_len.data_ptr(), batch, q.shape[0], int(max_seqlen),
+            q.shape[1], k.shape[2], q.shape[2], k.size(1), k.size(0), block_offsets.size(1),
+            q.stride(0), q.stride(1), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
+            o.stride(0), o.stride(1), block_offsets.stride(0), int(block_offsets.dtype == torch.int64),
+            float(sm_scale), 1, _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "paged_attention_fwd(prefill)")
     return o

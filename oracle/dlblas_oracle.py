@@ -392,6 +392,40 @@ def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_sc
     return out
 
 
+def paged_prefill_attention(q, k_cache, v_cache, block_offsets, q_start_loc, q_seqlens, kv_seqlens, sm_scale=None):
+    """Prefill over a paged cache that already holds `kv_seqlens - q_seqlens` earlier tokens per sequence
+    (ground truth of test_paged_attention.py:61-84 with the causal mask of :14-25 shifted by the history
+    length, as the kernel does at paged_attention.py:362).  q [total_q, Hq, D] packed by sequence; query i
+    of a sequence sits at position history + i and sees keys 0 .. history + i.  Scores and softmax in
+    fp32, P cast to the value dtype before P.V."""
+    total, hq, d = q.shape
+    page = k_cache.shape[1]
+    hkv = k_cache.shape[2]
+    group = hq // hkv
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    out = torch.zeros(total, hq, v_cache.shape[-1], dtype=q.dtype)
+    for b in range(len(q_seqlens)):
+        nq, n = int(q_seqlens[b]), int(kv_seqlens[b])
+        if nq == 0:
+            continue
+        s0 = int(q_start_loc[b])
+        hist = n - nq
+        npg = (n + page - 1) // page
+        pages = block_offsets[b, :npg].to(torch.int64)
+        ks = k_cache[pages].reshape(npg * page, hkv, -1)[:n]
+        vs = v_cache[pages].reshape(npg * page, hkv, -1)[:n]
+        kf = ks.transpose(0, 1).repeat_interleave(group, 0).float()      # [hq, n, d]
+        vf = vs.transpose(0, 1).repeat_interleave(group, 0)
+        qf = q[s0:s0 + nq].transpose(0, 1).float()                        # [hq, nq, d]
+        sc = torch.matmul(qf, kf.transpose(1, 2)) * sm_scale              # [hq, nq, n]
+        pos = torch.arange(nq)[:, None] + hist
+        sc = sc.masked_fill(torch.arange(n)[None, :] > pos, float("-inf"))
+        p = torch.softmax(sc, dim=-1, dtype=torch.float32).to(vf.dtype)
+        out[s0:s0 + nq] = torch.matmul(p.float(), vf.float()).transpose(0, 1).to(q.dtype)
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # rms_norm, rotary embedding, fill_kv_cache (the steps next to the hot path)
 # --------------------------------------------------------------------------------------

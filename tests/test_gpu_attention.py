@@ -276,3 +276,68 @@ def test_decode_attention_fwd_token_granular(cuda_device, hq, hkv, cap):
     ref = oracle.paged_decode_attention(q, kb.unsqueeze(1), vb.unsqueeze(1), req_to_token[b_req_idx], lens,
                                         sm_scale=D ** -0.5, logit_softcapping=cap if cap > 0 else None)
     torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+# ------------------------------------------------------------------ prefill over a paged cache with history
+def _paged_prefill_case(seed, q_lens, hist_lens, page, hq, hkv, D, dtype, table_dtype=torch.int32):
+    g = torch.Generator().manual_seed(seed)
+    q_lens, hist_lens = torch.tensor(q_lens), torch.tensor(hist_lens)
+    kv_lens = q_lens + hist_lens
+    pages_per_seq = (kv_lens + page - 1) // page
+    total_pages = int(pages_per_seq.sum())
+    perm = torch.randperm(total_pages + 3, generator=g)          # a few pages stay unused
+    table = torch.zeros(len(q_lens), int(pages_per_seq.max()) + 1, dtype=table_dtype)
+    k_cache = torch.randn(total_pages + 3, page, hkv, D, generator=g).to(dtype)
+    v_cache = torch.randn(total_pages + 3, page, hkv, D, generator=g).to(dtype)
+    at = 0
+    for b, n in enumerate(pages_per_seq.tolist()):
+        table[b, :n] = perm[at:at + n].to(table_dtype)
+        at += n
+    q = torch.randn(int(q_lens.sum()), hq, D, generator=g).to(dtype)
+    q_start = torch.cumsum(q_lens, 0) - q_lens
+    return dict(q=q, k_cache=k_cache, v_cache=v_cache, table=table, q_start=q_start, q_lens=q_lens, kv_lens=kv_lens)
+
+
+@pytest.mark.parametrize("q_lens,hist_lens,page,hq,hkv,D,dtype,tdt", [
+    ([5, 130, 64], [0, 0, 0], 64, 8, 2, 128, torch.bfloat16, torch.int32),          # no history: plain prefill
+    ([3, 200, 1, 77], [100, 37, 500, 64], 64, 8, 2, 128, torch.bfloat16, torch.int64),
+    ([129, 16], [63, 1000], 16, 4, 4, 64, torch.float16, torch.int32),              # four pages per key block
+    ([300, 2], [129, 31], 128, 8, 1, 128, torch.float16, torch.int32),              # two key blocks per page
+    ([40], [24], 32, 2, 2, 64, torch.bfloat16, torch.int64),
+])
+def test_paged_prefill_with_history(cuda_device, q_lens, hist_lens, page, hq, hkv, D, dtype, tdt):
+    """The prefill branch of paged_attention_fwd: new tokens attend causally to a cache that already holds
+    their own K/V and `hist` earlier tokens, against the oracle's masked naive attention."""
+    d = _paged_prefill_case(sum(q_lens) + page, q_lens, hist_lens, page, hq, hkv, D, dtype, tdt)
+    dev = cuda_device
+    q = d["q"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["table"].to(dev), d["q_start"].to(dev),
+                        d["q_lens"].to(dev), d["kv_lens"].to(dev), int(max(q_lens)))
+    ref = oracle.paged_prefill_attention(d["q"], d["k_cache"], d["v_cache"], d["table"], d["q_start"], d["q_lens"],
+                                         d["kv_lens"])
+    out = o.cpu()
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_paged_prefill_equals_contiguous_prefill(cuda_device):
+    """Without history the paged branch and context_attention_fwd see the same keys in the same 64-key
+    blocks, so their outputs are bit-identical."""
+    d = _paged_prefill_case(3, [257, 64, 90], [0, 0, 0], 64, 8, 2, 128, torch.bfloat16)
+    dev = cuda_device
+    q = d["q"].to(dev)
+    o = torch.empty_like(q)
+    paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["table"].to(dev), d["q_start"].to(dev),
+                        d["q_lens"].to(dev), d["kv_lens"].to(dev), 257)
+    # the same K/V, token-contiguous
+    ks, vs = [], []
+    for b, n in enumerate(d["kv_lens"].tolist()):
+        npg = (n + 63) // 64
+        pages = d["table"][b, :npg].long()
+        ks.append(d["k_cache"][pages].reshape(npg * 64, 2, 128)[:n])
+        vs.append(d["v_cache"][pages].reshape(npg * 64, 2, 128)[:n])
+    o2 = torch.empty_like(q)
+    context_attention_fwd(q, torch.cat(ks).to(dev), torch.cat(vs).to(dev), o2, d["q_start"].int().to(dev),
+                          d["q_lens"].int().to(dev), 257)
+    assert torch.equal(o, o2)
