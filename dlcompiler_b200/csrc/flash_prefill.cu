@@ -8,19 +8,21 @@
 // (natural log, scale included).
 //
 // One CTA = one (sequence, q-head, 128-query tile); two CTAs are resident per
-// SM (256 TMEM columns and ~113 KiB of shared memory each), so one CTA's
-// softmax overlaps the other's MMAs.  Inside a CTA, 192 threads (168 registers each; moving registers
-// to the softmax warps with setmaxnreg was tried: ptxas keeps allocating under the launch bound and spills):
+// SM (256 TMEM columns and ~97 KiB of shared memory each), so one CTA's
+// softmax overlaps the other's MMAs.  Inside a CTA, 192 threads (moving registers to the softmax warps
+// with setmaxnreg was tried: ptxas keeps allocating under the launch bound and spills):
 //   warp 4     TMA producer: Q tile once, then K and V tiles of 64 keys into
-//              2-stage rings (3-D tensor maps over [token, head, d], 128-byte swizzle)
+//              2-stage rings (3-D tensor maps over [token, head, d], 128-byte swizzle; for a paged
+//              cache 4-D maps over [page, slot, head, d] and one box per page of the block)
 //   warp 5     one lane issues tcgen05.mma: S_j = Q K_j^T (M128 N64 K16 x 8) into
 //              a double-buffered TMEM S, then O += P_{j-1} V_{j-1}
-//              (M128 N128 K16 x 4, V as an MN-major operand straight from the
-//              row-major tile), software-pipelined so S_j is computed while
-//              the softmax of block j-1 runs
+//              (M128 N128 K16 x 4, P as the A operand from TMEM, V as an MN-major operand
+//              straight from the row-major tile), software-pipelined so S_j is computed while
+//              the softmax of block j-1 runs; two commits per block (s_full also frees the K
+//              stage, pv_done the V stage)
 //   warps 0-3  softmax: one thread per query row reads its S row from TMEM
-//              (tcgen05.ld), online softmax in the base-2 domain, writes P
-//              (16-bit, swizzled K-major) to shared memory for the next MMA,
+//              (tcgen05.ld), online softmax in the base-2 domain, writes P back with
+//              tcgen05.st as 16-bit pairs over the first 32 columns of the same S buffer,
 //              rescales O in TMEM only when the row max grew by more than
 //              2^8 (lazy rescaling), and finally normalises and stores O
 // CTAs are ordered (sequence, kv head) group by group, heavy causal tiles first inside a group, so the
