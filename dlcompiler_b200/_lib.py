@@ -32,6 +32,7 @@ SIGNATURES = {
                                   c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p]),
     "dlb_gshard_gate_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "dlb_gshard_gate_bwd_weights": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int64, c_void_p]),
     "dlb_moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
                                          c_int64, c_void_p, c_void_p, c_void_p]),
     "dlb_moe_permute_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64,

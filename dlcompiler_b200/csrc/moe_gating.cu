@@ -506,6 +506,65 @@ __global__ void __launch_bounds__(256) gshard_bwd_kernel(const float* __restrict
   }
 }
 
+// Backward through the routing weights as well (the reference's `higher_precision` path,
+// python/dlBLAS/dlblas/kernels/topk_gating.py:145-256): with g_k the kept gate values of a token,
+// D = sum_k g_k, C = max(D, eps) and w_k = g_k / C,
+//   d loss / d g_k = gw_k / C - [D >= eps] * sum_j gw_j g_j / C^2        (kept choices only)
+// is scattered to the chosen experts, the auxiliary-loss term grad_l_aux * ce[e] * E / S is added, and
+// the result goes through the softmax backward  grad_logits_i = g_i * (gg_i - sum_j g_j gg_j).
+// One warp per token; lane k < K holds choice k.
+__global__ void __launch_bounds__(256) gshard_bwd_weights_kernel(
+    const float* __restrict__ gates, const float* __restrict__ ce, const float* __restrict__ grad_l_aux,
+    const int32_t* __restrict__ ids_km, const int32_t* __restrict__ loc, const float* __restrict__ grad_weights,
+    float* __restrict__ grad_logits, int64_t S, int E, int K, int capacity, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (s >= S) return;
+  const float scale = grad_l_aux[0] * (float)E / (float)S;
+  int my_e = -1;
+  float my_g = 0.f, my_gw = 0.f;
+  if (lane < K) {
+    const int e = ids_km[(int64_t)lane * S + s];
+    if (loc[(int64_t)lane * S + s] < capacity) {
+      my_e = e;
+      my_g = gates[s * E + e];
+      my_gw = grad_weights[(int64_t)lane * S + s];
+    }
+  }
+  float denom = my_g, cross = my_gw * my_g;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    cross += __shfl_xor_sync(0xffffffffu, cross, o);
+  }
+  const float c = fmaxf(denom, eps);
+  const float common = denom >= eps ? -cross / (c * c) : 0.f;
+  const float my_d = my_e >= 0 ? my_gw / c + common : 0.f;     // d loss / d gate of my choice
+  float dot = 0.f;
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int e = e0 + lane;
+    float gg = e < E ? ce[e] * scale : 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int ek = __shfl_sync(0xffffffffu, my_e, k);
+      const float dk = __shfl_sync(0xffffffffu, my_d, k);
+      if (ek == e) gg += dk;
+    }
+    if (e < E) dot += gates[s * E + e] * gg;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int e = e0 + lane;
+    float gg = e < E ? ce[e] * scale : 0.f;
+    for (int k = 0; k < K; ++k) {
+      const int ek = __shfl_sync(0xffffffffu, my_e, k);
+      const float dk = __shfl_sync(0xffffffffu, my_d, k);
+      if (ek == e) gg += dk;
+    }
+    if (e < E) grad_logits[s * E + e] = gates[s * E + e] * (gg - dot);
+  }
+}
+
 }  // namespace dlb
 
 extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, int32_t* ids, float* weights,
@@ -618,6 +677,26 @@ extern "C" int dlb_gshard_gate_bwd(const float* gates, const float* ce, const fl
   DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gshard_gate_bwd: too many tokens");
   gshard_bwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(gates, ce, grad_l_aux, grad_logits, tokens,
                                                                         experts);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_gshard_gate_bwd_weights(const float* gates, const float* ce, const float* grad_l_aux,
+                                           const int32_t* ids_choice_major, const int32_t* loc,
+                                           const float* grad_weights, float* grad_logits, int64_t tokens, int experts,
+                                           int top_k, int64_t capacity, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0 && experts >= 1 && top_k >= 1 && top_k <= 32 && capacity >= 1, DLB_ERR_BAD_ARG,
+                "gshard_gate_bwd_weights: bad sizes");
+  if (tokens == 0) return DLB_OK;
+  DLB_CHECK_ARG(gates && ce && grad_l_aux && ids_choice_major && loc && grad_weights && grad_logits, DLB_ERR_BAD_ARG,
+                "gshard_gate_bwd_weights: null pointer");
+  DLB_CHECK_ARG(capacity < (1LL << 31), DLB_ERR_TOO_LARGE, "gshard_gate_bwd_weights: capacity too large");
+  const int64_t blocks = (tokens + 7) / 8;
+  DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gshard_gate_bwd_weights: too many tokens");
+  gshard_bwd_weights_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      gates, ce, grad_l_aux, ids_choice_major, loc, grad_weights, grad_logits, tokens, experts, top_k, (int)capacity,
+      1.1920928955078125e-07f);
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }

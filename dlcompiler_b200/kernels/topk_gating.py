@@ -49,23 +49,43 @@ class TopKGatingFunc(torch.autograd.Function):
                                              loc.data_ptr(), me.data_ptr(), ce.data_ptr(), l_aux.data_ptr(),
                                              ec_idx.data_ptr(), weights.data_ptr(), select.data_ptr(), stream),
                        "topk_gating(assign)")
-        ctx.save_for_backward(gates, ce)
         ctx.out_dtype = logits.dtype
+        ctx.higher_precision = bool(higher_precision)
         ctx.mark_non_differentiable(ec_idx, select)
+        if higher_precision:
+            ctx.save_for_backward(gates, ce, ids_km, loc)
+            ctx.top_k, ctx.capacity = k, capacity
+        else:
+            ctx.save_for_backward(gates, ce)
         return l_aux.to(logits.dtype), ec_idx, weights.to(logits.dtype), select
 
     @staticmethod
-    def backward(ctx, grad_l_aux, *unused):
-        # as in the reference's default path, only the auxiliary loss back-propagates (topk_gating.py:279-284)
-        gates, ce = ctx.saved_tensors
+    def backward(ctx, grad_l_aux, grad_ec_idx=None, grad_weights=None, grad_select=None):
+        gates = ctx.saved_tensors[0]
+        ce = ctx.saved_tensors[1]
         dev = gates.device
         S, E = gates.shape
-        g = grad_l_aux.float().reshape(1).contiguous()
+        g = (torch.zeros(1, device=dev) if grad_l_aux is None else grad_l_aux.float().reshape(1)).contiguous()
         grad_logits = torch.empty_like(gates)
         lib = _lib.load()
         with torch.cuda.device(dev):
-            _lib.check(lib.dlb_gshard_gate_bwd(gates.data_ptr(), ce.data_ptr(), g.data_ptr(), grad_logits.data_ptr(),
-                                               S, E, _lib.stream_ptr(dev)), "topk_gating(backward)")
+            if ctx.higher_precision:
+                # the routing weights back-propagate too (topk_gating.py:286-294).  The gradient is the exact
+                # derivative of weights = kept gate / max(sum of kept gates, eps); the reference's kernel divides
+                # the saved, already normalised gates by the denominator twice more (topk_gating.py:164-166 with
+                # gate_ks stored after the division at :75-77), which is not the derivative of its own forward.
+                ids_km, loc = ctx.saved_tensors[2], ctx.saved_tensors[3]
+                gw = (torch.zeros(ctx.top_k * S, device=dev) if grad_weights is None
+                      else grad_weights.float().reshape(-1)).contiguous()
+                _lib.check(lib.dlb_gshard_gate_bwd_weights(gates.data_ptr(), ce.data_ptr(), g.data_ptr(),
+                                                           ids_km.data_ptr(), loc.data_ptr(), gw.data_ptr(),
+                                                           grad_logits.data_ptr(), S, E, ctx.top_k, ctx.capacity,
+                                                           _lib.stream_ptr(dev)), "topk_gating(backward, weights)")
+            else:
+                # as in the reference's default path, only the auxiliary loss back-propagates (topk_gating.py:279-284)
+                _lib.check(lib.dlb_gshard_gate_bwd(gates.data_ptr(), ce.data_ptr(), g.data_ptr(),
+                                                   grad_logits.data_ptr(), S, E, _lib.stream_ptr(dev)),
+                           "topk_gating(backward)")
         return grad_logits.to(ctx.out_dtype), None, None, None, None
 
 

@@ -79,6 +79,15 @@ int dlb_gshard_assign(const float* gates, const int32_t* ids_choice_major, const
                       int32_t* ec_idx, float* weights, int64_t* expert_select_token_idx, void* stream);
 int dlb_gshard_gate_bwd(const float* gates, const float* ce, const float* grad_l_aux, float* grad_logits,
                         int64_t tokens, int experts, void* stream);
+/* Backward of topk_gating's `higher_precision` mode (python/dlBLAS/dlblas/kernels/topk_gating.py:145-256,
+ * 286-294): the gradient of the routing weights (grad_weights, fp32 [top_k * tokens], choice-major) flows
+ * through weights = kept gate / max(sum of kept gates, fp32 eps) back to the gates, the auxiliary-loss
+ * term is added, and the sum goes through the softmax backward.  ids_choice_major / loc as produced by
+ * dlb_gshard_gate / dlb_gshard_assign. */
+int dlb_gshard_gate_bwd_weights(const float* gates, const float* ce, const float* grad_l_aux,
+                                const int32_t* ids_choice_major, const int32_t* loc, const float* grad_weights,
+                                float* grad_logits, int64_t tokens, int experts, int top_k, int64_t capacity,
+                                void* stream);
 
 /* moe_align_block_size: stable counting sort of the numel (token, k) slots by expert id, each expert
  * segment padded to a multiple of `block` with the sentinel `numel`.  Block-padded form of the

@@ -536,3 +536,32 @@ def topk_gating_backward(logits, k, grad_l_aux=1.0):
     l_aux = torch.mean(gates.mean(dim=0) * ce) * E * E
     l_aux.backward(torch.tensor(grad_l_aux))
     return x.grad
+
+
+def topk_gating_backward_weights(logits, k, capacity_factor=1.0, min_capacity=2, grad_l_aux=1.0, grad_weights=None):
+    """d (grad_l_aux * l_aux + sum(grad_weights * token_exp_weights)) / d logits by autograd through the
+    forward expression of `topk_gating` above, in fp64 (the routing decisions -- ids, queue positions,
+    capacity drops -- do not depend on the logits differentiably).  This is the gradient the reference's
+    `higher_precision` backward (python/dlBLAS/dlblas/kernels/topk_gating.py:145-256) sets out to compute."""
+    x = logits.double().clone().requires_grad_(True)
+    S, E = x.shape
+    gates = F.softmax(x, dim=1)
+    capacity = int(torch.ceil((S / E) * torch.tensor(capacity_factor * k)).to(torch.int64))
+    capacity = max(capacity, int(min_capacity))
+    _, idx = _stable_topk(logits.float(), k)
+    idx_km = idx.t().reshape(-1)
+    masks = F.one_hot(idx_km, num_classes=E)
+    locations = (torch.cumsum(masks, dim=0) - 1).reshape(k, S, E)
+    masks = masks.reshape(k, S, E)
+    ce = masks[0].double().mean(dim=0)
+    l_aux = torch.mean(gates.mean(dim=0) * ce) * E * E
+    masks = masks * torch.lt(locations, capacity)
+    gate_s = (gates * masks.double()).sum(dim=2)                  # one non-zero term per (choice, token)
+    denom = torch.clamp(gate_s.sum(dim=0), min=torch.finfo(torch.float32).eps)
+    w = (gate_s / denom).reshape(-1)
+    loss = grad_l_aux * l_aux
+    if grad_weights is not None:
+        loss = loss + (grad_weights.double() * w).sum()
+    loss.backward()
+    return x.grad.float()
+

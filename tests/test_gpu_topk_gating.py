@@ -51,3 +51,23 @@ def test_topk_gating_backward(cuda_device):
     (l_aux * 3.0).backward()
     ref = oracle.topk_gating_backward(logits, 8, grad_l_aux=3.0)
     torch.testing.assert_close(x.grad.cpu(), ref, rtol=1e-4, atol=1e-8)
+
+
+@pytest.mark.parametrize("S,E,k,cf", [(512, 64, 8, 1.0), (300, 8, 2, 0.5), (64, 16, 4, 2.0)])
+def test_topk_gating_backward_through_weights(cuda_device, S, E, k, cf):
+    """`higher_precision=True`: the routing weights back-propagate as well; against autograd through the
+    oracle's forward expression (capacity drops included: cf = 0.5 drops about half of the choices)."""
+    g = torch.Generator().manual_seed(S + k)
+    logits = torch.randn(S, E, generator=g)
+    gw = torch.randn(k * S, generator=g)
+    x = logits.to(cuda_device).requires_grad_(True)
+    l_aux, _, w, _ = topk_gating(x, k, cf, 2, True)
+    (l_aux * 1.5 + (w * gw.to(cuda_device)).sum()).backward()
+    ref = oracle.topk_gating_backward_weights(logits, k, cf, 2, grad_l_aux=1.5, grad_weights=gw)
+    torch.testing.assert_close(x.grad.cpu(), ref, rtol=2e-4, atol=2e-6)
+    # the default mode still ignores the weights' gradient, as the reference does
+    y = logits.to(cuda_device).requires_grad_(True)
+    l2, _, w2, _ = topk_gating(y, k, cf, 2, False)
+    (l2 * 1.5 + (w2 * gw.to(cuda_device)).sum()).backward()
+    torch.testing.assert_close(y.grad.cpu(), oracle.topk_gating_backward(logits, k, grad_l_aux=1.5), rtol=1e-4,
+                               atol=1e-8)
