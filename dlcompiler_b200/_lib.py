@@ -57,8 +57,8 @@ SIGNATURES = {
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_float, c_int, c_int, c_void_p, c_void_p]),
-    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 20 + [c_int, c_float, c_int, c_int, c_void_p,
-                                                                      c_void_p]),
+    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 20 + [c_int, c_int64, c_float, c_float, c_int, c_int,
+                                                                      c_void_p, c_void_p]),
     "dlb_paged_decode_workspace_floats": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "dlb_paged_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -29,6 +29,8 @@
 // resident CTAs share K/V through L2 and the tail of each group is short.
 #include <math_constants.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace dlb {
@@ -168,13 +170,17 @@ struct PrefillParams {
   int64_t bt_stride;
   int table_is_int64;
   const int32_t* kv_seq_len;      // [batch]
+  // Extras of the paged prefill branch (kernel instantiated with EXTRAS only when one is on):
+  int window;                     // > 0: query at position pos sees keys pos - window .. pos (paged_attention.py:421-424,447)
+  float softcap;                  // > 0: scores become softcap * tanh(score * sm_scale / softcap) (paged_attention.py:441-444)
+  float sm_scale;
 };
 
 __device__ __forceinline__ int table_entry(const void* t, int64_t i, int is64) {
   return is64 ? (int)reinterpret_cast<const int64_t*>(t)[i] : reinterpret_cast<const int32_t*>(t)[i];
 }
 
-template <typename T, int D>
+template <typename T, int D, bool EXTRAS>
 __global__ void __launch_bounds__(fp::THREADS, 2)
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
@@ -203,7 +209,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int kv_len = p.paged ? p.kv_seq_len[seq] : seq_len;
   const int hist = kv_len - seq_len;
   const int kv_end = p.causal ? min(kv_len, q0 + BM + hist) : kv_len;
-  const int nb = (kv_end + BN - 1) / BN;
+  // with a sliding window the tile starts at the block that holds the first key its first row may see;
+  // `j` below counts blocks from there, jb0 + j is the block's index in the sequence
+  const int jb0 = (EXTRAS && p.window > 0) ? max(0, q0 + hist - p.window) / BN : 0;
+  const int nb = (kv_end + BN - 1) / BN - jb0;
   const int kvh = head / p.group;
 
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -261,13 +270,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int row = start + j * BN;
+        const int row = start + (jb0 + j) * BN;
         // paged: the 64 keys of block j come from 64 / min(page, 64) pages of this sequence's table
         const int box_slots = min(p.page_size, BN);
         const int n_sub = p.paged ? BN / box_slots : 0;
         int pg[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
         for (int u = 0; u < n_sub; ++u) {
-          const int tok = j * BN + u * box_slots;
+          const int tok = (jb0 + j) * BN + u * box_slots;
           int page_slot = tok / p.page_size;
           if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // past the table: any valid page, masked later
           int page = table_entry(p.block_table, (int64_t)seq * p.bt_stride + page_slot, p.table_is_int64);
@@ -378,16 +387,30 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_32x32b_x32(tmem_base + lane_field + s * BN + 32, sr[1]);
       tmem_wait_ld();
 
-      // mask (diagonal / tail blocks only), on the raw scores
-      const int key0 = j * BN;
-      const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0 + hist);
+      // soft-cap: the scores go to the log2 domain here (cap * tanh(s * sm_scale / cap) * log2 e) and the scale
+      // applied further down becomes 1
+      float eff_scale = p.scale_log2;
+      if (EXTRAS && p.softcap > 0.f) {
+        const float inv = p.sm_scale / p.softcap, capl2 = p.softcap * 1.4426950408889634f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            sr[h][c] = __float_as_uint(capl2 * tanhf(__uint_as_float(sr[h][c]) * inv));
+        eff_scale = 1.f;
+      }
+      // mask (diagonal / tail / window-edge blocks only)
+      const int key0 = (jb0 + j) * BN;
+      const int win_lo = (EXTRAS && p.window > 0) ? q_pos + hist - p.window : -(1 << 30);   // first visible key
+      const bool need_mask = (key0 + BN > kv_end) || (p.causal && key0 + BN - 1 > q0 + hist) ||
+                             (EXTRAS && p.window > 0 && key0 < q0 + BM + hist - p.window);
       if (need_mask) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = key0 + h * 32 + c;
-            const bool visible = key < kv_end && (!p.causal || key <= q_pos + hist);
+            const bool visible = key < kv_end && (!p.causal || key <= q_pos + hist) && key >= win_lo;
             if (!visible) sr[h][c] = 0xff800000u;   // -inf
           }
         }
@@ -404,7 +427,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
       float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]);
-      mx *= p.scale_log2;
+      mx *= eff_scale;
       // lazy rescale decision
       float alpha = 1.f;
       bool rescale = false;
@@ -440,7 +463,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       // back to TMEM over the first columns of the S buffer it came from, where the P.V MMA reads it
       // as its A operand
       const float neg_m = (m_ref == -CUDART_INF_F) ? 0.f : -m_ref;
-      const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
+      const uint64_t scale2 = pack_f2(eff_scale, eff_scale);
       const uint64_t negm2 = pack_f2(neg_m, neg_m);
       uint64_t sum2a = pack_f2(0.f, 0.f), sum2b = sum2a;
 #pragma unroll
@@ -532,10 +555,10 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
 }
 
-template <typename T, int D>
-static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
-                          unsigned grid, cudaStream_t stream) {
-  auto kern = flash_prefill_kernel<T, D>;
+template <typename T, int D, bool EXTRAS>
+static int launch_prefill_x(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                            const PrefillParams& p, unsigned grid, cudaStream_t stream) {
+  auto kern = flash_prefill_kernel<T, D, EXTRAS>;
   constexpr int SMEM = fp::Layout<D>::SMEM_BYTES;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) {
@@ -544,6 +567,12 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   }
   kern<<<grid, fp::THREADS, SMEM, stream>>>(tq, tk, tv, p);
   return DLB_OK;
+}
+template <typename T, int D>
+static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const PrefillParams& p,
+                          unsigned grid, cudaStream_t stream) {
+  return (p.window > 0 || p.softcap > 0.f) ? launch_prefill_x<T, D, true>(tq, tk, tv, p, grid, stream)
+                                           : launch_prefill_x<T, D, false>(tq, tk, tv, p, grid, stream);
 }
 
 }  // namespace dlb
@@ -612,6 +641,9 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   p.bt_stride = 0;
   p.table_is_int64 = 0;
   p.kv_seq_len = nullptr;
+  p.window = 0;
+  p.softcap = 0.f;
+  p.sm_scale = sm_scale;
 
   cudaStream_t s = (cudaStream_t)stream;
   int rc2;
@@ -635,8 +667,9 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
                                        int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_page,
                                        int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
                                        int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
-                                       int64_t o_stride_h, int64_t bt_stride, int table_is_int64, float sm_scale,
-                                       int causal, int dtype, int32_t* status, void* stream) {
+                                       int64_t o_stride_h, int64_t bt_stride, int table_is_int64, int64_t window,
+                                       float sm_scale, float softcap, int causal, int dtype, int32_t* status,
+                                       void* stream) {
   using namespace dlb;
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
@@ -700,6 +733,9 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
   p.bt_stride = bt_stride;
   p.table_is_int64 = table_is_int64;
   p.kv_seq_len = kv_seq_len;
+  p.window = window > 0 ? (int)std::min<int64_t>(window, 1 << 29) : 0;
+  p.softcap = softcap;
+  p.sm_scale = sm_scale;
 
   cudaStream_t s = (cudaStream_t)stream;
   int rc2;

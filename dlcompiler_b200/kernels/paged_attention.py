@@ -44,8 +44,8 @@ def paged_attention_fwd(
     Prefill (`q` [total_q, Hq, D] packed by `q_start_loc` / `q_seqlens`): query i of a sequence sits at
     position `kv_seqlens - q_seqlens + i` and attends causally to the cache, which must already hold the
     new tokens' K/V (fill_kv_cache runs first, as in the reference's callers).
-    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power of two >= 16;
-    sliding window and soft-cap in decode only.
+    Sliding window and tanh soft-cap as in the reference, in both branches.
+    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power of two >= 16.
     """
     dev = _lib.require_cuda(q, k, v, o, block_offsets, kv_seqlens)
     if window_size is None:
@@ -98,8 +98,6 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
                    logit_softcapping, dev):
     """Prefill branch of paged_attention_fwd (paged_attention.py:617-671): the tcgen05 prefill kernel with
     its K/V tiles fetched page by page."""
-    if window_size > 0 or logit_softcapping > 0:
-        raise NotImplementedError("sliding window / soft-cap are implemented for decode only")
     assert q.dim() == 3 and o.shape == q.shape and q.stride(-1) == 1 and o.stride(-1) == 1
     assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
@@ -117,6 +115,7 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
             q.shape[1], k.shape[2], q.shape[2], k.size(1), k.size(0), block_offsets.size(1),
             q.stride(0), q.stride(1), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
             o.stride(0), o.stride(1), block_offsets.stride(0), int(block_offsets.dtype == torch.int64),
-            float(sm_scale), 1, _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
+            int(window_size), float(sm_scale), float(logit_softcapping), 1, _lib.dtype_code(q), status.data_ptr(),
+            _lib.stream_ptr(dev))
     _lib.check(rc, "paged_attention_fwd(prefill)")
     return o

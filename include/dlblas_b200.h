@@ -188,8 +188,9 @@ int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* 
 /* Prefill over a paged cache that already holds the earlier tokens of each sequence (chunked prefill,
  * prefix reuse): q [total_q, hq, d] packed by sequence (q_start_loc, q_seq_len), caches
  * [num_pages, page_size, hkv, d], block_table [batch, max_pages] (int32 or int64), kv_seq_len [batch] =
- * history + q_seq_len; query i of a sequence sees keys 0 .. history + i.  Same kernel as
- * dlb_flash_prefill_varlen with K/V tiles fetched page by page.  Replaces the prefill branch of
+ * history + q_seq_len; query i of a sequence sees keys 0 .. history + i (with window > 0 only the last
+ * window + 1 of them; with softcap > 0 scores become softcap * tanh(score * sm_scale / softcap)).  Same
+ * kernel as dlb_flash_prefill_varlen with K/V tiles fetched page by page.  Replaces the prefill branch of
  * paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:617-671 (kernel :311-489). */
 int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                             const void* block_table, const int32_t* q_start_loc, const int32_t* q_seq_len,
@@ -198,8 +199,8 @@ int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_ca
                             int64_t max_pages, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_page,
                             int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
                             int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t, int64_t o_stride_h,
-                            int64_t bt_stride, int table_is_int64, float sm_scale, int causal, int dtype,
-                            int32_t* status, void* stream);
+                            int64_t bt_stride, int table_is_int64, int64_t window, float sm_scale, float softcap,
+                            int causal, int dtype, int32_t* status, void* stream);
 
 /* Number of fp32 elements of the split-KV workspace dlb_paged_decode needs (0 when max_splits == 1). */
 int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t head_dim, int64_t max_splits);

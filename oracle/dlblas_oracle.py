@@ -392,12 +392,14 @@ def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_sc
     return out
 
 
-def paged_prefill_attention(q, k_cache, v_cache, block_offsets, q_start_loc, q_seqlens, kv_seqlens, sm_scale=None):
+def paged_prefill_attention(q, k_cache, v_cache, block_offsets, q_start_loc, q_seqlens, kv_seqlens, sm_scale=None,
+                            window_size=None, logit_softcapping=None):
     """Prefill over a paged cache that already holds `kv_seqlens - q_seqlens` earlier tokens per sequence
     (ground truth of test_paged_attention.py:61-84 with the causal mask of :14-25 shifted by the history
     length, as the kernel does at paged_attention.py:362).  q [total_q, Hq, D] packed by sequence; query i
-    of a sequence sits at position history + i and sees keys 0 .. history + i.  Scores and softmax in
-    fp32, P cast to the value dtype before P.V."""
+    of a sequence sits at position history + i and sees keys 0 .. history + i; with a window only keys
+    >= max(history + i - window, 0) (paged_attention.py:421-424,447); optional tanh soft-cap of the scaled
+    scores (paged_attention.py:441-444).  Scores and softmax in fp32, P cast to the value dtype before P.V."""
     total, hq, d = q.shape
     page = k_cache.shape[1]
     hkv = k_cache.shape[2]
@@ -419,8 +421,14 @@ def paged_prefill_attention(q, k_cache, v_cache, block_offsets, q_start_loc, q_s
         vf = vs.transpose(0, 1).repeat_interleave(group, 0)
         qf = q[s0:s0 + nq].transpose(0, 1).float()                        # [hq, nq, d]
         sc = torch.matmul(qf, kf.transpose(1, 2)) * sm_scale              # [hq, nq, n]
+        if logit_softcapping is not None and logit_softcapping > 0:
+            sc = logit_softcapping * torch.tanh(sc / logit_softcapping)
         pos = torch.arange(nq)[:, None] + hist
-        sc = sc.masked_fill(torch.arange(n)[None, :] > pos, float("-inf"))
+        keys = torch.arange(n)[None, :]
+        hidden = keys > pos
+        if window_size is not None and window_size > 0:
+            hidden = hidden | (keys < (pos - window_size).clamp(min=0))
+        sc = sc.masked_fill(hidden, float("-inf"))
         p = torch.softmax(sc, dim=-1, dtype=torch.float32).to(vf.dtype)
         out[s0:s0 + nq] = torch.matmul(p.float(), vf.float()).transpose(0, 1).to(q.dtype)
     return out

@@ -341,3 +341,19 @@ def test_paged_prefill_equals_contiguous_prefill(cuda_device):
     context_attention_fwd(q, torch.cat(ks).to(dev), torch.cat(vs).to(dev), o2, d["q_start"].int().to(dev),
                           d["q_lens"].int().to(dev), 257)
     assert torch.equal(o, o2)
+
+
+@pytest.mark.parametrize("window,softcap", [(100, None), (17, None), (None, 30.0), (64, 20.0), (5000, None)])
+def test_paged_prefill_window_and_softcap(cuda_device, window, softcap):
+    """Sliding window (a query sees its last window + 1 keys) and tanh soft-cap in the prefill branch."""
+    d = _paged_prefill_case(17, [3, 200, 130, 64], [100, 37, 500, 0], 64, 8, 2, 128, torch.bfloat16)
+    dev = cuda_device
+    q = d["q"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["table"].to(dev), d["q_start"].to(dev),
+                        d["q_lens"].to(dev), d["kv_lens"].to(dev), 200, window_size=window, logit_softcapping=softcap)
+    ref = oracle.paged_prefill_attention(d["q"], d["k_cache"], d["v_cache"], d["table"], d["q_start"], d["q_lens"],
+                                         d["kv_lens"], window_size=window, logit_softcapping=softcap)
+    out = o.cpu()
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
