@@ -120,7 +120,7 @@ __device__ __forceinline__ bool split_range(int ctx, int window, int chunk, int 
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(pd::THREADS, 2)
+__global__ void __launch_bounds__(pd::THREADS + 32, 2)
 paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                           const DecodeParams p) {
   using namespace pd;
@@ -152,7 +152,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     if (p.max_splits == 1) {
       const int rows = min(16, p.group - hblk * 16);
       T* o = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b;
-      for (int idx = threadIdx.x; idx < rows * D; idx += pd::THREADS)
+      for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x)
         o[(int64_t)(kvh * p.group + hblk * 16 + idx / D) * p.o_stride_h + idx % D] = Elem<T>::from_f(0.f);
     }
     return;   // whole CTA leaves
@@ -161,7 +161,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], p.gather ? 32 : 1);   // gather: one arrival per producer lane
+      mbar_init(&full_bar[s], p.gather ? 64 : 1);   // gather: one arrival per lane of the two producer warps
       mbar_init(&empty_bar[s], CONSUMER_WARPS);
     }
     *abort_flag = 0;
@@ -181,7 +181,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 #pragma unroll
     for (int j = 0; j < 4; ++j) oacc[t][j] = 0.f;
 
-  if (warp == CONSUMER_WARPS) {
+  if (warp >= CONSUMER_WARPS) {
     // ------------------------------ producer ------------------------------
     // A tile is 64 keys = 64 / min(page, 64) boxes per K/V half; the boxes are spread over the
     // lanes of this warp so that small pages (down to one token per page) still issue quickly.
@@ -194,7 +194,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       // 128 bytes per token and column half, and the copy engine's operation rate, not bandwidth, becomes
       // the limit (measured 0.96 TB/s at page size 1).  Instead the 32 lanes gather 16-byte chunks with
       // cp.async straight into the same 128-byte-swizzled tile layout: 16 lanes per token row, two rows
-      // per pass, the page of a row looked up by its 16 lanes together.
+      // per pass.  The launch has a second producer warp in this mode: each takes 32 of a tile's 64 rows
+      // (a producer warp's instruction rate, not bandwidth, is what limits the gather).
       const T* kc = reinterpret_cast<const T*>(p.k_cache);
       const T* vc = reinterpret_cast<const T*>(p.v_cache);
       constexpr int CHUNKS = D / 8;                 // 16-byte chunks per token row
@@ -215,28 +216,27 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
         uint8_t* kdst = smem + s * STAGE_BYTES + hbox * HALF_BYTES;
         uint8_t* vdst = kdst + KV_BYTES;
         const int tok0 = lo + t * TILE_KEYS;
-        // the 64 rows' (page, slot) are looked up once, two rows per lane, and handed out by shuffles
-        int pg[2], sl[2];
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
+        // this warp's 32 rows' (page, slot) are looked up once, one row per lane, and handed out by shuffles
+        const int q = warp - CONSUMER_WARPS;
+        int pg, sl;
+        {
           const int tok = tok0 + q * 32 + lane;
           int page_slot = tok / p.page_size;
           if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // rows past the table: any valid page
           int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
           if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
-          pg[q] = page;
-          sl[q] = tok % p.page_size;
+          pg = page;
+          sl = tok % p.page_size;
         }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
+        {
 #pragma unroll 4
           for (int rr = sub; rr < 32; rr += ROWS_PER_PASS) {
             const int r = q * 32 + rr;
-            const int page = __shfl_sync(0xffffffffu, pg[q], rr);
+            const int page = __shfl_sync(0xffffffffu, pg, rr);
             const uint32_t off = (uint32_t)(r * 128 + ((cc ^ (r & 7)) << 4));
             int64_t ko = (int64_t)page * p.k_stride_page, vo = (int64_t)page * p.v_stride_page;
             if (!one_token_pages) {   // uniform
-              const int slot = __shfl_sync(0xffffffffu, sl[q], rr);
+              const int slot = __shfl_sync(0xffffffffu, sl, rr);
               ko += (int64_t)slot * p.k_stride_slot;
               vo += (int64_t)slot * p.v_stride_slot;
             }
@@ -249,7 +249,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     }
     const int keys_per_box = min(p.page_size, TILE_KEYS);
     const int boxes_per_tile = TILE_KEYS / keys_per_box;
-    for (int t = 0; !p.gather && t < n_tiles; ++t) {
+    for (int t = 0; !p.gather && warp == CONSUMER_WARPS && t < n_tiles; ++t) {
       const int s = t % STAGES;
       const uint32_t ph = (t / STAGES) & 1;
       int ok = 1;
@@ -450,7 +450,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
   }
   __syncthreads();
   T* out = reinterpret_cast<T*>(p.out);
-  for (int idx = threadIdx.x; idx < rows_valid * D; idx += THREADS) {
+  for (int idx = threadIdx.x; idx < rows_valid * D; idx += blockDim.x) {
     const int row = idx / D;
     const int d = idx - row * D;
     float m = -CUDART_INF_F;
@@ -520,7 +520,7 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   }
   const int hblocks = (p.group + 15) / 16;
   dim3 grid(p.max_splits, p.hkv * hblocks, p.batch);
-  kern<<<grid, THREADS, SMEM, stream>>>(tk, tv, p);
+  kern<<<grid, p.gather ? THREADS + 32 : THREADS, SMEM, stream>>>(tk, tv, p);
   DLB_CUDA_LAUNCH_CHECK();
   if (p.max_splits > 1) {
     paged_decode_merge_kernel<T, D><<<dim3(p.hq, p.batch), D, 0, stream>>>(p);
