@@ -115,16 +115,6 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ----------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------
@@ -213,24 +203,6 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
       "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
-// Pull a tile into L2 ahead of the load that will bring it to shared memory.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
-               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N> __device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // ----------------------------------------------------------------------------
 // tcgen05: tensor memory + 5th-generation tensor-core MMA (cta_group::1)
 // ----------------------------------------------------------------------------
@@ -251,33 +223,13 @@ __device__ __forceinline__ void tc_fence_before_sync() {
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.
-__device__ __forceinline__ void umma_ss_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc]; issued by ONE thread.  A occupies lanes 0..127 (one row each);
-// a 32-bit TMEM column holds two K-consecutive 16-bit elements, so one K16 step spans 8 columns.
-__device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Lean issue forms.  A single thread issues every MMA of a CTA, so the instructions AROUND each
-// tcgen05.mma bound the tensor pipe at small N: measured on B200 with back-to-back MMAs from one
-// thread, the forms above (64-bit descriptor built or added per MMA, accumulate flag through setp)
-// sustain 99 / 107 / 171 clocks per M128 K16 MMA at N = 64 / 128 / 256, the forms below (descriptor
+// tcgen05.mma, issued by ONE thread.  D[tmem] (+)= A * B with A from a shared-memory descriptor (ss) or
+// from TMEM (ts: A occupies lanes 0..127, one row each; a 32-bit TMEM column holds two K-consecutive
+// 16-bit elements, so one K16 step spans 8 columns), B from a shared-memory descriptor.
+// The forms are deliberately lean.  A single thread issues every MMA of a CTA, so the instructions
+// AROUND each tcgen05.mma bound the tensor pipe at small N: measured on B200 with back-to-back MMAs
+// from one thread, 64-bit descriptors built or added per MMA with the accumulate flag through setp
+// sustain 99 / 107 / 171 clocks per M128 K16 MMA at N = 64 / 128 / 256; the forms below (descriptor
 // as two 32-bit halves of which only the low one moves, accumulate flag as a literal) 48 / 64 / 128,
 // i.e. the math rate at N >= 128.  ACC = 0 overwrites the accumulator, 1 adds to it.
 template <int ACC>

@@ -46,10 +46,10 @@ constexpr int KV_BOX = BN * 128;  // one 64-wide column box of a K or V tile
 constexpr int KV_STAGES = 2;
 constexpr int TMEM_COLS = 256;    // S0 [0,64) S1 [64,128) O [128,128+D)
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
-// Bit g set: group g (of every 8 groups of four scores) computes 2^x with the polynomial instead of the
-// SFU.  Measured on B200: the softmax warps are issue-bound, not SFU-bound, so 0 (all SFU) is fastest
-// (0x52 = 37.5 % polynomial was 10 % slower on the 4 x 8192 benchmark).
-constexpr unsigned POLY_EXP2_GROUPS = 0x00;
+// (Computing a share of the exponentials with a degree-3 polynomial on the FMA pipe instead of the SFU,
+// as large kernels of this kind do, was measured on B200 at 12.5 %, 25 % and 37.5 % of the scores and
+// was 2 %, 4 % and 10 % slower on the 4 x 8192 benchmark: the softmax warps are bound by issue slots
+// and latency, not by the SFU.  It is not in the code.)
 // shared-memory layout for head size D (64 or 128)
 template <int D> struct Layout {
   static constexpr int BOXES = D / 64;
@@ -119,32 +119,6 @@ __device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
-}
-
-// 2^x for two scores at once on the FMA/ALU pipes (no SFU): round-to-nearest split x = n + f
-// with the 1.5 * 2^23 trick, degree-3 polynomial for 2^f on [-0.5, 0.5] (max relative error
-// 7.5e-5, far below the 16-bit rounding of P), exponent added as an integer.  The softmax loop
-// sends a fixed share of its exponentials here so that the SFU, which can retire only 16
-// exponentials per clock per SM, stops being the longest pipe.
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& e0, float& e1) {
-  float xa, xb;
-  unpack_f2(x2, xa, xb);
-  xa = fmaxf(xa, -126.f);
-  xb = fmaxf(xb, -126.f);
-  const uint64_t x = pack_f2(xa, xb);
-  const uint64_t magic = pack_f2(12582912.f, 12582912.f);
-  const uint64_t t = add_f2(x, magic);                                   // low mantissa bits = round(x)
-  const uint64_t r = add_f2(t, pack_f2(-12582912.f, -12582912.f));       // round(x) as a float
-  const uint64_t f = fma_f2(r, pack_f2(-1.f, -1.f), x);                  // x - round(x)
-  uint64_t p = fma_f2(pack_f2(0.05517083778977394f, 0.05517083778977394f), f,
-                      pack_f2(0.24260935187339783f, 0.24260935187339783f));
-  p = fma_f2(p, f, pack_f2(0.6932609677314758f, 0.6932609677314758f));
-  p = fma_f2(p, f, pack_f2(0.9999281764030457f, 0.9999281764030457f));
-  float pa, pb, ta, tb;
-  unpack_f2(p, pa, pb);
-  unpack_f2(t, ta, tb);
-  e0 = __int_as_float(__float_as_int(pa) + (__float_as_int(ta) << 23));
-  e1 = __int_as_float(__float_as_int(pb) + (__float_as_int(tb) << 23));
 }
 
 struct PrefillParams {
@@ -275,7 +249,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int box_slots = min(p.page_size, BN);
         const int n_sub = p.paged ? BN / box_slots : 0;
         int pg[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
-        for (int u = 0; u < n_sub; ++u) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (u >= n_sub) break;
           const int tok = (jb0 + j) * BN + u * box_slots;
           int page_slot = tok / p.page_size;
           if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // past the table: any valid page, masked later
@@ -290,10 +266,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         uint8_t* kd = smem + OFF_K + s * KV_BYTES;
         mbar_arrive_expect_tx(&k_full[s], KV_BYTES);
         if (p.paged) {
-          for (int u = 0; u < n_sub; ++u)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (u >= n_sub) break;
 #pragma unroll
             for (int bx = 0; bx < BOXES; ++bx)
               tma_load_4d(kd + bx * KV_BOX + u * box_slots * 128, &tmap_k, &k_full[s], bx * 64, kvh, sl[u], pg[u]);
+          }
         } else {
 #pragma unroll
           for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
@@ -302,10 +281,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         uint8_t* vd = smem + OFF_V + s * KV_BYTES;
         mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
         if (p.paged) {
-          for (int u = 0; u < n_sub; ++u)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (u >= n_sub) break;
 #pragma unroll
             for (int bx = 0; bx < BOXES; ++bx)
               tma_load_4d(vd + bx * KV_BOX + u * box_slots * 128, &tmap_v, &v_full[s], bx * 64, kvh, sl[u], pg[u]);
+          }
         } else {
 #pragma unroll
           for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(vd + bx * KV_BOX, &tmap_v, &v_full[s], bx * 64, kvh, row);
@@ -470,35 +452,21 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-#pragma unroll
-          for (int u = 0; u < 8; u += 4) {
-            const uint64_t a01 = fma_f2(
-                pack_f2(__uint_as_float(sr[h][c + u]), __uint_as_float(sr[h][c + u + 1])), scale2, negm2);
-            const uint64_t a23 = fma_f2(
-                pack_f2(__uint_as_float(sr[h][c + u + 2]), __uint_as_float(sr[h][c + u + 3])), scale2, negm2);
-            float e0, e1, e2, e3;
-            // groups of four scores selected by POLY_EXP2_GROUPS take the polynomial path, the rest the SFU
-            const int grp = ((h * 32 + c + u) >> 2) & 7;
-            if (((POLY_EXP2_GROUPS >> grp) & 1) != 0) {
-              exp2_poly2(a01, e0, e1);
-              exp2_poly2(a23, e2, e3);
-            } else {
-              float x0, x1, x2, x3;
-              unpack_f2(a01, x0, x1);
-              unpack_f2(a23, x2, x3);
-              e0 = fast_exp2(x0);
-              e1 = fast_exp2(x1);
-              e2 = fast_exp2(x2);
-              e3 = fast_exp2(x3);
-            }
-            sum2a = add_f2(sum2a, pack_f2(e0, e1));
-            sum2b = add_f2(sum2b, pack_f2(e2, e3));
-            typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
-            typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
-            pk[(c + u) / 2] = *reinterpret_cast<uint32_t*>(&v01);
-            pk[(c + u) / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
-          }
+        for (int c = 0; c < 32; c += 4) {
+          const uint64_t a01 =
+              fma_f2(pack_f2(__uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1])), scale2, negm2);
+          const uint64_t a23 =
+              fma_f2(pack_f2(__uint_as_float(sr[h][c + 2]), __uint_as_float(sr[h][c + 3])), scale2, negm2);
+          float x0, x1, x2, x3;
+          unpack_f2(a01, x0, x1);
+          unpack_f2(a23, x2, x3);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1), e2 = fast_exp2(x2), e3 = fast_exp2(x3);
+          sum2a = add_f2(sum2a, pack_f2(e0, e1));
+          sum2b = add_f2(sum2b, pack_f2(e2, e3));
+          typename Elem<T>::T2 v01 = Elem<T>::from_f2(e0, e1);
+          typename Elem<T>::T2 v23 = Elem<T>::from_f2(e2, e3);
+          pk[c / 2] = *reinterpret_cast<uint32_t*>(&v01);
+          pk[c / 2 + 1] = *reinterpret_cast<uint32_t*>(&v23);
         }
         tmem_st_32x32b_x16(tmem_base + lane_field + s * BN + h * 16, pk);
       }

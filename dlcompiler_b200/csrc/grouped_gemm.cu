@@ -36,10 +36,9 @@ constexpr int BK = 64;            // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_N = 256;
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
-// k-blocks an explicit L2 prefetch of the weight tiles runs ahead of the ring's loads.  Measured on
-// B200 at the benchmark shape: 6 made the step 18 % SLOWER (the 8 CTAs that share a weight tile all
-// prefetch it, and the extra TMA traffic competes with the loads), so it is off.
-constexpr int PREFETCH_DISTANCE = 0;
+// (An explicit TMA L2 prefetch of the weight tiles 6 k-blocks ahead of the ring's loads was measured on
+// B200 at the benchmark shape and made the step 18 % SLOWER: the 8 CTAs that share a weight tile all
+// prefetch it, and the extra TMA traffic competes with the loads.  It is not in the code.)
 constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_BYTES = UMMA_N * BK * 2;    // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -175,9 +174,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    // Two walkers over the same (tile, k-block) sequence: `ld` feeds the shared-memory ring, `pf`
-    // runs PREFETCH_DISTANCE k-blocks ahead and only pulls the weight tiles into L2, so that the
-    // ring's loads find them there instead of paying the HBM round trip.
     if (lane == 0) {
       struct Walker {
         TileCursor cur;
@@ -197,11 +193,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           w.valid = w.tile < total_tiles;
           if (w.valid) w.cur.locate(bs, p.num_experts, n_tiles, w.tile, w.m_blk, w.n_blk);
         }
-      };
-      auto prefetch_b = [&](const Walker& w) {
-        const int b_row = w.cur.e * p.rows_per_expert + w.n_blk * BN_OUT;
-        tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row);
-        if constexpr (kSilu) tma_prefetch_l2_2d(&tmap_b, w.kb * BK, b_row + p.up_row_offset);
       };
       if (p.wait_flags != nullptr) {
         // rows of A are stored by other GPUs: do not read them before every rank has signalled
@@ -227,13 +218,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         __threadfence_system();
       }
-      Walker ld, pf;
+      Walker ld;
       start_walker(ld);
-      start_walker(pf);
-      for (int i = 0; i < PREFETCH_DISTANCE && pf.valid; ++i) {
-        prefetch_b(pf);
-        advance(pf);
-      }
       uint32_t it = 0;
       while (ld.valid) {
         const int s = it % STAGES;
@@ -249,12 +235,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tma_load_2d(b_dst + B_BYTES / 2, &tmap_b, &full_bar[s], ld.kb * BK, b_row + p.up_row_offset);
         } else {
           tma_load_2d(b_dst, &tmap_b, &full_bar[s], ld.kb * BK, b_row);
-        }
-        if constexpr (PREFETCH_DISTANCE > 0) {
-          if (pf.valid) {
-            prefetch_b(pf);
-            advance(pf);
-          }
         }
         advance(ld);
         ++it;
