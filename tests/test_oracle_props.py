@@ -144,3 +144,35 @@ def test_decode_oracle_window_and_softcap():
     capped = oracle.paged_decode_attention(d["q"], d["k_cache"], d["v_cache"], d["block_table"], d["kv_seqlens"],
                                            logit_softcapping=1e6)
     torch.testing.assert_close(full, capped, atol=1e-2, rtol=0)
+
+
+def test_paged_prefill_oracle_is_the_tail_of_a_full_prefill():
+    """The history form of the prefill oracle against the plain causal one: the last n - hist rows of a
+    full prefill over n tokens are exactly a prefill of those rows over a cache holding all n keys; a
+    window at least as long as the context changes nothing, a short one equals attention over the
+    truncated key range."""
+    g = torch.Generator().manual_seed(0)
+    n, hist, page, hkv, hq, D = 50, 20, 16, 2, 4, 64
+    k = torch.randn(n, hkv, D, generator=g).bfloat16()
+    v = torch.randn(n, hkv, D, generator=g).bfloat16()
+    q = torch.randn(n, hq, D, generator=g).bfloat16()
+    full = oracle.context_attention(q, k, v, torch.tensor([0]), torch.tensor([n]))
+    npg = (n + page - 1) // page
+    kc = torch.zeros(npg, page, hkv, D).bfloat16()
+    vc = torch.zeros_like(kc)
+    kc.view(-1, hkv, D)[:n] = k
+    vc.view(-1, hkv, D)[:n] = v
+    table = torch.arange(npg)[None]
+    args = (q[hist:], kc, vc, table, torch.tensor([0]), torch.tensor([n - hist]), torch.tensor([n]))
+    assert torch.equal(oracle.paged_prefill_attention(*args), full[hist:])
+    assert torch.equal(oracle.paged_prefill_attention(*args, window_size=n), full[hist:])
+    w = 7
+    out = oracle.paged_prefill_attention(*args, window_size=w)
+    row = n - 1                                   # last query: keys row - w .. row
+    # the last query alone over its window, computed directly
+    kf = k[row - w:row + 1].transpose(0, 1).repeat_interleave(hq // hkv, 0).float()
+    vf = v[row - w:row + 1].transpose(0, 1).repeat_interleave(hq // hkv, 0)
+    sc = torch.matmul(q[row].float().unsqueeze(1), kf.transpose(1, 2)) / D ** 0.5
+    p = torch.softmax(sc, dim=-1, dtype=torch.float32).to(vf.dtype)
+    direct = torch.matmul(p.float(), vf.float()).squeeze(1).to(q.dtype)
+    assert torch.equal(out[-1], direct)
