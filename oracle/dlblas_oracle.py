@@ -8,9 +8,14 @@ shipped package imports it and it must never be used as a compute path.
 
 Parity status
   pinned   silu_and_mul, fused_moe (launcher and end-to-end), varlen prefill
-           attention, paged decode attention: checked against fixtures produced
-           by executing the reference tests' own ground-truth functions
-           (tests/golden/make_golden.py, tests/golden/*.pt).
+           attention, paged decode attention, paged prefill with history,
+           rms_norm / add_rms_norm, rotary embedding, fill_kv_cache, GShard
+           topk_gating: checked against fixtures produced by executing the
+           reference tests' (for topk_gating: the reference benchmark's) own
+           ground-truth functions (tests/golden/make_golden.py, tests/golden/*.pt).
+           The sliding-window and soft-cap forms of the paged prefill and the
+           topk_gating gradients have no reference fixture; they are tied to the
+           pinned functions by tests/test_oracle_props.py and by autograd.
   UNPINNED grouped_topk_gating (group-limited sigmoid routing) and
            moe_align_block_size: the reference contains neither, so these two
            restate the definitions written in this file; "parity unpinned".

@@ -166,6 +166,32 @@ def main():
         cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
                       "block_offsets": table, "kv_seqlens": full, "gt": fns["_conti_input"](gt, seq_lens)})
     torch.save(cases, os.path.join(HERE, "paged_decode.pt"))
+    # ---------------------------------------------------------------- paged prefill with history (same test file:
+    # the reference's test of the prefill branch, test_paged_attention.py:150-290, with its own mask builder)
+    cases = []
+    for i, (d, hq, hkv, page, seqs, hist, dtype) in enumerate([
+            (64, 8, 2, 16, [30, 50, 70, 90], [50, 40, 30, 20], torch.float16),       # the reference test's own lengths
+            (128, 8, 2, 64, [5, 130, 1, 64], [100, 37, 200, 0], torch.bfloat16),
+            (128, 4, 4, 16, [17, 33, 2, 80], [0, 15, 64, 1], torch.float16)]):
+        torch.manual_seed(223 + i)
+        seq_lens = torch.tensor(seqs)
+        history = torch.tensor(hist)
+        full = seq_lens + history
+        bq = torch.rand(4, int(seq_lens.max()), hq, d).to(dtype)
+        bk = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        bv = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        nblk = (full + page - 1) // page
+        offs = [torch.arange(int(n)) * 4 + idx for idx, n in enumerate(nblk)]
+        table = torch.zeros(4, max(len(o) for o in offs), dtype=torch.int64)
+        for o, row in zip(offs, table):
+            row[:len(o)] = o
+        mask = fns["_make_bias"](seq_lens, history, -1e30)
+        gt = fns["_naive_attention"](bq, (bk, bv), mask)
+        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, d)
+        cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
+                      "block_offsets": table, "q_seqlens": seq_lens, "kv_seqlens": full,
+                      "gt": fns["_conti_input"](gt, seq_lens)})
+    torch.save(cases, os.path.join(HERE, "paged_prefill.pt"))
     # ---------------------------------------------------------------- rms_norm / add_rms_norm
     fns = load_functions(os.path.join(tests, "test_rms_norm.py"), ["TestRMSNorm.gt"])
     rms_gt = fns["TestRMSNorm.gt"]           # a fixture that `return`s its value

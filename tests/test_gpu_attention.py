@@ -357,3 +357,19 @@ def test_paged_prefill_window_and_softcap(cuda_device, window, softcap):
     out = o.cpu()
     assert torch.isfinite(out.float()).all()
     torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_paged_prefill_golden(cuda_device, golden_dir):
+    """The prefill branch against the reference test's own ground truth (fixtures made by executing
+    test_paged_attention.py's mask builder and naive attention on the CPU)."""
+    for c in torch.load(os.path.join(golden_dir, "paged_prefill.pt"), weights_only=True):
+        dev = cuda_device
+        q = c["q"].to(dev)
+        o = torch.full_like(q, float("nan"))
+        q_lens = c["q_seqlens"]
+        start = torch.cumsum(q_lens, 0) - q_lens
+        paged_attention_fwd(q, c["k_cache"].to(dev), c["v_cache"].to(dev), o, c["block_offsets"].to(dev),
+                            start.to(dev), q_lens.to(dev), c["kv_seqlens"].to(dev), int(q_lens.max()))
+        # reference test: atol=1e-3, rtol=1e-5 for fp16 (test_paged_attention.py:286)
+        tol = 1e-3 if q.dtype == torch.float16 else 8e-3
+        torch.testing.assert_close(o.cpu(), c["gt"], atol=tol, rtol=1e-5)

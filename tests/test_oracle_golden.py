@@ -72,6 +72,18 @@ def test_paged_decode_ground_truth(golden_dir):
         torch.testing.assert_close(out, c["gt"], atol=tol, rtol=1e-5)
 
 
+def test_paged_prefill_ground_truth(golden_dir):
+    """Prefill over a paged cache with history against the reference test's own mask builder and naive
+    attention (test_paged_attention.py:14-25,61-84)."""
+    for c in _load(golden_dir, "paged_prefill.pt"):
+        q_lens = c["q_seqlens"]
+        start = torch.cumsum(q_lens, 0) - q_lens
+        out = oracle.paged_prefill_attention(c["q"], c["k_cache"], c["v_cache"], c["block_offsets"], start, q_lens,
+                                             c["kv_seqlens"])
+        tol = 1e-3 if out.dtype == torch.float16 else 8e-3
+        torch.testing.assert_close(out, c["gt"], atol=tol, rtol=1e-5)
+
+
 def test_rms_norm_ground_truths(golden_dir):
     for c in _load(golden_dir, "rms_norm.pt"):
         x, w, res, eps = c["x"], c["w"], c["res"], c["eps"]
