@@ -89,6 +89,13 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def wait_first(self, limit_s=15.0):
+        """Blocks until the first sample has arrived (nvidia-smi takes a second or more to start on a box
+        with many GPUs), so that a short timed region is not over before sampling begins."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.rows and time.perf_counter() - t0 < limit_s:
+            time.sleep(0.02)
+
     def __exit__(self, *exc):
         if self.proc is not None:
             self.proc.terminate()
@@ -484,6 +491,7 @@ def run_ours(args):
 
         launches_per_step = 5
         with ClockSampler(local_rank) as clk:
+            clk.wait_first()
             ms = time_steps(step, args.steps, args.warmup, min_warm_s=args.warm_seconds)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]
@@ -532,7 +540,11 @@ def run_ours(args):
 
         launches_per_step = launches
         with ClockSampler(local_rank) as clk:
-            # every rank must run the same number of steps (they meet in cross-GPU barriers): fixed count
+            # no step may start while a rank still waits for its sampler: the ranks meet in cross-GPU
+            # barriers with bounded waits
+            clk.wait_first()
+            barrier()
+            # every rank must run the same number of steps: fixed count
             ms = time_steps(step, args.steps, max(args.warmup, 1000), barrier)
         torch.cuda.synchronize()
         timed = events[-2 * args.steps:]

@@ -51,6 +51,8 @@ SIGNATURES = {
                             c_int, c_void_p]),
     "dlb_ep_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_int, c_int,
                                c_void_p, c_void_p]),
+    "dlb_ep_combine_pull": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64,
+                                    c_int64, c_int, c_void_p, c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),
     "dlb_ep_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

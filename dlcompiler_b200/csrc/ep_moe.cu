@@ -230,10 +230,11 @@ __global__ void __launch_bounds__(256) ep_send_kernel(const EpSendParams p) {
       reinterpret_cast<int32_t*>(p.meta.p[r])[pos] = (p.rank << 24) | slot;
     }
   }
-  __threadfence_system();
+  // one system-scope fence per CTA, after the barrier that orders every thread's peer stores before it
+  // (a fence in every thread made each of the CTA's warps wait for the links on its own)
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
+    __threadfence_system();
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == (int)gridDim.x - 1) {
       *p.done_counter = 0;
@@ -244,13 +245,8 @@ __global__ void __launch_bounds__(256) ep_send_kernel(const EpSendParams p) {
   }
 }
 
-// Top-k combine that first waits (bounded) until every rank has signalled flag slot 2.
-template <typename T>
-__global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ partial, T* __restrict__ out,
-                                                         int64_t tokens, int top_k, int hidden,
-                                                         int64_t out_row_stride, const int* wait_flags, int world,
-                                                         int epoch, int* status) {
-  using T2 = typename Elem<T>::T2;
+// Threads 0..world-1 of the CTA wait (bounded) until wait_flags[r] >= epoch, then the whole CTA proceeds.
+__device__ __forceinline__ void wait_all_ranks(const int* wait_flags, int world, int epoch, int* status, int site) {
   if (threadIdx.x < world) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
@@ -260,7 +256,7 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ p
         if (t0 == 0) t0 = now;
         if (now - t0 > DLB_WAIT_BUDGET_NS) {
           if (status != nullptr && atomicCAS(status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
-            status[1] = 44;
+            status[1] = site;
             status[2] = (int)blockIdx.x;
             status[3] = (int)threadIdx.x;
           }
@@ -271,6 +267,16 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ p
     __threadfence_system();
   }
   __syncthreads();
+}
+
+// Top-k combine that first waits (bounded) until every rank has signalled flag slot 2.
+template <typename T>
+__global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ partial, T* __restrict__ out,
+                                                         int64_t tokens, int top_k, int hidden,
+                                                         int64_t out_row_stride, const int* wait_flags, int world,
+                                                         int epoch, int* status) {
+  using T2 = typename Elem<T>::T2;
+  wait_all_ranks(wait_flags, world, epoch, status, 44);
   const int vecs = hidden / 8;
   const int64_t total = tokens * (int64_t)vecs;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -296,6 +302,68 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ p
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = Elem<T>::from_f2(acc[2 * j], acc[2 * j + 1]);
     *(reinterpret_cast<uint4*>(out + t * out_row_stride) + v) = o;
+  }
+}
+
+// Top-k combine that PULLS: once every rank has signalled that its down projection is complete, each
+// token's top-k rows are read straight out of the owners' result buffers (coalesced 16-byte peer loads
+// over NVLink) and summed.  The expert side then writes its rows locally, in full cache lines, instead
+// of pushing row fragments through the links from the GEMM epilogue.
+struct EpPullParams {
+  PeerPtrs y;                     // every rank's [cap][hidden] down-projection output
+  const void* topk_ids;           // [tokens * top_k] GLOBAL expert ids
+  const int32_t* dest_pos;        // [tokens * top_k] row inside the owner's buffer (from the route step)
+  void* out;
+  const int* wait_flags;
+  int* status;
+  int64_t y_row_stride, out_row_stride, tokens;
+  int top_k, hidden, experts, world, cap, ids_are_int64, epoch;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) ep_combine_pull_kernel(const EpPullParams p) {
+  using T2 = typename Elem<T>::T2;
+  wait_all_ranks(p.wait_flags, p.world, p.epoch, p.status, 45);
+  const int vecs = p.hidden / 8;
+  const int epr = p.experts / p.world;
+  const int64_t total = p.tokens * (int64_t)vecs;
+  T* out = reinterpret_cast<T*>(p.out);
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int v = (int)(idx - t * vecs);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    auto fetch = [&](int k) -> uint4 {
+      const int slot = (int)(t * p.top_k + k);
+      const int pos = p.dest_pos[slot];
+      if (pos < 0 || pos >= p.cap) return make_uint4(0u, 0u, 0u, 0u);
+      const int r = load_id(p.topk_ids, slot, p.ids_are_int64) / epr;
+      // stored by another GPU during this step: never a cached copy
+      return __ldcv(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.y.p[r]) + (int64_t)pos * p.y_row_stride) + v);
+    };
+    auto add = [&](const uint4& x) {
+      const T2* x2 = reinterpret_cast<const T2*>(&x);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<T>::to_f2(x2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    };
+    int k = 0;
+    for (; k + 2 <= p.top_k; k += 2) {   // two link round trips in flight per thread
+      const uint4 x0 = fetch(k), x1 = fetch(k + 1);
+      add(x0);
+      add(x1);
+    }
+    if (k < p.top_k) add(fetch(k));
+    uint4 o;
+    T2* o2 = reinterpret_cast<T2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = Elem<T>::from_f2(acc[2 * j], acc[2 * j + 1]);
+    *(reinterpret_cast<uint4*>(out + t * p.out_row_stride) + v) = o;
   }
 }
 
@@ -443,6 +511,57 @@ extern "C" int dlb_ep_combine(const void* partial, void* out, int64_t tokens, in
                                                                 status);
   } else {
     set_last_error("ep_combine: unsupported dtype %d", dtype);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
+
+extern "C" int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, const void* topk_ids, int ids_are_int64,
+                                   const int32_t* dest_pos, void* out, int64_t tokens, int top_k, int64_t hidden,
+                                   int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world,
+                                   int experts, int64_t cap, int epoch, int32_t* status, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0 && tokens * top_k < (1LL << 24), DLB_ERR_BAD_ARG,
+                "ep_combine_pull: bad sizes");
+  DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && wait_flags != nullptr, DLB_ERR_BAD_ARG,
+                "ep_combine_pull: bad wait arguments");
+  DLB_CHECK_ARG(experts >= world && experts % world == 0, DLB_ERR_BAD_ARG, "ep_combine_pull: %d experts over %d ranks",
+                experts, world);
+  DLB_CHECK_ARG(hidden % 8 == 0 && out_row_stride % 8 == 0 && y_row_stride % 8 == 0, DLB_ERR_ALIGNMENT,
+                "ep_combine_pull: hidden and row strides must be multiples of 8");
+  DLB_CHECK_ARG((((uintptr_t)out) & 15) == 0, DLB_ERR_ALIGNMENT, "ep_combine_pull: unaligned output");
+  DLB_CHECK_ARG(tokens == 0 || (topk_ids && dest_pos && out), DLB_ERR_BAD_ARG, "ep_combine_pull: null pointer");
+  EpPullParams p;
+  const int rc = fill_ptrs(&p.y, y_sym, world, "down-projection output");
+  if (rc != DLB_OK) return rc;
+  p.topk_ids = topk_ids;
+  p.dest_pos = dest_pos;
+  p.out = out;
+  p.wait_flags = wait_flags;
+  p.status = status;
+  p.y_row_stride = y_row_stride;
+  p.out_row_stride = out_row_stride;
+  p.tokens = tokens;
+  p.top_k = top_k;
+  p.hidden = (int)hidden;
+  p.experts = experts;
+  p.world = world;
+  p.cap = (int)cap;
+  p.ids_are_int64 = ids_are_int64;
+  p.epoch = epoch;
+  const int64_t total = tokens * (hidden / 8);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks < 1) blocks = 1;   // the wait still has to happen so that the next step may reuse the buffers
+  const int64_t limit = (int64_t)sm_count(current_device()) * 8;
+  if (blocks > limit) blocks = limit;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == DLB_DTYPE_BF16) {
+    ep_combine_pull_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(p);
+  } else if (dtype == DLB_DTYPE_F16) {
+    ep_combine_pull_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>(p);
+  } else {
+    set_last_error("ep_combine_pull: unsupported dtype %d", dtype);
     return DLB_ERR_UNSUPPORTED;
   }
   DLB_CUDA_LAUNCH_CHECK();

@@ -358,7 +358,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
     }
-    if constexpr (kPeer) __threadfence_system();   // peer stores performed before the kernel retires
   }
 
   // ------------------------------ teardown ------------------------------
@@ -369,9 +368,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (p.done_counter != nullptr && threadIdx.x == 0) {
-    // every CTA's stores are fenced above (epilogue) and ordered by the barrier; the CTA that
-    // arrives last tells every rank that this GPU's rows are in place
-    __threadfence();
+    // every thread's stores (into peer memory, or into local rows the peers will read) are ordered
+    // before this thread by the barrier; one system-scope fence per CTA publishes them, and the CTA
+    // that arrives last tells every rank that this GPU's rows are in place
+    __threadfence_system();
     const int prev = atomicAdd(p.done_counter, 1);
     if (prev == (int)gridDim.x - 1) {
       *p.done_counter = 0;

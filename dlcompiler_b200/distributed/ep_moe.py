@@ -180,7 +180,7 @@ class EpPeerContext:
     """
 
     def __init__(self, group, num_experts: int, device, max_tokens_per_rank: int, top_k: int, hidden: int,
-                 out_hidden: int, inter: int, dtype=torch.bfloat16):
+                 out_hidden: int, inter: int, dtype=torch.bfloat16, pull: bool = True):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -219,8 +219,16 @@ class EpPeerContext:
         self.rows, self._h_rows, self.rows_tbl = sym((self.cap, hidden), dtype)
         self.w, self._h_w, self.w_tbl = sym((self.cap,), torch.float32)
         self.meta, self._h_meta, self.meta_tbl = sym((self.cap,), torch.int32)
-        self.back, self._h_back, self.back_tbl = sym((self.max_slots, out_hidden), dtype)
-        for t in (self.counts, self.flags, self.rows, self.w, self.meta, self.back):
+        # results travel back in one of two ways: pulled by the combine out of the owners' output buffer
+        # `y` (default), or pushed by the down GEMM's epilogue into the senders' `back` buffers
+        self.pull = pull
+        if pull:
+            self.y, self._h_y, self.y_tbl = sym((self.cap, out_hidden), dtype)
+            result_buf = self.y
+        else:
+            self.back, self._h_back, self.back_tbl = sym((self.max_slots, out_hidden), dtype)
+            result_buf = self.back
+        for t in (self.counts, self.flags, self.rows, self.w, self.meta, result_buf):
             t.zero_()
         # plan outputs and the activation buffer are ordinary local memory
         self.dest_pos = torch.empty(max(self.max_slots, 1), dtype=torch.int32, device=device)
@@ -250,8 +258,12 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
                layout, destination row of every slot
       send     rows, weights and (rank, slot) tags stored into the owners' buffers; last CTA raises a flag
       GEMM     gate/up + silu on the received rows (its producer waits for every rank's flag first)
-      GEMM     down x weight, epilogue stores each row into the SENDER's result buffer; last CTA raises a flag
-      combine  waits for every rank's flag, then sums each token's top-k rows
+      GEMM     down x weight into this rank's output buffer; last CTA raises a flag on every rank
+      combine  waits for every rank's flag, then reads each token's top-k rows out of the owners' output
+               buffers (peer loads) and sums them
+    With `ctx.pull` off the down GEMM's epilogue instead stores each row into the SENDER's result buffer
+    and the combine reads locally; measured at 8 GPUs the row fragments a GEMM epilogue can store (16 bytes
+    per thread per row) cost 56 us more per step than the pull.
     """
     from .. import _lib
 
@@ -300,17 +312,30 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
             _events.append(("grouped_gemm_gate_up_silu", e0, e1))
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-        rc = lib.dlb_moe_grouped_gemm_sync(
-            ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(), E_local, H_out, inter,
-            w2_local.stride(1), None, ctx.back_tbl, world, ctx.back.stride(0), H_out, ctx.row_map.data_ptr(),
-            ctx.block_start.data_ptr(), ctx.w.data_ptr(), ctx.meta.data_ptr(), ctx.cap,
-            _lib.GEMM_WEIGHT | _lib.GEMM_PEER, dt, None, ctx.signal2_tbl, ctx.counters[1:2].data_ptr(), world, epoch,
-            ctx.status.data_ptr(), stream)
+        if ctx.pull:
+            rc = lib.dlb_moe_grouped_gemm_sync(
+                ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(), E_local, H_out, inter,
+                w2_local.stride(1), ctx.y.data_ptr(), None, 0, ctx.y.stride(0), H_out, ctx.row_map.data_ptr(),
+                ctx.block_start.data_ptr(), ctx.w.data_ptr(), None, ctx.cap, _lib.GEMM_WEIGHT, dt, None,
+                ctx.signal2_tbl, ctx.counters[1:2].data_ptr(), world, epoch, ctx.status.data_ptr(), stream)
+        else:
+            rc = lib.dlb_moe_grouped_gemm_sync(
+                ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(), E_local, H_out, inter,
+                w2_local.stride(1), None, ctx.back_tbl, world, ctx.back.stride(0), H_out, ctx.row_map.data_ptr(),
+                ctx.block_start.data_ptr(), ctx.w.data_ptr(), ctx.meta.data_ptr(), ctx.cap,
+                _lib.GEMM_WEIGHT | _lib.GEMM_PEER, dt, None, ctx.signal2_tbl, ctx.counters[1:2].data_ptr(), world,
+                epoch, ctx.status.data_ptr(), stream)
         _lib.check(rc, "moe_grouped_gemm_sync(down)")
         if _events is not None:
             e1.record()
-            _events.append(("grouped_gemm_down_peer_scatter", e0, e1))
-        rc = lib.dlb_ep_combine(ctx.back.data_ptr(), out.data_ptr(), T, topk, H_out, out.stride(0), dt,
-                                flags_local + 4 * (2 * 16), world, epoch, ctx.status.data_ptr(), stream)
+            _events.append(("grouped_gemm_down", e0, e1))
+        if ctx.pull:
+            rc = lib.dlb_ep_combine_pull(ctx.y_tbl, ctx.y.stride(0), ids.data_ptr(), is64, ctx.dest_pos.data_ptr(),
+                                         out.data_ptr(), T, topk, H_out, out.stride(0), dt,
+                                         flags_local + 4 * (2 * 16), world, ctx.num_experts, ctx.cap, epoch,
+                                         ctx.status.data_ptr(), stream)
+        else:
+            rc = lib.dlb_ep_combine(ctx.back.data_ptr(), out.data_ptr(), T, topk, H_out, out.stride(0), dt,
+                                    flags_local + 4 * (2 * 16), world, epoch, ctx.status.data_ptr(), stream)
         _lib.check(rc, "ep_combine")
     return out

@@ -154,6 +154,11 @@ int dlb_moe_grouped_gemm_sync(const void* a, int64_t a_rows, int64_t a_row_strid
  *                   rank's rows_sym [cap][hidden], w_sym [cap], meta_sym [cap]; the last CTA raises flag
  *                   slot 1 on every rank (done_counter: device int32, zero).
  *   dlb_ep_combine  dlb_moe_combine that first waits until wait_flags[r] >= epoch for every rank r.
+ *   dlb_ep_combine_pull  the same wait, then out[t] = sum over k of row dest_pos[t * top_k + k] of the
+ *                   down-projection output y_sym [cap][hidden] of the rank that owns expert
+ *                   topk_ids[t * top_k + k], read over NVLink with coalesced peer loads (slots whose
+ *                   dest_pos is outside [0, cap) contribute nothing).  The expert side then runs
+ *                   dlb_moe_grouped_gemm_sync with DLB_GEMM_WEIGHT alone, writing y locally.
  *   dlb_ep_barrier  stand-alone cross-GPU barrier on a flag slot (bounded wait; timeout -> status). */
 int dlb_ep_route(const void* topk_ids, int ids_are_int64, int64_t numel, void* const* counts_sym,
                  void* const* flags_sym, int32_t* dest_pos, int32_t* block_start, int32_t* num_post_padded,
@@ -167,6 +172,10 @@ int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_t hidden_co
 int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
                    int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
                    int32_t* status, void* stream);
+int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, const void* topk_ids, int ids_are_int64,
+                        const int32_t* dest_pos, void* out, int64_t tokens, int top_k, int64_t hidden,
+                        int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int experts,
+                        int64_t cap, int epoch, int32_t* status, void* stream);
 int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status, void* stream);
 
 /* out[t, :] = sum over k of partial[t * top_k + k, :] (fp32 accumulate, one rounding): the

@@ -41,14 +41,17 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         dl.check_device_status()
         ok = bool(torch.equal(out, full[sl]))
-        # the peer-memory exchange (our own kernels over NVLink) must give the same bits, step after step
-        pctx = ep_moe.EpPeerContext(dist.group.WORLD, wl.experts, dev, tl, wl.top_k, wl.hidden, wl.hidden, wl.inter)
-        for _ in range(3):
-            out2 = ep_moe.ep_fused_moe_peer(pctx, hs[sl], w1[rank * el:(rank + 1) * el].contiguous(),
-                                            w2[rank * el:(rank + 1) * el].contiguous(), tw[sl], ti[sl], wl.top_k)
-            torch.cuda.synchronize()
-            dl.check_device_status()
-            ok = ok and bool(torch.equal(out2, full[sl]))
+        # the peer-memory exchange (our own kernels over NVLink) must give the same bits, step after step,
+        # whether the results are pulled by the combine or pushed by the down GEMM's epilogue
+        for pull in (True, False):
+            pctx = ep_moe.EpPeerContext(dist.group.WORLD, wl.experts, dev, tl, wl.top_k, wl.hidden, wl.hidden,
+                                        wl.inter, pull=pull)
+            for _ in range(3):
+                out2 = ep_moe.ep_fused_moe_peer(pctx, hs[sl], w1[rank * el:(rank + 1) * el].contiguous(),
+                                                w2[rank * el:(rank + 1) * el].contiguous(), tw[sl], ti[sl], wl.top_k)
+                torch.cuda.synchronize()
+                dl.check_device_status()
+                ok = ok and bool(torch.equal(out2, full[sl]))
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
