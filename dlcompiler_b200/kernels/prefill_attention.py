@@ -15,6 +15,13 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     reference (prefill_attention.py:157).  Extension over the reference: if `lse` (fp32
     [Hq, total]) is given it receives m * sm_scale + log(sum), the natural-log convention of
     python/dlBLAS/dlblas/kernels/flash_attention.py:152-155.
+
+    The tensor-core kernel is built for head sizes 64 and 128.  Any other size up to 128 (the reference
+    rounds up to a power of two and masks, prefill_attention.py:179-180; its test runs 96, 80 and 13,
+    tests/kernels/test_attention_kernels.py:157) is run by zero-padding q, k and v to the next built size
+    on the device: padded feature columns add exact zeros to every score and produce output columns
+    that are dropped, and the softmax scale still comes from the true head size.  The padded copies cost
+    one extra pass over q, k, v and o.
     """
     dev = _lib.require_cuda(q, k, v, o, b_start_loc, b_seq_len, lse)
     assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3 and o.shape == q.shape
@@ -24,6 +31,15 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and o.stride(-1) == 1
     if sm_scale is None:
         sm_scale = 1.0 / (Lq**0.5)
+    if Lq not in (64, 128):
+        assert 1 <= Lq <= 128, "head sizes above 128 are not built"
+        pad = (64 if Lq <= 64 else 128) - Lq
+        qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+        op = torch.empty_like(qp)
+        context_attention_fwd(qp, kp, vp, op, b_start_loc, b_seq_len, max_input_len, lse=lse, causal=causal,
+                              sm_scale=sm_scale)
+        o.copy_(op[..., :Lq])
+        return o
     batch, head = b_seq_len.shape[0], q.shape[1]
     assert head % k.shape[1] == 0
     b_start_loc = b_start_loc.to(torch.int32).contiguous()

@@ -190,6 +190,19 @@ def test_prefill_head_size_64(cuda_device, lens, hq, hkv, dtype):
     torch.testing.assert_close(lse, rlse, rtol=1e-3, atol=1e-3)
 
 
+@pytest.mark.parametrize("head_dim", [96, 80, 13, 32, 48])
+def test_prefill_other_head_sizes(cuda_device, head_dim):
+    """The head sizes of the reference's own context-attention test (test_attention_kernels.py:136-160: 4 heads,
+    lengths 8 and 12, sizes 128, 96, 80, 13; it only checks that the call runs) and of its paged test (48, 32),
+    here checked against the oracle, with a longer ragged sequence added."""
+    wl = W.PrefillWorkload(seq_lens=[8, 12, 150], hq=4, hkv=4, head_dim=head_dim, dtype=torch.float16)
+    d = wl.make()
+    out, lse = _run_prefill(cuda_device, d, lse=True)
+    ref, rlse = oracle.context_attention(d["q"], d["k"], d["v"], d["b_start_loc"], d["b_seq_len"], return_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(lse, rlse, rtol=1e-3, atol=1e-3)
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_dense_flash_attention_bhmd(cuda_device, causal):
     """[B, H, M, D] layout of flash_attention.py:170-211 with grouped heads, LSE of :152-155."""
