@@ -29,6 +29,8 @@ namespace pd {
 constexpr int TILE_KEYS = 64;
 constexpr int CONSUMER_WARPS = 4;
 constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
+constexpr int GATHER_WARPS = 4;                 // producer warps when rows are gathered with cp.async
+constexpr int GATHER_ROWS = 64 / GATHER_WARPS;  // rows of a 64-key tile per producer warp
 constexpr int STAGES = 3;
 }  // namespace pd
 
@@ -120,7 +122,7 @@ __device__ __forceinline__ bool split_range(int ctx, int window, int chunk, int 
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(pd::THREADS + 32, 2)
+__global__ void __launch_bounds__(pd::THREADS + 32 * (pd::GATHER_WARPS - 1), 2)
 paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                           const DecodeParams p) {
   using namespace pd;
@@ -161,7 +163,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], p.gather ? 64 : 1);   // gather: one arrival per lane of the two producer warps
+      mbar_init(&full_bar[s], p.gather ? 32 * GATHER_WARPS : 1);   // gather: one arrival per lane of the producer warps
       mbar_init(&empty_bar[s], CONSUMER_WARPS);
     }
     *abort_flag = 0;
@@ -194,8 +196,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       // 128 bytes per token and column half, and the copy engine's operation rate, not bandwidth, becomes
       // the limit (measured 0.96 TB/s at page size 1).  Instead the 32 lanes gather 16-byte chunks with
       // cp.async straight into the same 128-byte-swizzled tile layout: 16 lanes per token row, two rows
-      // per pass.  The launch has a second producer warp in this mode: each takes 32 of a tile's 64 rows
-      // (a producer warp's instruction rate, not bandwidth, is what limits the gather).
+      // per pass.  The launch has GATHER_WARPS producer warps in this mode, each taking its share of a
+      // tile's 64 rows (a producer warp's instruction rate, not bandwidth, is what limits the gather).
       const T* kc = reinterpret_cast<const T*>(p.k_cache);
       const T* vc = reinterpret_cast<const T*>(p.v_cache);
       constexpr int CHUNKS = D / 8;                 // 16-byte chunks per token row
@@ -216,11 +218,11 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
         uint8_t* kdst = smem + s * STAGE_BYTES + hbox * HALF_BYTES;
         uint8_t* vdst = kdst + KV_BYTES;
         const int tok0 = lo + t * TILE_KEYS;
-        // this warp's 32 rows' (page, slot) are looked up once, one row per lane, and handed out by shuffles
+        // this warp's rows' (page, slot) are looked up once, one row per lane, and handed out by shuffles
         const int q = warp - CONSUMER_WARPS;
         int pg, sl;
         {
-          const int tok = tok0 + q * 32 + lane;
+          const int tok = tok0 + q * GATHER_ROWS + (lane % GATHER_ROWS);
           int page_slot = tok / p.page_size;
           if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // rows past the table: any valid page
           int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
@@ -230,8 +232,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
         }
         {
 #pragma unroll 4
-          for (int rr = sub; rr < 32; rr += ROWS_PER_PASS) {
-            const int r = q * 32 + rr;
+          for (int rr = sub; rr < GATHER_ROWS; rr += ROWS_PER_PASS) {
+            const int r = q * GATHER_ROWS + rr;
             const int page = __shfl_sync(0xffffffffu, pg, rr);
             const uint32_t off = (uint32_t)(r * 128 + ((cc ^ (r & 7)) << 4));
             int64_t ko = (int64_t)page * p.k_stride_page, vo = (int64_t)page * p.v_stride_page;
@@ -520,7 +522,7 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
   }
   const int hblocks = (p.group + 15) / 16;
   dim3 grid(p.max_splits, p.hkv * hblocks, p.batch);
-  kern<<<grid, p.gather ? THREADS + 32 : THREADS, SMEM, stream>>>(tk, tv, p);
+  kern<<<grid, p.gather ? THREADS + 32 * (GATHER_WARPS - 1) : THREADS, SMEM, stream>>>(tk, tv, p);
   DLB_CUDA_LAUNCH_CHECK();
   if (p.max_splits > 1) {
     paged_decode_merge_kernel<T, D><<<dim3(p.hq, p.batch), D, 0, stream>>>(p);
