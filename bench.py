@@ -363,7 +363,20 @@ def bench_neighbours(dev, peaks, steps, warmup):
     out["fill_kv_cache"] = _hbm_entry("fill_kv_cache 4 x 8192 tokens, 8 heads x 128, page 64, bf16",
                                       4 * k.numel() * 2, ms, peaks, steps, "268 MB per pass > L2")
     out["fill_kv_cache"]["roofline"]["traffic"] = NCU_TRAFFIC["fill_kv_cache"]
-    del q, k, v_states, kc, vc, cos, sin
+    # paged prefill: the same 4 x 8192 queries against the cache just filled (no history), page 64
+    o_pp = torch.empty_like(q)
+    qlen64 = qlen.to(torch.int64)
+    ms = time_steps(lambda: dl.paged_attention_fwd(q, kc, vc, o_pp, table, start.to(torch.int64), qlen64, qlen64, S),
+                    steps, warmup)
+    pp_flops = sum(4 * S * S * d * hq // 2 for _ in range(B))
+    tf = pp_flops / ms / 1e9
+    out["paged_prefill"] = {"workload": "paged_attention_fwd prefill, C4 shape (B=4 S=8192 Hq=32 Hkv=8 D=128) over "
+                                        "64-token pages, bf16", "ms": ms, "value": tf, "unit": "TFLOP/s",
+                            "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops_sustained"],
+                                         "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops_sustained"],
+                                         "traffic": None, "basis": peaks["basis"]},
+                            "l2": "q/cache/o 670 MB > L2", "gpu_launches": steps}
+    del q, k, v_states, kc, vc, cos, sin, o_pp
     # token-granular decode (page size 1): 16 requests of the decode configuration
     wl = W.DecodeWorkload(batch=16, page=1)
     dd = wl.make(device=dev)

@@ -241,14 +241,13 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_arrive_expect_tx(q_full, Q_BYTES);
 #pragma unroll
       for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(smem + OFF_Q + bx * Q_BOX, &tmap_q, q_full, bx * 64, head, start + q0);
-      for (int j = 0; j < nb; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int row = start + (jb0 + j) * BN;
-        // paged: the 64 keys of block j come from 64 / min(page, 64) pages of this sequence's table
-        const int box_slots = min(p.page_size, BN);
-        const int n_sub = p.paged ? BN / box_slots : 0;
-        int pg[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
+      // paged: the 64 keys of block j come from 64 / min(page, 64) pages of this sequence's table.  The
+      // table entries of block j + 1 are fetched right after block j's K loads are issued, so that the
+      // look-up's latency never sits between a freed stage and its next load.
+      const int box_slots = min(p.page_size, BN);
+      const int n_sub = p.paged ? BN / box_slots : 0;
+      int pg[4] = {0, 0, 0, 0}, sl[4] = {0, 0, 0, 0};
+      auto look_up = [&](int j) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (u >= n_sub) break;
@@ -259,6 +258,18 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           if (tok >= kv_len || page < 0 || page >= p.num_pages) page = 0;
           pg[u] = page;
           sl[u] = tok % p.page_size;
+        }
+      };
+      if (nb > 0) look_up(0);
+      for (int j = 0; j < nb; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int row = start + (jb0 + j) * BN;
+        int pv[4], sv[4];   // block j's pages for the V loads below
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          pv[u] = pg[u];
+          sv[u] = sl[u];
         }
         // K stage s is free once the Q K^T of block j - 2 has retired (s_full), V stage s once its P V has
         // (pv_done): no separate "empty" commits, every commit costs the single issuing thread ~100 clocks
@@ -277,6 +288,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int bx = 0; bx < BOXES; ++bx) tma_load_3d(kd + bx * KV_BOX, &tmap_k, &k_full[s], bx * 64, kvh, row);
         }
+        if (j + 1 < nb) look_up(j + 1);
         if (!mbar_wait(&pv_done[s], ph ^ 1, abort_flag, p.status, 22, j)) break;
         uint8_t* vd = smem + OFF_V + s * KV_BYTES;
         mbar_arrive_expect_tx(&v_full[s], KV_BYTES);
@@ -286,7 +298,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             if (u >= n_sub) break;
 #pragma unroll
             for (int bx = 0; bx < BOXES; ++bx)
-              tma_load_4d(vd + bx * KV_BOX + u * box_slots * 128, &tmap_v, &v_full[s], bx * 64, kvh, sl[u], pg[u]);
+              tma_load_4d(vd + bx * KV_BOX + u * box_slots * 128, &tmap_v, &v_full[s], bx * 64, kvh, sv[u], pv[u]);
           }
         } else {
 #pragma unroll
