@@ -180,7 +180,7 @@ class EpPeerContext:
     """
 
     def __init__(self, group, num_experts: int, device, max_tokens_per_rank: int, top_k: int, hidden: int,
-                 out_hidden: int, inter: int, dtype=torch.bfloat16, pull: bool = True):
+                 out_hidden: int, inter: int, dtype=torch.bfloat16, pull: bool = None):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -220,8 +220,16 @@ class EpPeerContext:
         self.w, self._h_w, self.w_tbl = sym((self.cap,), torch.float32)
         self.meta, self._h_meta, self.meta_tbl = sym((self.cap,), torch.int32)
         # results travel back in one of two ways: pulled by the combine out of the owners' output buffer
-        # `y` (default), or pushed by the down GEMM's epilogue into the senders' `back` buffers
-        self.pull = pull
+        # `y`, or pushed by the down GEMM's epilogue into the senders' `back` buffers.  The push rides under
+        # the main loop of the GEMM's later tiles, the pull is a separate pass; so the push wins whenever the
+        # down GEMM has more than one wave of tiles (measured at 4 GPUs: 0.78 ms pushed, 0.90 ms pulled), and
+        # the pull wins when all tiles finish together and nothing is left to hide the pushes behind
+        # (8 GPUs: 0.478 ms pushed, 0.455 ms pulled).  Default: decide from the expected tile count.
+        if pull is None:
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            m_blocks = (self.max_slots + 127) // 128 + self.experts_per_rank    # balanced routing + padding
+            pull = m_blocks * ((out_hidden + 255) // 256) <= sms
+        self.pull = bool(pull)
         if pull:
             self.y, self._h_y, self.y_tbl = sym((self.cap, out_hidden), dtype)
             result_buf = self.y
@@ -262,8 +270,8 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
       combine  waits for every rank's flag, then reads each token's top-k rows out of the owners' output
                buffers (peer loads) and sums them
     With `ctx.pull` off the down GEMM's epilogue instead stores each row into the SENDER's result buffer
-    and the combine reads locally; measured at 8 GPUs the row fragments a GEMM epilogue can store (16 bytes
-    per thread per row) cost 56 us more per step than the pull.
+    and the combine reads locally.  `EpPeerContext` picks the form from the number of tiles the down GEMM
+    is expected to have (one wave or less: pull).
     """
     from .. import _lib
 

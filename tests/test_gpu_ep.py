@@ -42,8 +42,8 @@ def _worker(rank, world, port, ret):
         dl.check_device_status()
         ok = bool(torch.equal(out, full[sl]))
         # the peer-memory exchange (our own kernels over NVLink) must give the same bits, step after step,
-        # whether the results are pulled by the combine or pushed by the down GEMM's epilogue
-        for pull in (True, False):
+        # whether the results are pulled by the combine or pushed by the down GEMM's epilogue (None: context decides)
+        for pull in (True, False, None):
             pctx = ep_moe.EpPeerContext(dist.group.WORLD, wl.experts, dev, tl, wl.top_k, wl.hidden, wl.hidden,
                                         wl.inter, pull=pull)
             for _ in range(3):
