@@ -71,7 +71,7 @@ def _fixture_value(gen_fn, *args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (DLCompiler)")
     args = ap.parse_args()
     tests = os.path.join(args.reference, "python/dlBLAS/tests/kernels")
     torch.set_num_threads(max(1, os.cpu_count() or 1))
