@@ -170,6 +170,14 @@ def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weig
 # ----------------------------------------------------------------------------------------------
 # Peer-memory variant: dispatch and combine are plain NVLink stores issued by our own kernels
 # ----------------------------------------------------------------------------------------------
+def prefers_pull(slots_per_rank: int, experts_per_rank: int, out_hidden: int, sm_count: int) -> bool:
+    """True when the down GEMM of one rank is expected to fit in one wave of 128 x 256 tiles (one persistent
+    CTA per SM), the case in which pulled results beat pushed ones.  Balanced routing is assumed: a rank
+    receives as many rows as it sends, plus at most one padding block per local expert."""
+    m_blocks = (slots_per_rank + 127) // 128 + experts_per_rank
+    return m_blocks * ((out_hidden + 255) // 256) <= sm_count
+
+
 class EpPeerContext:
     """Symmetric buffers and pointer tables for the peer-memory exchange (see csrc/ep_moe.cu).
 
@@ -227,8 +235,7 @@ class EpPeerContext:
         # (8 GPUs: 0.478 ms pushed, 0.455 ms pulled).  Default: decide from the expected tile count.
         if pull is None:
             sms = torch.cuda.get_device_properties(device).multi_processor_count
-            m_blocks = (self.max_slots + 127) // 128 + self.experts_per_rank    # balanced routing + padding
-            pull = m_blocks * ((out_hidden + 255) // 256) <= sms
+            pull = prefers_pull(self.max_slots, self.experts_per_rank, out_hidden, sms)
         self.pull = bool(pull)
         if pull:
             self.y, self._h_y, self.y_tbl = sym((self.cap, out_hidden), dtype)

@@ -107,3 +107,13 @@ def test_exchange_plan_sizes_and_validation():
         ep_moe.exchange_plan(torch.tensor([[1, -1, 0, 0], [0, 0, 0, 0]]), 0, 2)
     with pytest.raises(AssertionError):
         ep_moe.exchange_plan(torch.tensor([[1, 1, 0], [0, 0, 0]]), 0, 2)
+
+
+def test_result_return_form_follows_the_down_gemm_tile_count():
+    """The peer-memory exchange pulls results when the down GEMM fits one wave of tiles, pushes otherwise:
+    the benchmark shape (4096 tokens, top-2, 8 experts, hidden 4096) on 148 SMs pulls only at 8 ranks."""
+    for world, expect in ((1, False), (2, False), (4, False), (8, True)):
+        slots = 4096 // world * 2
+        assert ep_moe.prefers_pull(slots, 8 // world, 4096, 148) is expect
+    assert ep_moe.prefers_pull(512, 4, 512, 148)          # small problems: one wave
+    assert not ep_moe.prefers_pull(1024, 1, 4096, 132)    # the same 144 tiles on a smaller device: two waves
