@@ -1,6 +1,7 @@
 """Benchmark of the dlBLAS hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ops all|none]
+    python bench.py --profile-case {silu,gating,moe,prefill,decode,rotary} [--steps N]
 
 Headline (one JSON line on stdout): fused_moe on the Mixtral-like configuration
 (T=4096, H=4096, I=14336, E=8, top_k=2, bf16) in TFLOP/s, whole job.  N > 1 runs the
@@ -10,7 +11,11 @@ four configurations (silu_and_mul, grouped gating, varlen prefill, paged decode)
 their own roofline fractions, measured at N=1.
 
 `--impl reference` times the CPU checker (the torch restatement of the reference's own
-test ground truth, oracle/dlblas_oracle.py) on the host cores on a bounded token sample.
+test ground truth, oracle/dlblas_oracle.py) on the host cores, every step one pass over all 4096
+tokens of the same configuration.
+
+`--profile-case` runs one op a few times on a profiler-sized case (inputs larger than L2, a few GB at
+most) and prints one line on stderr; it is the command an `ncu -k regex:<kernel> -c <n>` capture wraps.
 """
 from __future__ import annotations
 
@@ -31,17 +36,16 @@ import torch  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
-# DRAM bytes per launch of the grouped GEMM kernel from the committed ncu capture
-# (profiles/grouped_gemm_*.md); None until a capture exists for the benchmark shape.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark shapes, from ncu captures of the
+# kernels as they are in this tree (a capture on a smaller case is scaled by the units one launch
+# processes); None where the kernel changed after its last capture.
 NCU_TRAFFIC = {
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch at the benchmark shapes, from the one-pass
-    # ncu capture summarised in profiles/dram_traffic_full_size.md
     "grouped_gemm": {"gate_up_silu": 2968.7e6, "down_scatter": 1468.0e6, "per_step": 4436.7e6},
     "silu_and_mul": 229.0e6,
-    "flash_prefill": 2126.8e6,
+    "flash_prefill": None,
     "paged_decode": 4430.5e6,
     "rms_norm": 480.8e6,
-    "apply_rotary_pos_emb": 629.3e6,
+    "apply_rotary_pos_emb": None,
     "fill_kv_cache": 221.9e6,
 }
 
@@ -129,7 +133,7 @@ class ClockSampler:
 def time_steps(fn, steps, warmup, barrier=None, min_warm_s=0.0):
     """W untimed steps (repeated until at least `min_warm_s` seconds of load have passed, so that the
     clock sampler sees the device under load), then K steps between CUDA events on the current stream;
-    returns ms per step."""
+    returns (ms per step, warm-up steps actually run)."""
     t0 = time.perf_counter()
     done = 0
     while done < warmup or time.perf_counter() - t0 < min_warm_s:
@@ -150,7 +154,49 @@ def time_steps(fn, steps, warmup, barrier=None, min_warm_s=0.0):
     torch.cuda.synchronize()
     if barrier is not None:
         barrier()
-    return start.elapsed_time(end) / steps
+    return start.elapsed_time(end) / steps, done
+
+
+def time_op(fn, steps, warmup):
+    return time_steps(fn, steps, warmup)[0]
+
+
+class GemmLaunchTimer:
+    """Brackets every grouped-GEMM launch of the library with a pair of CUDA events while installed, so
+    that the dominant kernel is timed inside the steps, on the stream it is launched on.  The library's
+    public functions stay free of timing arguments: the two launch sites are wrapped from here."""
+
+    def __init__(self):
+        self.pairs = []
+
+    def _wrap(self, fn):
+        def timed(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **kw)
+            e1.record()
+            self.pairs.append((e0, e1))
+            return r
+        return timed
+
+    def __enter__(self):
+        from dlcompiler_b200 import _lib
+        from dlcompiler_b200.kernels import fused_moe as fm
+
+        self._fm, self._lib = fm, _lib.load()
+        self._orig_gemm = fm._grouped_gemm
+        self._orig_sync = self._lib.dlb_moe_grouped_gemm_sync
+        fm._grouped_gemm = self._wrap(self._orig_gemm)
+        self._lib.dlb_moe_grouped_gemm_sync = self._wrap(self._orig_sync)
+        return self
+
+    def __exit__(self, *exc):
+        self._fm._grouped_gemm = self._orig_gemm
+        self._lib.dlb_moe_grouped_gemm_sync = self._orig_sync
+
+    def ms_per_step(self, steps, launches_per_step=2):
+        timed = self.pairs[-launches_per_step * steps:]
+        return sum(a.elapsed_time(b) for a, b in timed) / steps
 
 
 class PipelinedE2E:
@@ -196,9 +242,15 @@ class PipelinedE2E:
         torch.cuda.current_stream().wait_stream(self.s_in)
 
 
-def time_pipelined(pipe, steps, warmup, barrier=None):
-    for _ in range(warmup):
+def time_pipelined(pipe, steps, warmup, barrier=None, min_warm_s=0.0):
+    """Same regime as `time_steps`: W warm-up steps, repeated until `min_warm_s` seconds of load."""
+    t0 = time.perf_counter()
+    done = 0
+    while done < warmup or time.perf_counter() - t0 < min_warm_s:
         pipe.step()
+        done += 1
+        if done % 8 == 0:
+            torch.cuda.synchronize()
     pipe.drain()
     torch.cuda.synchronize()
     if barrier is not None:
@@ -214,11 +266,7 @@ def time_pipelined(pipe, steps, warmup, barrier=None):
     torch.cuda.synchronize()
     if barrier is not None:
         barrier()
-    return start.elapsed_time(end) / steps
-
-
-def flush_l2(buf):
-    buf.zero_()
+    return start.elapsed_time(end) / steps, done
 
 
 # --------------------------------------------------------------------------- per-op benches (N = 1)
@@ -229,7 +277,7 @@ def bench_silu(dev, peaks, steps, warmup):
     wl = W.SiluWorkload()
     x = wl.make()["gate_up"].to(dev)
     out = torch.empty(wl.tokens, wl.hidden, dtype=x.dtype, device=dev)
-    ms = time_steps(lambda: dl.silu_and_mul(x, out), steps, warmup)   # 270 MB per pass > 126 MB L2
+    ms = time_op(lambda: dl.silu_and_mul(x, out), steps, warmup)   # 270 MB per pass > 126 MB L2
     gbs = wl.bytes() / ms / 1e6
     return {"workload": "C1 silu_and_mul bf16 [4096, 2x11008]", "ms": ms, "value": gbs, "unit": "GB/s",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -260,7 +308,7 @@ def bench_gating(dev, peaks, steps, warmup):
     with torch.cuda.graph(graph):
         sweep()
     reps = max(steps, 20)
-    ms = time_steps(graph.replay, reps, max(warmup, 3)) / nbuf
+    ms = time_op(graph.replay, reps, max(warmup, 3)) / nbuf
     gbs = wl.bytes() / ms / 1e6
     return {"workload": "C2 grouped sigmoid gating fp32 [16384, 256] top-8", "ms": ms, "value": gbs, "unit": "GB/s",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -279,7 +327,7 @@ def bench_prefill(dev, peaks, steps, warmup):
     o = torch.empty_like(q)
     lse = torch.empty(wl.hq, q.shape[0], dtype=torch.float32, device=dev)
     st, ln = d["b_start_loc"].to(dev), d["b_seq_len"].to(dev)
-    ms = time_steps(lambda: dl.context_attention_fwd(q, k, v, o, st, ln, d["max_input_len"], lse=lse), steps, warmup)
+    ms = time_op(lambda: dl.context_attention_fwd(q, k, v, o, st, ln, d["max_input_len"], lse=lse), steps, warmup)
     tf = wl.flops() / ms / 1e9
     return {"workload": "C4 varlen causal GQA prefill bf16 B=4 S=8192 Hq=32 Hkv=8 D=128", "ms": ms, "value": tf,
             "unit": "TFLOP/s",
@@ -300,7 +348,7 @@ def bench_decode(dev, peaks, steps, warmup):
     table, lens = d["block_table"].to(dev), d["kv_seqlens"].to(dev)
     qs = torch.arange(wl.batch, device=dev)
     ql = torch.ones(wl.batch, dtype=torch.int64, device=dev)
-    ms = time_steps(lambda: dl.paged_attention_fwd(q, d["k_cache"], d["v_cache"], o, table, qs, ql, lens, 1), steps,
+    ms = time_op(lambda: dl.paged_attention_fwd(q, d["k_cache"], d["v_cache"], o, table, qs, ql, lens, 1), steps,
                     warmup)
     nbytes = wl.bytes(d["kv_seqlens"])
     gbs = nbytes / ms / 1e6
@@ -334,7 +382,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     r = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     w = torch.rand(H, generator=g, device=dev).to(torch.bfloat16)
     o, o_r = torch.empty_like(x), torch.empty_like(x)
-    ms = time_steps(lambda: dl.rms_norm(x, w, 1e-6, residual=r, out=o, out_residual=o_r), steps, warmup)
+    ms = time_op(lambda: dl.rms_norm(x, w, 1e-6, residual=r, out=o, out_residual=o_r), steps, warmup)
     out["rms_norm"] = _hbm_entry("rms_norm + residual bf16 [16384, 4096]", 4 * T * H * 2 + H * 2, ms, peaks, steps,
                                  "537 MB per pass > L2")
     out["rms_norm"]["roofline"]["traffic"] = NCU_TRAFFIC["rms_norm"]
@@ -345,7 +393,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     k = torch.randn(tok, hk, d, generator=g, device=dev).to(torch.bfloat16)
     cos = torch.rand(tok, d, generator=g, device=dev).to(torch.bfloat16)
     sin = torch.rand(tok, d, generator=g, device=dev).to(torch.bfloat16)
-    ms = time_steps(lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k), steps, warmup)
+    ms = time_op(lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k), steps, warmup)
     out["apply_rotary_pos_emb"] = _hbm_entry("rotary in place, q [32768, 32, 128] k [32768, 8, 128] bf16",
                                              2 * (q.numel() + k.numel()) * 2 + 2 * cos.numel() * 2, ms, peaks, steps,
                                              "688 MB per pass > L2")
@@ -359,14 +407,14 @@ def bench_neighbours(dev, peaks, steps, warmup):
     qlen = torch.full((B,), S, dtype=torch.int32, device=dev)
     start = torch.arange(B, dtype=torch.int32, device=dev) * S
     v_states = torch.randn(tok, hk, d, generator=g, device=dev).to(torch.bfloat16)
-    ms = time_steps(lambda: dl.fill_kv_cache(k, v_states, kc, vc, start, qlen, qlen, S, table), steps, warmup)
+    ms = time_op(lambda: dl.fill_kv_cache(k, v_states, kc, vc, start, qlen, qlen, S, table), steps, warmup)
     out["fill_kv_cache"] = _hbm_entry("fill_kv_cache 4 x 8192 tokens, 8 heads x 128, page 64, bf16",
                                       4 * k.numel() * 2, ms, peaks, steps, "268 MB per pass > L2")
     out["fill_kv_cache"]["roofline"]["traffic"] = NCU_TRAFFIC["fill_kv_cache"]
     # paged prefill: the same 4 x 8192 queries against the cache just filled (no history), page 64
     o_pp = torch.empty_like(q)
     qlen64 = qlen.to(torch.int64)
-    ms = time_steps(lambda: dl.paged_attention_fwd(q, kc, vc, o_pp, table, start.to(torch.int64), qlen64, qlen64, S),
+    ms = time_op(lambda: dl.paged_attention_fwd(q, kc, vc, o_pp, table, start.to(torch.int64), qlen64, qlen64, S),
                     steps, warmup)
     pp_flops = sum(4 * S * S * d * hq // 2 for _ in range(B))
     tf = pp_flops / ms / 1e9
@@ -385,7 +433,7 @@ def bench_neighbours(dev, peaks, steps, warmup):
     tb, ln = dd["block_table"].to(dev), dd["kv_seqlens"].to(dev)
     kb, vb = dd["k_cache"].squeeze(1), dd["v_cache"].squeeze(1)
     req = torch.arange(wl.batch, device=dev)
-    ms = time_steps(lambda: dl.decode_attention_fwd(qd, kb, vb, od, tb, req, None, ln, None, tb.size(1), d ** -0.5),
+    ms = time_op(lambda: dl.decode_attention_fwd(qd, kb, vb, od, tb, req, None, ln, None, tb.size(1), d ** -0.5),
                     steps, warmup)
     out["decode_attention_fwd"] = _hbm_entry(f"decode_attention_fwd (page size 1) B=16 ctx_sum={int(ln.sum())} bf16",
                                              wl.bytes(dd["kv_seqlens"]), ms, peaks, 2 * steps, "KV 1.1 GB > L2")
@@ -420,7 +468,8 @@ def cpu_fused_moe(sample_tokens, threads=None, budget_s=12.0, max_passes=6):
 
 
 def run_reference(args):
-    """The reference arm: CPU implementation on the host cores, bounded sample per step."""
+    """The reference arm: the CPU implementation on the host cores, every step one pass over the same
+    configuration as our arm (all 4096 tokens of C3)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         args._stdout_guard.restore()
@@ -432,9 +481,8 @@ def run_reference(args):
     torch.set_num_threads(threads)
     wl = W.MoeWorkload()
     d = wl.make()
-    sample = 256
-    hs = d["hidden_states"][:sample]
-    tw, ti = oracle.softmax_topk(d["router_logits"][:sample], wl.top_k)
+    hs = d["hidden_states"]
+    tw, ti = oracle.softmax_topk(d["router_logits"], wl.top_k)
     ti = ti.long()
     for _ in range(min(args.warmup, 2)):
         oracle.fused_moe(hs, d["w1"], d["w2"], tw, ti)
@@ -442,20 +490,23 @@ def run_reference(args):
     for _ in range(args.steps):
         oracle.fused_moe(hs, d["w1"], d["w2"], tw, ti)
     dt = (time.perf_counter() - t0) / args.steps
-    tf = wl.flops(sample) / dt / 1e12
+    tf = wl.flops() / dt / 1e12
+    what = ("all 4096 tokens per step; torch CPU restatement of the reference test ground truth (the "
+            "reference's Triton kernels cannot run on CPU)")
     line = {
         "impl": "reference", "metric": "fused_moe_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16",
-                   "sample": f"first {sample} tokens per step"},
-        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample} of 4096 tokens per step, torch CPU restatement of the reference "
-                                   "test ground truth (the reference's Triton kernels cannot run on CPU)"},
+        "config": {"workload": MOE_WORKLOAD, "sample": "whole workload every step"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": what},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     args._stdout_guard.restore()
     print(json.dumps(line), flush=True)
+
+
+MOE_WORKLOAD = ("C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16 (moe_align block 128 -> gate/up GEMM+silu -> "
+                "down GEMM x weight -> combine)")
 
 
 # --------------------------------------------------------------------------- headline: fused_moe
@@ -479,7 +530,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist_mod
 
-        os.environ["NCCL_DEBUG"] = os.environ.get("DLB_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
+        os.environ.setdefault("NCCL_DEBUG", "WARN")     # stdout is redirected anyway; a caller's setting stands
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
 
@@ -491,39 +542,44 @@ def run_ours(args):
     # routing inputs of the step: softmax -> top-2 of the seeded router logits (our router kernel)
     tw_dev, ti_dev = dl.softmax_topk(d["router_logits"].to(dev), wl.top_k)
     tw_cpu, ti_cpu = tw_dev.cpu(), ti_dev.cpu()
+    ep_check = None
+    timer = GemmLaunchTimer()
 
     if world == 1:
         wts = wl.make()
         w1, w2 = wts["w1"].to(dev), wts["w2"].to(dev)
         del wts
         hs, tw, ti = d["hidden_states"].to(dev), tw_cpu.to(dev), ti_cpu.to(dev)
-        events = []
 
         def step():
-            return dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k, _events=events)
+            return dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k)
 
+        def e2e_compute(h, w, i):
+            return dl.fused_moe(h, w1, w2, w, i, wl.top_k)
+
+        host_inputs = [d["hidden_states"], tw_cpu, ti_cpu]
+        out_rows = wl.tokens
         launches_per_step = 5
-        with ClockSampler(local_rank) as clk:
-            clk.wait_first()
-            ms = time_steps(step, args.steps, args.warmup, min_warm_s=args.warm_seconds)
-        torch.cuda.synchronize()
-        timed = events[-2 * args.steps:]
-        gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
-        clocks = clk.summary()
-
-        # end to end: pinned host inputs -> device -> fused_moe -> host result, every step
-        pipe = PipelinedE2E([d["hidden_states"], tw_cpu, ti_cpu],
-                            lambda h, w, i: dl.fused_moe(h, w1, w2, w, i, wl.top_k),
-                            (wl.tokens, wl.hidden), torch.bfloat16, dev)
-        ms_e2e = time_pipelined(pipe, args.steps, max(args.warmup, 4))
-        h2d, d2h = pipe.h2d, pipe.d2h
-        dl.check_device_status()
+        warm_steps, warm_s = args.warmup, args.warm_seconds
         parallelism = "single GPU"
-        flops = wl.flops()
     else:
         from dlcompiler_b200.distributed import ep_moe
 
         t_local = wl.tokens // world
+        e_local = wl.experts // world
+        sl = slice(rank * t_local, (rank + 1) * t_local)
+        hs, tw, ti = d["hidden_states"][sl].to(dev), tw_cpu[sl].to(dev), ti_cpu[sl].to(dev)
+        wts = wl.make()
+        # correctness of the sharded step, outside any timed region: this rank's token slice through the
+        # single-GPU fused_moe with ALL experts' weights must give the same bits as the exchange
+        w1_all, w2_all = wts["w1"].to(dev), wts["w2"].to(dev)
+        expect = dl.fused_moe(hs, w1_all, w2_all, tw, ti, wl.top_k)
+        torch.cuda.synchronize()
+        del w1_all, w2_all
+        torch.cuda.empty_cache()
+        w1 = wts["w1"][rank * e_local:(rank + 1) * e_local].to(dev)
+        w2 = wts["w2"][rank * e_local:(rank + 1) * e_local].to(dev)
+        del wts
         exchange = args.exchange
         if exchange == "peer":
             try:
@@ -539,45 +595,61 @@ def run_ours(args):
             ctx = ep_moe.EpMoeContext(dist.group.WORLD, wl.experts, dev)
             ep_step = ep_moe.ep_fused_moe
             launches = ep_moe.KERNELS_PER_STEP
-        e_local = wl.experts // world
-        wts = wl.make()
-        w1 = wts["w1"][rank * e_local:(rank + 1) * e_local].to(dev)
-        w2 = wts["w2"][rank * e_local:(rank + 1) * e_local].to(dev)
-        del wts
-        sl = slice(rank * t_local, (rank + 1) * t_local)
-        hs, tw, ti = d["hidden_states"][sl].to(dev), tw_cpu[sl].to(dev), ti_cpu[sl].to(dev)
-        events = []
 
         def step():
-            return ep_step(ctx, hs, w1, w2, tw, ti, wl.top_k, _events=events)
+            return ep_step(ctx, hs, w1, w2, tw, ti, wl.top_k)
 
-        launches_per_step = launches
-        with ClockSampler(local_rank) as clk:
-            # no step may start while a rank still waits for its sampler: the ranks meet in cross-GPU
-            # barriers with bounded waits
-            clk.wait_first()
-            barrier()
-            # every rank must run the same number of steps: fixed count
-            ms = time_steps(step, args.steps, max(args.warmup, 1000), barrier)
-        torch.cuda.synchronize()
-        timed = events[-2 * args.steps:]
-        gemm_ms = sum(s.elapsed_time(e) for _, s, e in timed) / args.steps
-        clocks = clk.summary()
+        def e2e_compute(h, w, i):
+            return ep_step(ctx, h, w1, w2, w, i, wl.top_k)
 
-        pipe = PipelinedE2E([d["hidden_states"][sl].contiguous(), tw_cpu[sl].contiguous(), ti_cpu[sl].contiguous()],
-                            lambda h, w, i: ep_step(ctx, h, w1, w2, w, i, wl.top_k),
-                            (t_local, wl.hidden), torch.bfloat16, dev)
-        ms_e2e = time_pipelined(pipe, args.steps, max(args.warmup, 4), barrier)
-        h2d, d2h = pipe.h2d * world, pipe.d2h * world
+        # three steps in a row (the symmetric buffers are reused from step to step), each compared bit for bit
+        same = True
+        for _ in range(3):
+            got = step()
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(got, expect))
         dl.check_device_status()
+        flag = torch.tensor([int(same)], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        ep_check = {"ranks": world, "bit_identical": bool(flag.item()), "steps_checked": 3,
+                    "against": "single-GPU fused_moe on each rank's token slice with all experts' weights"}
+        del expect, got
+        host_inputs = [d["hidden_states"][sl].contiguous(), tw_cpu[sl].contiguous(), ti_cpu[sl].contiguous()]
+        out_rows = t_local
+        launches_per_step = launches
+        # every rank must run the same number of steps (the ranks meet in cross-GPU waits): a fixed count,
+        # long enough for the clocks to settle under load
+        warm_steps, warm_s = max(args.warmup, 1000), 0.0
+        how = ("dispatch/combine by our own kernels over NVLink peer memory" if exchange == "peer"
+               else "NCCL all-to-all dispatch/combine")
+        parallelism = f"ep{world}: tokens and experts sharded over {world} ranks, {how}"
+
+    bar = barrier if dist is not None else None
+    with ClockSampler(local_rank) as clk:
+        # no step may start while a rank still waits for its sampler
+        clk.wait_first()
+        barrier()
+        with timer:
+            ms, warm_ran = time_steps(step, args.steps, warm_steps, bar, min_warm_s=warm_s)
+        torch.cuda.synchronize()
+    gemm_ms = timer.ms_per_step(args.steps)
+    clocks = clk.summary()
+
+    # end to end: pinned host inputs -> device -> fused_moe -> host result, every step; same warm-up regime as
+    # the device-only loop, with its own clock record
+    pipe = PipelinedE2E(host_inputs, e2e_compute, (out_rows, wl.hidden), torch.bfloat16, dev)
+    with ClockSampler(local_rank) as clk_e2e:
+        clk_e2e.wait_first()
+        barrier()
+        ms_e2e, warm_ran_e2e = time_pipelined(pipe, args.steps, warm_steps, bar, min_warm_s=warm_s)
+    h2d, d2h = pipe.h2d * world, pipe.d2h * world
+    dl.check_device_status()
+    if dist is not None:
         # max over ranks of the device-timed step
         t = torch.tensor([ms, ms_e2e, gemm_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e, gemm_ms = t.tolist()
-        how = ("dispatch/combine by our own kernels over NVLink peer memory" if exchange == "peer"
-               else "NCCL all-to-all dispatch/combine")
-        parallelism = f"ep{world}: tokens and experts sharded over {world} ranks, {how}"
-        flops = wl.flops()
+    flops = wl.flops()
 
     tflops = flops / ms / 1e9
     e2e_tflops = flops / ms_e2e / 1e9
@@ -587,22 +659,25 @@ def run_ours(args):
     peak = peaks["bf16_tflops_sustained"]
     line = {
         "metric": "fused_moe_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16 (moe_align block 128 -> "
-                               "gate/up GEMM+silu -> down GEMM x weight -> combine)",
-                   "parallelism": parallelism, "l2": "expert weights 2.8 GB per pass > 126 MB L2"},
+        "warmup": warm_ran, "warmup_requested": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": MOE_WORKLOAD, "parallelism": parallelism,
+                   "l2": "expert weights 2.8 GB per pass > 126 MB L2"},
         "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (2 launches per step)", "achieved": gemm_tf,
-                     "peak": peak, "unit": "TFLOP/s", "frac": gemm_tf / peak, "traffic": NCU_TRAFFIC["grouped_gemm"]["per_step"] / 2,
-                     "traffic_by_launch": NCU_TRAFFIC["grouped_gemm"],
+                     "peak": peak, "unit": "TFLOP/s", "frac": gemm_tf / peak,
+                     "frac_of_burst": gemm_tf / peaks["bf16_tflops"], "frac_of_nominal_2250": gemm_tf / 2250.0,
+                     "traffic": NCU_TRAFFIC["grouped_gemm"]["per_step"] / 2 if world == 1 else None,
+                     "traffic_by_launch": NCU_TRAFFIC["grouped_gemm"] if world == 1 else None,
                      "basis": f"{peaks['basis']} sustained cuBLAS bf16", "ms_per_step_in_kernel": gemm_ms},
         "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e,
+                "ms_per_step": ms_e2e, "warmup": warm_ran_e2e, "clocks": clk_e2e.summary(),
                 "how": "public API on pinned host buffers; copies double-buffered on side streams so they "
                        "overlap the neighbouring steps' compute"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    if ep_check is not None:
+        line["ep_check"] = ep_check
     if rank == 0 and world == 1:
         if args.ops != "none":
             ops = {}
@@ -629,6 +704,68 @@ def run_ours(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- profiler-sized cases
+def run_profile_case(args):
+    """One op, a few launches, on a case sized for an `ncu` capture: inputs larger than L2, a few GB on the
+    device at most."""
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import workloads as W
+
+    dev = torch.device("cuda:0")
+    op = args.profile_case
+    if op == "silu":
+        x = W.SiluWorkload().make()["gate_up"].to(dev)                 # the benchmark shape: 270 MB
+        fn = lambda: dl.silu_and_mul(x)
+        what = "silu_and_mul bf16 [4096, 2x11008]"
+    elif op == "gating":
+        wl = W.GatingWorkload(tokens=16384 * 8)                        # 134 MB of logits > L2
+        d = wl.make()
+        lg, b = d["logits"].to(dev), d["bias"].to(dev)
+        fn = lambda: dl.grouped_topk_gating(lg, b, wl.top_k, wl.n_group, wl.topk_group, wl.scale_factor)
+        what = "grouped gating fp32 [131072, 256]"
+    elif op == "moe":
+        wl = W.MoeWorkload(tokens=2048, hidden=4096, inter=7168, experts=4, top_k=2)   # 0.7 GB of weights
+        d = wl.make()
+        tw, ti = dl.softmax_topk(d["router_logits"].to(dev), wl.top_k)
+        hs, w1, w2 = d["hidden_states"].to(dev), d["w1"].to(dev), d["w2"].to(dev)
+        fn = lambda: dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k)
+        what = "fused_moe T=2048 H=4096 I=7168 E=4 top_k=2 bf16"
+    elif op == "prefill":
+        wl = W.PrefillWorkload(batch=2, seq_len=4096)                  # q/k/v/o 168 MB > L2
+        d = wl.make()
+        q, k, v = d["q"].to(dev), d["k"].to(dev), d["v"].to(dev)
+        o = torch.empty_like(q)
+        st, ln = d["b_start_loc"].to(dev), d["b_seq_len"].to(dev)
+        fn = lambda: dl.context_attention_fwd(q, k, v, o, st, ln, d["max_input_len"])
+        what = "prefill B=2 S=4096 Hq=32 Hkv=8 D=128 bf16"
+    elif op == "rotary":
+        tok, hq, hk, dd = 8192, 32, 8, 128                             # q + k 84 MB in, 84 MB out, cos/sin 4 MB
+        g = torch.Generator(device=dev)
+        g.manual_seed(7)
+        q = torch.randn(tok, hq, dd, generator=g, device=dev).to(torch.bfloat16)
+        k = torch.randn(tok, hk, dd, generator=g, device=dev).to(torch.bfloat16)
+        cos = torch.rand(tok, dd, generator=g, device=dev).to(torch.bfloat16)
+        sin = torch.rand(tok, dd, generator=g, device=dev).to(torch.bfloat16)
+        fn = lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k)
+        what = "rotary in place q [8192, 32, 128] k [8192, 8, 128] bf16"
+    else:
+        wl = W.DecodeWorkload(batch=16)                                # ~1.1 GB of KV cache
+        d = wl.make(device=dev)
+        q = d["q"].to(dev)
+        o = torch.empty_like(q)
+        tb, ln = d["block_table"].to(dev), d["kv_seqlens"].to(dev)
+        qs, ql = torch.arange(wl.batch, device=dev), torch.ones(wl.batch, dtype=torch.int64, device=dev)
+        fn = lambda: dl.paged_attention_fwd(q, d["k_cache"], d["v_cache"], o, tb, qs, ql, ln, 1)
+        what = f"paged decode B=16 ctx_sum={int(d['kv_seqlens'].sum())} page 64 bf16"
+    iters = max(1, min(args.steps, 8))
+    for _ in range(iters):
+        fn()
+    torch.cuda.synchronize()
+    dl.check_device_status()
+    args._stdout_guard.restore()
+    print(f"profile case {op}: {what}, {iters} iterations", file=sys.stderr)
 
 
 class _StdoutToStderr:
@@ -659,11 +796,17 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=4096)
     ap.add_argument("--warm-seconds", type=float, default=1.0,
                     help="N = 1: keep warming up until this much wall time has passed (device under load)")
+    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "decode", "rotary"],
+                    help="run one op --steps times (at most 8) on a profiler-sized case and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     guard = _StdoutToStderr()
     args._stdout_guard = guard
-    if args.impl == "reference":
+    if args.profile_case is not None:
+        if "--steps" not in sys.argv:
+            args.steps = 2
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

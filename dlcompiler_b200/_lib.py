@@ -24,6 +24,8 @@ _DTYPES = {torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16, torch.float32: 
 SIGNATURES = {
     "dlb_version": (c_int, []),
     "dlb_last_error": (c_char_p, []),
+    "dlb_set_wait_budget_ms": (c_int, [c_int64]),
+    "dlb_moe_start_end": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "dlb_silu_and_mul": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "dlb_grouped_topk_gating": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int,
                                         c_int, c_int, c_int, c_int, c_float, c_void_p]),
@@ -50,11 +52,12 @@ SIGNATURES = {
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int64,
                             c_int, c_void_p]),
     "dlb_ep_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_int, c_int,
-                               c_void_p, c_void_p]),
+                               c_void_p, c_void_p, c_void_p]),
     "dlb_ep_combine_pull": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                     c_int64, c_int, c_void_p, c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),
     "dlb_ep_barrier": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
+    "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_int,
+                                c_int64, c_int64, c_void_p]),
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
@@ -163,6 +166,18 @@ def status_word(device: torch.device) -> torch.Tensor:
         t = torch.zeros(4, dtype=torch.int32, device=device)
         _status_words[idx] = t
     return t
+
+
+def existing_status_word(device: torch.device):
+    """The device's status word if some earlier call created it, else None (the kernels take NULL).
+    For call paths that must not allocate."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return _status_words.get(idx)
+
+
+def set_wait_budget_ms(ms: int) -> None:
+    """Limit, in milliseconds, of every wait on a flag raised by another GPU (default 2000)."""
+    check(load().dlb_set_wait_budget_ms(int(ms)), "set_wait_budget_ms")
 
 
 def check_device_status(device=None) -> None:

@@ -18,6 +18,7 @@ import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
+INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 BUILD_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libdlblas_b200.so")
 
@@ -49,6 +50,9 @@ def _digest(path: str) -> str:
         if hdr.endswith((".cuh", ".h")):
             with open(os.path.join(CSRC, hdr), "rb") as f:
                 h.update(f.read())
+    for hdr in sorted(os.listdir(INCLUDE)):
+        with open(os.path.join(INCLUDE, hdr), "rb") as f:
+            h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()
 
@@ -59,7 +63,7 @@ def _compile_one(src: str, force: bool, verbose: bool) -> tuple[str, str]:
     dig = _digest(src)
     if not force and os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == dig:
         return obj, ""
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", CSRC, "-I", INCLUDE, "-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")

@@ -26,10 +26,10 @@
 #define DLB_ERR_DRIVER (-4)
 #define DLB_ERR_TOO_LARGE (-5)
 
-// Element types accepted at the C boundary.
-#define DLB_DTYPE_F16 0
-#define DLB_DTYPE_BF16 1
-#define DLB_DTYPE_F32 2
+// The public prototypes: every translation unit that defines an entry point sees its declaration, so
+// a definition whose arguments drift from the header fails to compile.  The element type codes
+// (DLB_DTYPE_*) and the flag values of the boundary come from there.
+#include "dlblas_b200.h"
 
 // Layout of the device status word array (int32[4]) that kernels with bounded
 // waits write when they give up:  [0] = error code (0 = none), [1] = wait site,
@@ -57,6 +57,9 @@ void set_last_error(const char* fmt, ...);
       return (int)e__;                                                      \
     }                                                                       \
   } while (0)
+
+// Wall-clock limit of a wait on another GPU's flag (dlb_set_wait_budget_ms; 2 s unless changed).
+uint64_t wait_budget_ns();
 
 // Cached per-device properties (immutable after first query).
 int sm_count(int device);

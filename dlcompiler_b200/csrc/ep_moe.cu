@@ -46,7 +46,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
 // Signal every peer (slot, my rank) = epoch, then wait until every peer's flag in my own copy
 // reached the epoch.  Executed by threads 0..world-1 of one CTA.  Returns false on timeout.
 __device__ __forceinline__ bool cross_gpu_barrier(const PeerPtrs& flags, int slot, int rank, int world, int epoch,
-                                                  int* status, int site) {
+                                                  int* status, int site, uint64_t budget_ns) {
   const int t = threadIdx.x;
   bool ok = true;
   if (t < world) {
@@ -59,7 +59,7 @@ __device__ __forceinline__ bool cross_gpu_barrier(const PeerPtrs& flags, int slo
       if ((it & 0x3f) == 0x3f) {
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) t0 = now;
-        if (now - t0 > DLB_WAIT_BUDGET_NS) {
+        if (now - t0 > budget_ns) {
           ok = false;
           if (status != nullptr && atomicCAS(status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
             status[1] = site;
@@ -76,8 +76,8 @@ __device__ __forceinline__ bool cross_gpu_barrier(const PeerPtrs& flags, int slo
 }
 
 __global__ void __launch_bounds__(32) ep_barrier_kernel(const PeerPtrs flags, int slot, int rank, int world,
-                                                        int epoch, int* status) {
-  cross_gpu_barrier(flags, slot, rank, world, epoch, status, 42 + slot);
+                                                        int epoch, int* status, uint64_t budget_ns) {
+  cross_gpu_barrier(flags, slot, rank, world, epoch, status, 42 + slot, budget_ns);
 }
 
 // ----------------------------------------------------------------------------
@@ -94,6 +94,7 @@ struct EpRouteParams {
   int32_t* row_map;               // [cap]
   int numel, ids_are_int64, rank, world, experts, cap, epoch;
   int* status;
+  uint64_t budget_ns;             // wall-clock limit of the cross-GPU wait
 };
 
 __device__ __forceinline__ int load_id(const void* ids, int i, int is64) {
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(ep::PLAN_THREADS) ep_route_kernel(const EpRout
     for (int r = 0; r < p.world; ++r) reinterpret_cast<int32_t*>(p.counts.p[r])[p.rank * E + e] = counts[e];
   __threadfence_system();
   __syncthreads();
-  cross_gpu_barrier(p.flags, 0, p.rank, p.world, p.epoch, p.status, 41);
+  cross_gpu_barrier(p.flags, 0, p.rank, p.world, p.epoch, p.status, 41, p.budget_ns);
   __syncthreads();
   const volatile int32_t* cm = reinterpret_cast<const volatile int32_t*>(p.counts.p[p.rank]);
   for (int e = t; e < E; e += ep::PLAN_THREADS) {
@@ -246,7 +247,8 @@ __global__ void __launch_bounds__(256) ep_send_kernel(const EpSendParams p) {
 }
 
 // Threads 0..world-1 of the CTA wait (bounded) until wait_flags[r] >= epoch, then the whole CTA proceeds.
-__device__ __forceinline__ void wait_all_ranks(const int* wait_flags, int world, int epoch, int* status, int site) {
+__device__ __forceinline__ void wait_all_ranks(const int* wait_flags, int world, int epoch, int* status, int site,
+                                               uint64_t budget_ns) {
   if (threadIdx.x < world) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
@@ -254,7 +256,7 @@ __device__ __forceinline__ void wait_all_ranks(const int* wait_flags, int world,
       if ((spin & 0x3f) == 0x3f) {
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) t0 = now;
-        if (now - t0 > DLB_WAIT_BUDGET_NS) {
+        if (now - t0 > budget_ns) {
           if (status != nullptr && atomicCAS(status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
             status[1] = site;
             status[2] = (int)blockIdx.x;
@@ -274,9 +276,10 @@ template <typename T>
 __global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ partial, T* __restrict__ out,
                                                          int64_t tokens, int top_k, int hidden,
                                                          int64_t out_row_stride, const int* wait_flags, int world,
-                                                         int epoch, int* status) {
+                                                         int epoch, int* status, const int32_t* __restrict__ dest_pos,
+                                                         uint64_t budget_ns) {
   using T2 = typename Elem<T>::T2;
-  wait_all_ranks(wait_flags, world, epoch, status, 44);
+  wait_all_ranks(wait_flags, world, epoch, status, 44, budget_ns);
   const int vecs = hidden / 8;
   const int64_t total = tokens * (int64_t)vecs;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -287,6 +290,9 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const T* __restrict__ p
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < top_k; ++k) {
+      // a slot that was sent nowhere (expert id out of range) has no row this step: its place in the
+      // buffer still holds an earlier step's data
+      if (dest_pos != nullptr && dest_pos[t * top_k + k] < 0) continue;
       // written by other GPUs during this step: bypass any stale cached copy
       const uint4 x = __ldcv(reinterpret_cast<const uint4*>(partial + (t * top_k + k) * (int64_t)hidden) + v);
       const T2* x2 = reinterpret_cast<const T2*>(&x);
@@ -318,12 +324,13 @@ struct EpPullParams {
   int* status;
   int64_t y_row_stride, out_row_stride, tokens;
   int top_k, hidden, experts, world, cap, ids_are_int64, epoch;
+  uint64_t budget_ns;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) ep_combine_pull_kernel(const EpPullParams p) {
   using T2 = typename Elem<T>::T2;
-  wait_all_ranks(p.wait_flags, p.world, p.epoch, p.status, 45);
+  wait_all_ranks(p.wait_flags, p.world, p.epoch, p.status, 45, p.budget_ns);
   const int vecs = p.hidden / 8;
   const int epr = p.experts / p.world;
   const int64_t total = p.tokens * (int64_t)vecs;
@@ -389,7 +396,7 @@ extern "C" int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int wo
   PeerPtrs f;
   const int rc = fill_ptrs(&f, flags_sym, world, "flags");
   if (rc != DLB_OK) return rc;
-  ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, slot, rank, world, epoch, status);
+  ep_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, slot, rank, world, epoch, status, wait_budget_ns());
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }
@@ -426,6 +433,7 @@ extern "C" int dlb_ep_route(const void* topk_ids, int ids_are_int64, int64_t num
   p.cap = (int)cap;
   p.epoch = epoch;
   p.status = status;
+  p.budget_ns = wait_budget_ns();
   const size_t smem = sizeof(int32_t) * (size_t)experts * (6 + ep::PLAN_THREADS / 32);
   cudaError_t e = cudaFuncSetAttribute(ep_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -487,7 +495,7 @@ extern "C" int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_
 
 extern "C" int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
                               int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
-                              int32_t* status, void* stream) {
+                              const int32_t* dest_pos, int32_t* status, void* stream) {
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0, DLB_ERR_BAD_ARG, "ep_combine: bad sizes");
   DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && wait_flags != nullptr, DLB_ERR_BAD_ARG,
@@ -504,11 +512,11 @@ extern "C" int dlb_ep_combine(const void* partial, void* out, int64_t tokens, in
   if (dtype == DLB_DTYPE_BF16) {
     ep_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
         (const __nv_bfloat16*)partial, (__nv_bfloat16*)out, tokens, top_k, (int)hidden, out_row_stride, wait_flags,
-        world, epoch, status);
+        world, epoch, status, dest_pos, wait_budget_ns());
   } else if (dtype == DLB_DTYPE_F16) {
     ep_combine_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)partial, (__half*)out, tokens, top_k,
                                                                 (int)hidden, out_row_stride, wait_flags, world, epoch,
-                                                                status);
+                                                                status, dest_pos, wait_budget_ns());
   } else {
     set_last_error("ep_combine: unsupported dtype %d", dtype);
     return DLB_ERR_UNSUPPORTED;
@@ -550,6 +558,7 @@ extern "C" int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, con
   p.cap = (int)cap;
   p.ids_are_int64 = ids_are_int64;
   p.epoch = epoch;
+  p.budget_ns = wait_budget_ns();
   const int64_t total = tokens * (hidden / 8);
   int64_t blocks = (total + 255) / 256;
   if (blocks < 1) blocks = 1;   // the wait still has to happen so that the next step may reuse the buffers

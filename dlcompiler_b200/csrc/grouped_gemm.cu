@@ -78,6 +78,7 @@ struct GroupedGemmParams {
   int* signal_flags[gg::MAX_PEERS];  // after the last store: the last CTA writes sync_epoch to signal_flags[r][0]
   int* done_counter;                 // device counter used to find the last CTA (left at zero)
   int sync_world, sync_epoch;
+  uint64_t wait_budget_ns;           // wall-clock limit of the wait on wait_flags
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -205,7 +206,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if ((spin & 0x3f) == 0x3f) {
               const uint64_t now = globaltimer_ns();
               if (t0 == 0) t0 = now;
-              if (now - t0 > DLB_WAIT_BUDGET_NS) {
+              if (now - t0 > p.wait_budget_ns) {
                 if (p.status != nullptr && atomicCAS(p.status, DLB_DEV_OK, DLB_DEV_WAIT_TIMEOUT) == DLB_DEV_OK) {
                   p.status[1] = 5;
                   p.status[2] = (int)blockIdx.x;
@@ -475,6 +476,7 @@ static int grouped_gemm_impl(const void* a, int64_t a_rows, int64_t a_row_stride
   p.done_counter = done_counter;
   p.sync_world = sync_world;
   p.sync_epoch = sync_epoch;
+  p.wait_budget_ns = wait_budget_ns();
   for (int i = 0; i < MAX_PEERS; ++i)
     p.signal_flags[i] = (signal_flags != nullptr && i < sync_world) ? (int*)signal_flags[i] : nullptr;
   if (signal_flags != nullptr)

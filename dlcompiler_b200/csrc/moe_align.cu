@@ -122,10 +122,13 @@ __global__ void __launch_bounds__(256) moe_permute_rows_kernel(const uint4* __re
 
 // out[t, :] = sum_k partial[t * top_k + k, :]  accumulated in fp32, rounded once
 // (torch's bf16 `sum(dim=1)`, python/dlBLAS/dlblas/kernels/fused_moe.py:375).
+// With `topk_ids` given, a slot whose id lies outside [id_lo, id_hi) adds nothing: no kernel wrote its row
+// (the reference zero-fills the whole buffer for that case, fused_moe.py:329-332,355-358).
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ partial, T* __restrict__ out,
                                                           int64_t tokens, int top_k, int hidden,
-                                                          int64_t out_row_stride) {
+                                                          int64_t out_row_stride, const void* __restrict__ topk_ids,
+                                                          int ids_are_int64, int64_t id_lo, int64_t id_hi) {
   using T2 = typename Elem<T>::T2;
   const int vecs = hidden / 8;
   const int64_t total = tokens * (int64_t)vecs;
@@ -137,6 +140,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < top_k; ++k) {
+      if (topk_ids != nullptr) {
+        const int64_t id = ids_are_int64 ? reinterpret_cast<const int64_t*>(topk_ids)[t * top_k + k]
+                                         : (int64_t)reinterpret_cast<const int32_t*>(topk_ids)[t * top_k + k];
+        if (id < id_lo || id >= id_hi) continue;
+      }
       const uint4 x = __ldcs(reinterpret_cast<const uint4*>(partial + (t * top_k + k) * (int64_t)hidden) + v);
       const T2* x2 = reinterpret_cast<const T2*>(&x);
 #pragma unroll
@@ -154,7 +162,65 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
   }
 }
 
+// Per-expert [start, end) ranges inside the ascending sort of the flattened ids
+// (python/dlBLAS/dlblas/kernels/fused_moe.py:238-293): start = number of ids smaller than the expert's
+// (negative ids sort first and count), end = start + the expert's count; an expert without slots gets
+// start = end = 0, as the reference's kernel leaves it.  One CTA; counts are integer adds, so the result
+// does not depend on the order of the atomics.
+template <typename IdT, typename OutT>
+__global__ void __launch_bounds__(ALIGN_THREADS) moe_start_end_kernel(const IdT* __restrict__ topk_ids, int numel,
+                                                                      int num_experts, OutT* __restrict__ exp_start,
+                                                                      OutT* __restrict__ exp_end) {
+  extern __shared__ int32_t smem[];
+  int32_t* counts = smem;            // [E + 1]; entry E counts the negative ids
+  const int tid = threadIdx.x;
+  for (int e = tid; e <= num_experts; e += ALIGN_THREADS) counts[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < numel; i += ALIGN_THREADS) {
+    const int64_t e = (int64_t)topk_ids[i];
+    if (e < 0) atomicAdd(&counts[num_experts], 1);
+    else if (e < num_experts) atomicAdd(&counts[(int)e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = counts[num_experts];
+    for (int e = 0; e < num_experts; ++e) {
+      const int c = counts[e];
+      exp_start[e] = (OutT)(c > 0 ? acc : 0);
+      exp_end[e] = (OutT)(c > 0 ? acc + c : 0);
+      acc += c;
+    }
+  }
+}
+
 }  // namespace dlb
+
+extern "C" int dlb_moe_start_end(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts,
+                                 void* exp_start, void* exp_end, int out_is_int64, void* stream) {
+  using namespace dlb;
+  DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 30), DLB_ERR_TOO_LARGE, "moe_start_end: numel=%lld out of range",
+                (long long)numel);
+  DLB_CHECK_ARG(num_experts >= 1 && num_experts <= 1024, DLB_ERR_UNSUPPORTED,
+                "moe_start_end: experts=%d not in [1,1024]", num_experts);
+  DLB_CHECK_ARG(exp_start && exp_end && (numel == 0 || topk_ids), DLB_ERR_BAD_ARG, "moe_start_end: null pointer");
+  const size_t smem = sizeof(int32_t) * ((size_t)num_experts + 1);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n = (int)numel;
+  if (ids_are_int64 && out_is_int64)
+    moe_start_end_kernel<int64_t, int64_t><<<1, ALIGN_THREADS, smem, s>>>((const int64_t*)topk_ids, n, num_experts,
+                                                                         (int64_t*)exp_start, (int64_t*)exp_end);
+  else if (ids_are_int64)
+    moe_start_end_kernel<int64_t, int32_t><<<1, ALIGN_THREADS, smem, s>>>((const int64_t*)topk_ids, n, num_experts,
+                                                                         (int32_t*)exp_start, (int32_t*)exp_end);
+  else if (out_is_int64)
+    moe_start_end_kernel<int32_t, int64_t><<<1, ALIGN_THREADS, smem, s>>>((const int32_t*)topk_ids, n, num_experts,
+                                                                         (int64_t*)exp_start, (int64_t*)exp_end);
+  else
+    moe_start_end_kernel<int32_t, int32_t><<<1, ALIGN_THREADS, smem, s>>>((const int32_t*)topk_ids, n, num_experts,
+                                                                         (int32_t*)exp_start, (int32_t*)exp_end);
+  DLB_CUDA_LAUNCH_CHECK();
+  return DLB_OK;
+}
 
 extern "C" int dlb_moe_align_block_size(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts,
                                         int block, int32_t* sorted_token_ids, int64_t sorted_capacity,
@@ -220,7 +286,8 @@ extern "C" int dlb_moe_permute_rows(const void* src, void* dst, const int32_t* s
 }
 
 extern "C" int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
-                               int64_t out_row_stride, int dtype, void* stream) {
+                               int64_t out_row_stride, int dtype, const void* topk_ids, int ids_are_int64,
+                               int64_t id_lo, int64_t id_hi, void* stream) {
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0, DLB_ERR_BAD_ARG, "moe_combine: bad sizes");
   if (tokens == 0 || hidden == 0) return DLB_OK;
@@ -234,10 +301,12 @@ extern "C" int dlb_moe_combine(const void* partial, void* out, int64_t tokens, i
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DLB_DTYPE_BF16) {
     moe_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>(
-        (const __nv_bfloat16*)partial, (__nv_bfloat16*)out, tokens, top_k, (int)hidden, out_row_stride);
+        (const __nv_bfloat16*)partial, (__nv_bfloat16*)out, tokens, top_k, (int)hidden, out_row_stride, topk_ids,
+        ids_are_int64, id_lo, id_hi);
   } else if (dtype == DLB_DTYPE_F16) {
     moe_combine_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((const __half*)partial, (__half*)out, tokens, top_k,
-                                                                 (int)hidden, out_row_stride);
+                                                                 (int)hidden, out_row_stride, topk_ids, ids_are_int64,
+                                                                 id_lo, id_hi);
   } else {
     set_last_error("moe_combine: unsupported dtype %d", dtype);
     return DLB_ERR_UNSUPPORTED;

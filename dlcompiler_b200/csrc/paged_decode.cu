@@ -646,7 +646,6 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
 //     split) slot the merge pass reads was written by the split pass of the same
 //     call.  Two calls whose kernels overlap on the GPU (different streams) race
 //     on it; serialise them.
-#define DLB_DECODE_STATIC_FLOATS (8ll * 1024 * 1024)
 
 namespace dlb {
 static __device__ __align__(256) float g_decode_scratch[DLB_DECODE_STATIC_FLOATS];

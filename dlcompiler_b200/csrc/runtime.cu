@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -18,6 +19,10 @@ void set_last_error(const char* fmt, ...) {
   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
   va_end(ap);
 }
+
+static std::atomic<uint64_t> g_wait_budget_ns{DLB_WAIT_BUDGET_NS};
+
+uint64_t wait_budget_ns() { return g_wait_budget_ns.load(std::memory_order_relaxed); }
 
 int current_device() {
   int dev = 0;
@@ -100,5 +105,11 @@ extern "C" {
 int dlb_version(void) { return 100; }
 
 const char* dlb_last_error(void) { return dlb::g_last_error; }
+
+int dlb_set_wait_budget_ms(int64_t ms) {
+  DLB_CHECK_ARG(ms >= 1 && ms <= 60000, DLB_ERR_BAD_ARG, "wait budget %lld ms not in [1, 60000]", (long long)ms);
+  dlb::g_wait_budget_ns.store((uint64_t)ms * 1000000ull, std::memory_order_relaxed);
+  return DLB_OK;
+}
 
 }  // extern "C"

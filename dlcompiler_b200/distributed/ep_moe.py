@@ -49,10 +49,11 @@ class CudaOps:
         return _permute_rows(src, row_map, n, src.size(0) * div, div, rows)
 
     @staticmethod
-    def expert_mlp(rows, weights, expert_of_row, w1, w2, events=None):
+    def expert_mlp(rows, weights, expert_of_row, w1, w2):
         """Rows [R, H] with their local expert id and routing weight -> down(silu(gate)*up) * weight, [R, H_out]."""
         from .. import _lib
-        from ..kernels.fused_moe import BLOCK_M, _EventPair, _grouped_gemm, _moe_align, _permute_rows
+        from ..kernels import fused_moe as fm
+        from ..kernels.fused_moe import BLOCK_M, _moe_align, _permute_rows
 
         R = rows.size(0)
         E, N, _ = w1.shape
@@ -60,25 +61,28 @@ class CudaOps:
         cap = sorted_ids.numel()
         a_sorted = _permute_rows(rows, sorted_ids, num_post, R, 1, cap)
         act = torch.empty((cap, N // 2), dtype=rows.dtype, device=rows.device)
-        ev = _EventPair(events, "grouped_gemm_gate_up_silu")
-        _grouped_gemm(a_sorted, w1, act, N // 2, sorted_ids, block_start, None, R, _lib.GEMM_FUSE_SILU)
-        ev.stop()
+        fm._grouped_gemm(a_sorted, w1, act, N // 2, sorted_ids, block_start, None, R, _lib.GEMM_FUSE_SILU)
         out = torch.empty((R, w2.size(1)), dtype=rows.dtype, device=rows.device)
-        ev = _EventPair(events, "grouped_gemm_down_scatter")
-        _grouped_gemm(act, w2, out, w2.size(1), sorted_ids, block_start, weights, R,
-                      _lib.GEMM_WEIGHT | _lib.GEMM_SCATTER)
-        ev.stop()
+        fm._grouped_gemm(act, w2, out, w2.size(1), sorted_ids, block_start, weights, R,
+                         _lib.GEMM_WEIGHT | _lib.GEMM_SCATTER)
         return out
 
     @staticmethod
-    def combine(partial, tokens, top_k):
+    def combine(partial, tokens, top_k, topk_ids, num_experts):
+        """Sum of each token's top-k rows; slots whose expert id is outside [0, num_experts) add nothing."""
         from .. import _lib
 
         out = torch.empty((tokens, partial.size(1)), dtype=partial.dtype, device=partial.device)
+        ids = topk_ids.reshape(-1)
+        if ids.dtype not in (torch.int32, torch.int64):
+            ids = ids.to(torch.int64)
+        ids = ids.contiguous()
         lib = _lib.load()
         with torch.cuda.device(partial.device):
             rc = lib.dlb_moe_combine(partial.data_ptr(), out.data_ptr(), tokens, top_k, partial.size(1),
-                                     out.stride(0), _lib.dtype_code(out), _lib.stream_ptr(partial.device))
+                                     out.stride(0), _lib.dtype_code(out), ids.data_ptr(),
+                                     int(ids.dtype == torch.int64), 0, num_experts,
+                                     _lib.stream_ptr(partial.device))
         _lib.check(rc, "moe_combine")
         return out
 
@@ -119,8 +123,7 @@ def exchange_plan(count_matrix: torch.Tensor, rank: int, experts_per_rank: int):
     return send_splits, recv_splits, recv_expert_counts
 
 
-def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int,
-                 _events: list = None):
+def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int):
     """fused_moe over an expert-parallel group.  `topk_ids` are GLOBAL expert ids; `w1_local` /
     `w2_local` hold experts [rank*E/G, (rank+1)*E/G).  Returns this rank's tokens' outputs."""
     ops = ctx.ops
@@ -154,7 +157,7 @@ def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weig
     local_expert = torch.arange(epr, dtype=torch.int32, device=dev).repeat(ctx.world)
     expert_of_row = torch.repeat_interleave(local_expert, recv_expert_counts.reshape(-1).to(dev), output_size=R)
     if R > 0:
-        y = ops.expert_mlp(recv_rows, recv_w, expert_of_row, w1_local, w2_local, _events)
+        y = ops.expert_mlp(recv_rows, recv_w, expert_of_row, w1_local, w2_local)
     else:
         y = torch.empty((0, w2_local.size(1)), dtype=hidden_states.dtype, device=dev)
 
@@ -164,7 +167,7 @@ def ep_fused_moe(ctx: EpMoeContext, hidden_states, w1_local, w2_local, topk_weig
     inverse = torch.empty(numel, dtype=torch.int32, device=dev)
     inverse[sorted_slots.long()] = torch.arange(numel, dtype=torch.int32, device=dev)
     partial = ops.gather_rows(back, inverse, numel, 1)                            # slot order [T*topk, H]
-    return ops.combine(partial, T, topk)
+    return ops.combine(partial, T, topk, topk_ids, ctx.num_experts)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -264,8 +267,7 @@ class EpPeerContext:
 PEER_KERNELS_PER_STEP = 5  # route, send, gemm (gate/up), gemm (down + peer scatter), combine
 
 
-def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int,
-                      _events: list = None):
+def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, topk_weights, topk_ids, topk: int):
     """Expert-parallel fused_moe whose token exchange runs inside our own kernels over peer memory.
 
     Same contract as `ep_fused_moe`.  Five launches per step, nothing returns to the host in between:
@@ -313,20 +315,12 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
                              ctx.meta_tbl, ctx.flags_tbl, ctx.counters[0:1].data_ptr(), numel, topk, rank, world,
                              ctx.num_experts, ctx.cap, epoch, stream)
         _lib.check(rc, "ep_send")
-        if _events is not None:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
         rc = lib.dlb_moe_grouped_gemm_sync(
             ctx.rows.data_ptr(), ctx.cap, ctx.rows.stride(0), w1_local.data_ptr(), E_local, N1, H, w1_local.stride(1),
             ctx.act.data_ptr(), None, 0, ctx.act.stride(0), ctx.inter, ctx.row_map.data_ptr(),
             ctx.block_start.data_ptr(), None, None, ctx.cap, _lib.GEMM_FUSE_SILU, dt,
             flags_local + 4 * (1 * 16), None, None, world, epoch, ctx.status.data_ptr(), stream)
         _lib.check(rc, "moe_grouped_gemm_sync(gate/up)")
-        if _events is not None:
-            e1.record()
-            _events.append(("grouped_gemm_gate_up_silu", e0, e1))
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
         if ctx.pull:
             rc = lib.dlb_moe_grouped_gemm_sync(
                 ctx.act.data_ptr(), ctx.cap, ctx.act.stride(0), w2_local.data_ptr(), E_local, H_out, inter,
@@ -341,9 +335,6 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
                 _lib.GEMM_WEIGHT | _lib.GEMM_PEER, dt, None, ctx.signal2_tbl, ctx.counters[1:2].data_ptr(), world,
                 epoch, ctx.status.data_ptr(), stream)
         _lib.check(rc, "moe_grouped_gemm_sync(down)")
-        if _events is not None:
-            e1.record()
-            _events.append(("grouped_gemm_down", e0, e1))
         if ctx.pull:
             rc = lib.dlb_ep_combine_pull(ctx.y_tbl, ctx.y.stride(0), ids.data_ptr(), is64, ctx.dest_pos.data_ptr(),
                                          out.data_ptr(), T, topk, H_out, out.stride(0), dt,
@@ -351,6 +342,7 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
                                          ctx.status.data_ptr(), stream)
         else:
             rc = lib.dlb_ep_combine(ctx.back.data_ptr(), out.data_ptr(), T, topk, H_out, out.stride(0), dt,
-                                    flags_local + 4 * (2 * 16), world, epoch, ctx.status.data_ptr(), stream)
+                                    flags_local + 4 * (2 * 16), world, epoch, ctx.dest_pos.data_ptr(),
+                                    ctx.status.data_ptr(), stream)
         _lib.check(rc, "ep_combine")
     return out

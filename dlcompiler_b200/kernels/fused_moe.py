@@ -81,22 +81,6 @@ def _grouped_gemm(a, b, out, n_out, row_map, block_start, weights, numel, flags)
     _lib.check(rc, "moe_grouped_gemm")
 
 
-class _EventPair:
-    """Optional CUDA-event bracket around one launch on the current stream."""
-
-    def __init__(self, sink, name):
-        self.sink, self.name = sink, name
-        if sink is not None:
-            self.start = torch.cuda.Event(enable_timing=True)
-            self.end = torch.cuda.Event(enable_timing=True)
-            self.start.record()
-
-    def stop(self):
-        if self.sink is not None:
-            self.end.record()
-            self.sink.append((self.name, self.start, self.end))
-
-
 def fused_moe(hidden_states: torch.Tensor,
               w1: torch.Tensor,
               w2: torch.Tensor,
@@ -105,8 +89,7 @@ def fused_moe(hidden_states: torch.Tensor,
               topk: int,
               expert_offset: int = 0,
               num_experts: int = None,
-              renormalize: bool = False,
-              _events: list = None) -> torch.Tensor:
+              renormalize: bool = False) -> torch.Tensor:
     """Mixture-of-experts MLP: out[t] = sum_k w[t,k] * down_e(silu(gate_e(x_t)) * up_e(x_t)), e = ids[t,k].
 
     Arguments as in the reference (fused_moe.py:296-304): `w1` is [E, 2*I, H] with the gate
@@ -115,10 +98,9 @@ def fused_moe(hidden_states: torch.Tensor,
     set (ids outside the slice contribute zero, as in the reference's expert-parallel mode).
     Rounding points match the reference: GEMM outputs are rounded to the activation dtype,
     silu and the product are rounded separately, routing weights are applied in fp32 before the
-    cast, and the top-k sum accumulates in fp32.
-
-    `_events`, when a list, receives (kernel name, start event, end event) for the two grouped
-    GEMM launches (used by the benchmark to time the dominant kernel inside a step).
+    cast, and the top-k sum accumulates in fp32.  A slot whose id lies outside the slice adds
+    nothing to its token (the reference zero-fills its intermediates for that, fused_moe.py:329-332;
+    here the combine skips the slot, so no buffer needs clearing).
     """
     dev = _lib.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids)
     assert hidden_states.dim() == 2 and w1.dim() == 3 and w2.dim() == 3
@@ -133,7 +115,6 @@ def fused_moe(hidden_states: torch.Tensor,
     assert topk_ids.shape == (M, topk) and topk_weights.shape == (M, topk)
     if num_experts is None:
         num_experts = E
-    full_exp = expert_offset == 0 and num_experts == E
 
     if renormalize:
         topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
@@ -153,21 +134,17 @@ def fused_moe(hidden_states: torch.Tensor,
 
     a_sorted = _permute_rows(hidden_states, sorted_ids, num_post, numel, topk, cap)
     act = torch.empty((cap, inter), dtype=hidden_states.dtype, device=dev)
-    ev = _EventPair(_events, "grouped_gemm_gate_up_silu")
     _grouped_gemm(a_sorted, w1, act, inter, sorted_ids, block_start, None, numel, _lib.GEMM_FUSE_SILU)
-    ev.stop()
-    if full_exp:
-        partial = torch.empty((numel, H_out), dtype=hidden_states.dtype, device=dev)
-    else:
-        partial = torch.zeros((numel, H_out), dtype=hidden_states.dtype, device=dev)
-    ev = _EventPair(_events, "grouped_gemm_down_scatter")
+    partial = torch.empty((numel, H_out), dtype=hidden_states.dtype, device=dev)
     _grouped_gemm(act, w2, partial, H_out, sorted_ids, block_start, topk_weights, numel,
                   _lib.GEMM_WEIGHT | _lib.GEMM_SCATTER)
-    ev.stop()
+    ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) else topk_ids.to(torch.int64)
+    ids = ids.contiguous()
     lib = _lib.load()
     with torch.cuda.device(dev):
         rc = lib.dlb_moe_combine(partial.data_ptr(), out.data_ptr(), M, topk, H_out, out.stride(0),
-                                 _lib.dtype_code(out), _lib.stream_ptr(dev))
+                                 _lib.dtype_code(out), ids.data_ptr(), int(ids.dtype == torch.int64),
+                                 expert_offset, expert_offset + E, _lib.stream_ptr(dev))
     _lib.check(rc, "moe_combine")
     return out
 
@@ -175,14 +152,27 @@ def fused_moe(hidden_states: torch.Tensor,
 def get_start_end(topk_idx: torch.Tensor, sorted_idx: torch.Tensor, num_experts: int):
     """Per-expert [start, end) ranges inside `sorted_idx` (fused_moe.py:267-293).
 
-    Index bookkeeping only (a histogram and a prefix sum over `num_experts` entries).
+    One kernel launch, no host synchronisation.  `sorted_idx` (the argsort of the flattened ids) only
+    gives the dtype of the result, as in the reference (`sorted_idx.new_empty`): the ranges follow from
+    the ids alone, start = number of smaller ids (negative ones included), and an expert without slots
+    gets start = end = 0 as the reference's kernel leaves it.
     """
+    _lib.require_cuda(topk_idx, sorted_idx)
     flat = topk_idx.flatten()
-    valid = (flat >= 0) & (flat < num_experts)
-    cnt = torch.bincount(flat[valid].to(torch.int64), minlength=num_experts)
-    exp_end = cnt.cumsum(0).to(sorted_idx.dtype)
-    exp_start = exp_end - cnt.to(sorted_idx.dtype)
-    return exp_start, exp_end
+    if flat.dtype not in (torch.int32, torch.int64):
+        flat = flat.to(torch.int64)
+    flat = flat.contiguous()
+    out_dtype = torch.int64 if sorted_idx.dtype == torch.int64 else torch.int32
+    start_end = torch.empty((2, num_experts), dtype=out_dtype, device=flat.device)
+    lib = _lib.load()
+    with torch.cuda.device(flat.device):
+        rc = lib.dlb_moe_start_end(flat.data_ptr(), int(flat.dtype == torch.int64), flat.numel(), num_experts,
+                                   start_end[0].data_ptr(), start_end[1].data_ptr(), int(out_dtype == torch.int64),
+                                   _lib.stream_ptr(flat.device))
+    _lib.check(rc, "get_start_end")
+    if out_dtype != sorted_idx.dtype:
+        start_end = start_end.to(sorted_idx.dtype)
+    return start_end[0], start_end[1]
 
 
 def fused_moe_kernel_launcher(

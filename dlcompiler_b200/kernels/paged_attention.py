@@ -53,7 +53,8 @@ def paged_attention_fwd(
     if logit_softcapping is None:
         logit_softcapping = -1.0
     Lq, Lk, Lv = q.shape[-1], k.shape[-1], v.shape[-1]
-    assert Lq == Lk, Lv == o.shape[-1]
+    assert Lq == Lk, f"q and k head sizes differ: {Lq} vs {Lk}"
+    assert Lv == o.shape[-1], f"v head size {Lv} does not match the output's {o.shape[-1]}"
     if sm_scale is None:
         sm_scale = 1.0 / (Lq**0.5)
     batch, head = q_seqlens.shape[0], q.shape[-2]

@@ -42,13 +42,14 @@ def paged_decode_no_alloc(q: Tensor, k: Tensor, v: Tensor, o: Tensor, block_offs
         chunk *= 2
         max_splits = (max_ctx + chunk - 1) // chunk
     lib = _lib.load()
-    status = _lib.status_word(dev)
+    # the status word is a torch tensor: use it only if an earlier call already made it (NULL is allowed)
+    status = _lib.existing_status_word(dev)
     with torch.cuda.device(dev):
         rc = lib.dlb_paged_decode_static(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), block_offsets.data_ptr(), kv_seqlens.data_ptr(),
             batch, head, hkv, D, page, k.size(0), max_pages, q.stride(0), q.stride(1), o.stride(0), o.stride(1),
             k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2), block_offsets.stride(0),
             int(block_offsets.dtype == torch.int64), int(kv_seqlens.dtype == torch.int64), chunk, max_splits, window,
-            float(sm_scale), float(softcap), _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
+            float(sm_scale), float(softcap), _lib.dtype_code(q), _lib.ptr(status), _lib.stream_ptr(dev))
     _lib.check(rc, "paged_decode_no_alloc")
     return o

@@ -38,6 +38,10 @@ extern "C" {
 int dlb_version(void);
 /* Text of the last error raised on the calling thread. */
 const char* dlb_last_error(void);
+/* Wall-clock limit, in milliseconds (1..60000, default 2000), of every wait on a flag that ANOTHER GPU
+ * raises (expert-parallel kernels).  A wait that runs out writes `status` and the kernel goes on; it
+ * never hangs.  Process-wide; applies to launches made after the call. */
+int dlb_set_wait_budget_ms(int64_t ms);
 
 /* silu_and_mul: out[t, i] = silu(x[t, i]) * x[t, n + i], fp32 math, one rounding.
  * Replaces python/dlBLAS/dlblas/kernels/activation.py:88-130 (wrapper) and :17-85 (kernels). */
@@ -102,6 +106,13 @@ int dlb_moe_align_block_size(const void* topk_ids, int ids_are_int64, int64_t nu
                              int64_t expert_ids_capacity, int32_t* num_tokens_post_padded, int32_t* block_start,
                              void* stream);
 
+/* Per-expert [start, end) ranges inside the ascending sort of the flattened ids: start = number of ids
+ * below the expert's (negative ids included), end = start + count, both 0 for an expert without slots.
+ * Outputs int32 or int64 [num_experts].  Replaces get_start_end / _start_end_kernel,
+ * python/dlBLAS/dlblas/kernels/fused_moe.py:267-293, :238-264. */
+int dlb_moe_start_end(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts, void* exp_start,
+                      void* exp_end, int out_is_int64, void* stream);
+
 /* dst[p, :] = src[sorted_token_ids[p] / top_k, :] for p < num_tokens_post_padded (zeros for sentinel
  * rows).  The gather the reference does inside its GEMM by pointer arithmetic (reindex_a,
  * python/dlBLAS/dlblas/kernels/fused_moe.py:136-140), as a separate pass so the GEMM can use TMA. */
@@ -153,7 +164,9 @@ int dlb_moe_grouped_gemm_sync(const void* a, int64_t a_rows, int64_t a_row_strid
  *   dlb_ep_send     stores every slot's hidden row, routing weight and (rank << 24 | slot) into the owner
  *                   rank's rows_sym [cap][hidden], w_sym [cap], meta_sym [cap]; the last CTA raises flag
  *                   slot 1 on every rank (done_counter: device int32, zero).
- *   dlb_ep_combine  dlb_moe_combine that first waits until wait_flags[r] >= epoch for every rank r.
+ *   dlb_ep_combine  dlb_moe_combine that first waits until wait_flags[r] >= epoch for every rank r; with
+ *                   dest_pos (may be NULL) slots whose dest_pos is negative add nothing (they were sent
+ *                   to no rank, so their row of `partial` is stale).
  *   dlb_ep_combine_pull  the same wait, then out[t] = sum over k of row dest_pos[t * top_k + k] of the
  *                   down-projection output y_sym [cap][hidden] of the rank that owns expert
  *                   topk_ids[t * top_k + k], read over NVLink with coalesced peer loads (slots whose
@@ -171,7 +184,7 @@ int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_t hidden_co
                 int epoch, void* stream);
 int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
                    int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
-                   int32_t* status, void* stream);
+                   const int32_t* dest_pos, int32_t* status, void* stream);
 int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, const void* topk_ids, int ids_are_int64,
                         const int32_t* dest_pos, void* out, int64_t tokens, int top_k, int64_t hidden,
                         int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int experts,
@@ -179,9 +192,12 @@ int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, const void* to
 int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status, void* stream);
 
 /* out[t, :] = sum over k of partial[t * top_k + k, :] (fp32 accumulate, one rounding): the
- * `intermediate_cache2.sum(dim=1)` of python/dlBLAS/dlblas/kernels/fused_moe.py:375. */
+ * `intermediate_cache2.sum(dim=1)` of python/dlBLAS/dlblas/kernels/fused_moe.py:375.  With topk_ids
+ * (may be NULL: every slot counts) a slot whose id is outside [id_lo, id_hi) adds nothing; its row of
+ * `partial` was written by no kernel (the reference zero-fills the buffer instead, :329-332, 355-358). */
 int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
-                    int64_t out_row_stride, int dtype, void* stream);
+                    int64_t out_row_stride, int dtype, const void* topk_ids, int ids_are_int64, int64_t id_lo,
+                    int64_t id_hi, void* stream);
 
 /* Varlen causal GQA flash-attention prefill.  q [total, hq, d], k/v [total, hkv, d], out like q,
  * lse (optional, may be NULL) fp32 [hq, total] = m * sm_scale + log(sum) in natural log.

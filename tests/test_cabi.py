@@ -26,6 +26,34 @@ def test_library_exports_every_declared_symbol():
     assert lib.dlb_version() >= 100
 
 
+def test_ctypes_prototypes_match_the_header_argument_by_argument():
+    """Every prototype in include/dlblas_b200.h against the ctypes table: same number of arguments and, per
+    argument, the same kind (pointer, int, int64_t, float).  The .cu files include the same header, so a
+    definition that drifts from it does not compile; this closes the third side of the triangle."""
+    from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+
+    text = open(os.path.join(ROOT, "include", "dlblas_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = re.findall(r"^([\w \*]+?)\b(dlb_\w+)\s*\(([^)]*)\)\s*;", text, flags=re.M)
+    assert len(protos) == len(_lib.SIGNATURES)
+
+    def kind(decl):
+        decl = decl.strip()
+        if "*" in decl:
+            return "ptr"
+        base = decl.split()[:-1] if len(decl.split()) > 1 else [decl]
+        base = " ".join(t for t in base if t != "const")
+        return {"int": "int", "int64_t": "i64", "float": "f32"}[base]
+
+    ctype_kind = {c_void_p: "ptr", c_char_p: "ptr", c_int: "int", c_int64: "i64", c_float: "f32"}
+    for ret, name, args in protos:
+        res, argtypes = _lib.SIGNATURES[name]
+        want = [] if args.strip() in ("", "void") else [kind(a) for a in args.split(",")]
+        got = [ctype_kind[t] for t in argtypes]
+        assert got == want, f"{name}: ctypes {got} != header {want}"
+        assert ctype_kind[res] == kind(ret + " x"), f"{name}: return type"
+
+
 def test_argument_errors_are_reported_without_a_device():
     lib = _lib.load()
     rc = lib.dlb_silu_and_mul(None, None, -1, 8, 16, 8, _lib.DTYPE_BF16, None)
@@ -41,6 +69,9 @@ def test_argument_errors_are_reported_without_a_device():
                                   None, None)
     assert rc < 0 and b"128-row" in lib.dlb_last_error()
     assert lib.dlb_paged_decode_workspace_floats(64, 32, 128, 8) == 64 * 32 * 8 * 130
+    assert lib.dlb_set_wait_budget_ms(0) < 0 and lib.dlb_set_wait_budget_ms(2000) == 0
+    rc = lib.dlb_moe_start_end(None, 1, 16, 4000, None, None, 1, None)
+    assert rc < 0 and b"experts" in lib.dlb_last_error()
 
 
 def test_wrappers_refuse_cpu_tensors():

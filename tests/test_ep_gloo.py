@@ -33,7 +33,7 @@ class TorchOps:
         return src[(row_map[:rows].long() // div)]
 
     @staticmethod
-    def expert_mlp(rows, weights, expert_of_row, w1, w2, events=None):
+    def expert_mlp(rows, weights, expert_of_row, w1, w2):
         out = torch.zeros(rows.size(0), w2.size(1), dtype=rows.dtype)
         for e in range(w1.size(0)):
             idx = torch.nonzero(expert_of_row == e).flatten()
@@ -47,7 +47,7 @@ class TorchOps:
         return out
 
     @staticmethod
-    def combine(partial, tokens, top_k):
+    def combine(partial, tokens, top_k, topk_ids, num_experts):
         return partial.view(tokens, top_k, -1).float().sum(1).to(partial.dtype)
 
 

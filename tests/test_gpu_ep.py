@@ -1,4 +1,5 @@
-"""Expert-parallel fused_moe on GPUs through NCCL, against the single-GPU fused_moe (bit-exact)."""
+"""Expert-parallel fused_moe on 1, 2, 4 and 8 GPUs against the single-GPU fused_moe (bit-exact), the
+failure path of a cross-GPU wait (one GPU, a peer that never signals), and ids outside the expert range."""
 import os
 import socket
 
@@ -52,6 +53,19 @@ def _worker(rank, world, port, ret):
                 torch.cuda.synchronize()
                 dl.check_device_status()
                 ok = ok and bool(torch.equal(out2, full[sl]))
+            # ids outside [0, E) (padding) are sent nowhere and add nothing, step after step (the buffers keep
+            # the rows of the steps before)
+            ti_pad = ti.clone()
+            ti_pad[1::5, 1] = -1
+            ti_pad[2::9, 0] = wl.experts + 3
+            full_pad = dl.fused_moe(hs, w1, w2, tw, ti_pad, wl.top_k)
+            for _ in range(2):
+                out3 = ep_moe.ep_fused_moe_peer(pctx, hs[sl], w1[rank * el:(rank + 1) * el].contiguous(),
+                                                w2[rank * el:(rank + 1) * el].contiguous(), tw[sl], ti_pad[sl],
+                                                wl.top_k)
+                torch.cuda.synchronize()
+                dl.check_device_status()
+                ok = ok and bool(torch.equal(out3, full_pad[sl]))
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
@@ -68,7 +82,43 @@ def test_ep_single_rank_group(cuda_device):
     _run(1)
 
 
-def test_ep_two_ranks(cuda_device):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    _run(2)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_many_ranks(cuda_device, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world)
+
+
+def test_cross_gpu_wait_gives_up_and_reports(cuda_device):
+    """A rank whose peer never raises its flag: the barrier kernel runs out of its wait budget, returns,
+    and the status word says where.  One GPU stands in for two ranks (both table entries point at the
+    same zeroed flag buffer, so the flag of "rank 1" is never written); nothing faults and nothing hangs."""
+    import ctypes
+
+    import dlcompiler_b200 as dl
+    from dlcompiler_b200 import _lib
+
+    lib = _lib.load()
+    dev = cuda_device
+    flags = torch.zeros(8 * 16, dtype=torch.int32, device=dev)
+    table = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr())
+    status = _lib.status_word(dev)
+    dl.check_device_status()
+    _lib.set_wait_budget_ms(50)
+    try:
+        slot = 3
+        with torch.cuda.device(dev):
+            rc = lib.dlb_ep_barrier(table, slot, 0, 2, 1, status.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc, "ep_barrier")
+        torch.cuda.synchronize()
+        vals = status.cpu().tolist()
+        assert vals[0] == 1 and vals[1] == 42 + slot and vals[2] == 0 and vals[3] == 1
+        assert flags[slot * 16 + 0].item() == 1 and flags[slot * 16 + 1].item() == 0
+        with pytest.raises(dl.DlblasError):
+            dl.check_device_status()
+        dl.check_device_status()                     # raised once, then clean
+        # the context is still usable
+        assert torch.equal(dl.silu_and_mul(torch.ones(4, 16, dtype=torch.bfloat16, device=dev)).cpu(),
+                           torch.full((4, 8), 0.73046875, dtype=torch.bfloat16))
+    finally:
+        _lib.set_wait_budget_ms(2000)

@@ -117,8 +117,8 @@ def test_fused_moe_expert_slices_sum_to_full(cuda_device):
     torch.testing.assert_close(acc, full, rtol=RTOL, atol=ATOL)
 
 
-def test_fused_moe_config_sample_and_linearity(cuda_device):
-    """Full benchmark shape: a token sample against the oracle, plus size-independent properties."""
+def test_fused_moe_config_all_tokens_and_linearity(cuda_device):
+    """Full benchmark shape: every token against the oracle, plus size-independent properties."""
     wl = W.MoeWorkload()
     d = wl.make()
     tw, ti = oracle.softmax_topk(d["router_logits"], wl.top_k)
@@ -126,10 +126,10 @@ def test_fused_moe_config_sample_and_linearity(cuda_device):
     out = fused_moe(hs, w1, w2, tw_d, ti_d, wl.top_k)
     again = fused_moe(hs, w1, w2, tw_d, ti_d, wl.top_k)
     assert torch.equal(out, again)                                   # deterministic
+    torch.set_num_threads(os.cpu_count() or 1)
+    ref = oracle.fused_moe_rounding_faithful(d["hidden_states"], d["w1"], d["w2"], tw, ti.long())
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
     sample = torch.arange(0, wl.tokens, 173)[:24]
-    ref = oracle.fused_moe_rounding_faithful(d["hidden_states"][sample], d["w1"], d["w2"], tw[sample],
-                                             ti[sample].long())
-    torch.testing.assert_close(out[sample].cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
     # scaling the routing weights by 2 scales the output by 2 (exact in binary floating point)
     twice = fused_moe(hs, w1, w2, tw_d * 2, ti_d, wl.top_k)
     assert torch.equal(twice, out * 2)
@@ -137,3 +137,55 @@ def test_fused_moe_config_sample_and_linearity(cuda_device):
     sub = fused_moe(hs[sample.to(cuda_device)], w1, w2, tw_d[sample.to(cuda_device)], ti_d[sample.to(cuda_device)],
                     wl.top_k)
     assert torch.equal(sub, out[sample.to(cuda_device)])
+
+
+def test_fused_moe_ids_outside_the_expert_range_add_nothing(cuda_device):
+    """Padding ids (-1) and ids of experts this call does not hold contribute zero, with the default
+    arguments as well as with an explicit num_experts (the reference zero-fills its intermediate buffers
+    for this, fused_moe.py:308-312, 329-332); no stale memory may leak into the sum."""
+    g = torch.Generator().manual_seed(21)
+    T, H, I, E, k = 200, 256, 256, 4, 2
+    hs = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16)
+    tw, ti = oracle.softmax_topk(torch.randn(T, E, generator=g), k)
+    ti = ti.long().clone()
+    ti[::3, 1] = -1
+    ti[1::7, 0] = E + 2
+    keep = ((ti >= 0) & (ti < E))
+    ref = oracle.fused_moe_rounding_faithful(hs, w1, w2, tw * keep, ti.clamp(0, E - 1))
+    hs_d, w1_d, w2_d, tw_d, ti_d = _to(cuda_device, hs, w1, w2, tw, ti)
+    # poison the allocator's free blocks so that an unwritten row would show
+    junk = torch.full((T * k, H), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    del junk
+    for kwargs in ({}, {"num_experts": E}):
+        out = fused_moe(hs_d, w1_d, w2_d, tw_d, ti_d, k, **kwargs)
+        assert torch.isfinite(out.float()).all()
+        torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_get_start_end_matches_the_reference_kernel_semantics(cuda_device):
+    """[start, end) per expert inside the argsort of the ids (fused_moe.py:238-293): negative ids sort first and
+    shift every start, ids >= num_experts sort last, an absent expert gets (0, 0); dtype follows sorted_idx."""
+    from dlcompiler_b200 import get_start_end
+
+    g = torch.Generator().manual_seed(5)
+    E = 8
+    ids = torch.randint(0, E, (300, 2), generator=g)
+    ids[ids == 5] = 6                       # expert 5 has no slot
+    ids[::11, 0] = -1
+    ids[3::13, 1] = E + 1
+    flat = ids.flatten()
+    order = flat.argsort()
+    sv = flat[order]
+    exp_s, exp_e = [], []
+    for e in range(E):
+        pos = torch.nonzero(sv == e).flatten()
+        exp_s.append(int(pos[0]) if pos.numel() else 0)
+        exp_e.append(int(pos[0]) + pos.numel() if pos.numel() else 0)
+    for dt in (torch.int64, torch.int32):
+        s, e = get_start_end(ids.to(cuda_device), order.to(dt).to(cuda_device), E)
+        assert s.dtype == dt and e.dtype == dt
+        assert s.cpu().tolist() == exp_s and e.cpu().tolist() == exp_e
+    s0, e0 = oracle.start_end_from_counts(torch.randint(0, E, (64, 2), generator=g), E)
+    assert (e0 - s0).sum() == 128

@@ -49,6 +49,40 @@ def test_static_scratch_decode_matches_regular_entry_point_twice(cuda_device):
         assert torch.cuda.memory_allocated(cuda_device) <= before + out.numel() * out.element_size()
 
 
+def test_static_scratch_decode_as_the_first_call_of_a_process(cuda_device):
+    """In a fresh process, with no other library call before it, the entry point must still allocate
+    nothing (not even the status word the other wrappers create on first use)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = """
+import torch
+from dlcompiler_b200 import workloads as W
+from dlcompiler_b200.kernels.paged_attention_static import paged_decode_no_alloc
+dev = torch.device("cuda:0")
+d = W.DecodeWorkload(batch=3, ctx_lo=200, ctx_hi=5000, page=64, seed=42).make()
+d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in d.items()}
+out = torch.full_like(d["q"], float("nan"))
+torch.cuda.synchronize()
+before = torch.cuda.memory_allocated(dev)
+paged_decode_no_alloc(d["q"], d["k_cache"], d["v_cache"], out, d["block_table"], d["kv_seqlens"])
+torch.cuda.synchronize()
+assert torch.cuda.memory_allocated(dev) == before, "the call allocated device memory"
+assert torch.isfinite(out.float()).all()
+from dlcompiler_b200 import paged_attention_fwd
+exp = torch.full_like(out, float("nan"))
+B = out.shape[0]
+paged_attention_fwd(d["q"], d["k_cache"], d["v_cache"], exp, d["block_table"], torch.arange(B, device=dev),
+                    torch.ones(B, dtype=torch.int64, device=dev), d["kv_seqlens"], 1)
+assert torch.equal(out, exp)
+print("first-call ok")
+"""
+    res = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "first-call ok" in res.stdout, res.stdout + res.stderr
+
+
 def test_static_scratch_rejects_oversized_requests(cuda_device):
     lib = _lib.load()
     too_many_splits = 4096
