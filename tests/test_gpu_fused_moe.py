@@ -80,6 +80,29 @@ def test_fused_moe_shapes(cuda_device, T, H, I, E, k, dtype):
     torch.testing.assert_close(out.float(), ref.float(), rtol=4 * eps, atol=4 * eps * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("T,H,I,E,k,dtype,skew", [
+    (1200, 256, 384, 2, 2, torch.bfloat16, 0.0),     # both experts get 1200 rows: 9 + 1 blocks -> 4-5 pairs + a tail
+    (1500, 512, 256, 3, 1, torch.bfloat16, 2.0),     # skewed: one long expert, one short, odd and even counts
+    (2048, 200, 72, 4, 2, torch.float16, 1.0),       # K, N multiples of 8 only, on the pair path
+    (1024, 128, 128, 2, 1, torch.bfloat16, 50.0),    # everything on expert 0, expert 1 empty
+])
+def test_fused_moe_many_blocks_per_expert(cuda_device, T, H, I, E, k, dtype, skew):
+    """Few experts with many 128-row blocks each: odd and even block counts, a long and a short expert, an
+    empty expert; bit-reproducible from call to call."""
+    g = torch.Generator().manual_seed(T + 13 * E)
+    hs = (torch.randn(T, H, generator=g)).to(dtype)
+    w1 = (torch.randn(E, 2 * I, H, generator=g) * (H ** -0.5)).to(dtype)
+    w2 = (torch.randn(E, H, I, generator=g) * (I ** -0.5)).to(dtype)
+    logits = torch.randn(T, E, generator=g) - skew * torch.arange(E)
+    tw, ti = oracle.softmax_topk(logits, k)
+    args = _to(cuda_device, hs, w1, w2, tw, ti)
+    out = fused_moe(*args, topk=k)
+    assert torch.equal(out, fused_moe(*args, topk=k))
+    ref = oracle.fused_moe_rounding_faithful(hs, w1, w2, tw, ti.long())
+    eps = torch.finfo(dtype).eps
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=4 * eps, atol=4 * eps * ref.abs().max().item())
+
+
 def test_fused_moe_empty_and_unused_experts(cuda_device):
     dev = cuda_device
     hs = torch.randn(0, 128, dtype=torch.bfloat16, device=dev)
