@@ -28,6 +28,7 @@ constexpr int MAX_RANKS = 16;
 constexpr int MAX_EXPERTS = 1024;
 constexpr int PLAN_THREADS = 1024;
 constexpr int FLAG_STRIDE = 16;   // flags of one barrier slot: FLAG_STRIDE ints, one per source rank
+constexpr int SEND_THREADS = 512;
 }  // namespace ep
 
 struct PeerPtrs {
@@ -216,23 +217,43 @@ struct EpSendParams {
   int numel, top_k, row_vecs, experts, world, rank, cap, ids_are_int64, epoch;
 };
 
-__global__ void __launch_bounds__(256) ep_send_kernel(const EpSendParams p) {
+// A few fat CTAs (two per SM) walk the slots, four rows in flight per pass, and each CTA issues ONE
+// system-scope fence at its very end: the fence has to wait for every peer store the CTA still has on the
+// links, so one CTA per slot (a fence per 8 KB row) cost 42 us for 1024 rows where the bytes need 10.
+__global__ void __launch_bounds__(ep::SEND_THREADS) ep_send_kernel(const EpSendParams p) {
   const int epr = p.experts / p.world;
-  for (int slot = blockIdx.x; slot < p.numel; slot += gridDim.x) {
-    const int pos = p.dest_pos[slot];
-    if (pos < 0 || pos >= p.cap) continue;
-    const int r = load_id(p.topk_ids, slot, p.ids_are_int64) / epr;
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.hidden) +
-                                                      (int64_t)(slot / p.top_k) * p.hidden_row_stride * 2);
-    uint4* dst = reinterpret_cast<uint4*>(p.rows.p[r]) + (int64_t)pos * p.row_vecs;
-    for (int v = threadIdx.x; v < p.row_vecs; v += blockDim.x) dst[v] = __ldg(src + v);
-    if (threadIdx.x == 0) {
-      reinterpret_cast<float*>(p.w.p[r])[pos] = p.topk_weights[slot];
-      reinterpret_cast<int32_t*>(p.meta.p[r])[pos] = (p.rank << 24) | slot;
+  constexpr int ROWS = 4;
+  for (int first = blockIdx.x * ROWS; first < p.numel; first += gridDim.x * ROWS) {
+    const uint4* src[ROWS];
+    uint4* dst[ROWS];
+#pragma unroll
+    for (int j = 0; j < ROWS; ++j) {
+      const int slot = first + j;
+      src[j] = nullptr;
+      dst[j] = nullptr;
+      if (slot >= p.numel) continue;
+      const int pos = p.dest_pos[slot];
+      if (pos < 0 || pos >= p.cap) continue;
+      const int r = load_id(p.topk_ids, slot, p.ids_are_int64) / epr;
+      src[j] = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.hidden) +
+                                              (int64_t)(slot / p.top_k) * p.hidden_row_stride * 2);
+      dst[j] = reinterpret_cast<uint4*>(p.rows.p[r]) + (int64_t)pos * p.row_vecs;
+      if (threadIdx.x == j) {
+        reinterpret_cast<float*>(p.w.p[r])[pos] = p.topk_weights[slot];
+        reinterpret_cast<int32_t*>(p.meta.p[r])[pos] = (p.rank << 24) | slot;
+      }
+    }
+    for (int v = threadIdx.x; v < p.row_vecs; v += blockDim.x) {
+      uint4 x[ROWS];
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j)
+        if (src[j] != nullptr) x[j] = __ldg(src[j] + v);
+#pragma unroll
+      for (int j = 0; j < ROWS; ++j)
+        if (src[j] != nullptr) dst[j][v] = x[j];
     }
   }
   // one system-scope fence per CTA, after the barrier that orders every thread's peer stores before it
-  // (a fence in every thread made each of the CTA's warps wait for the links on its own)
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -485,10 +506,10 @@ extern "C" int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_
   p.cap = (int)cap;
   p.ids_are_int64 = ids_are_int64;
   p.epoch = epoch;
-  int64_t blocks = numel < 1 ? 1 : numel;
-  const int64_t limit = (int64_t)sm_count(current_device()) * 8;
+  int64_t blocks = numel < 1 ? 1 : (numel + 3) / 4;
+  const int64_t limit = (int64_t)sm_count(current_device()) * 2;
   if (blocks > limit) blocks = limit;
-  ep_send_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  ep_send_kernel<<<(unsigned)blocks, ep::SEND_THREADS, 0, (cudaStream_t)stream>>>(p);
   DLB_CUDA_LAUNCH_CHECK();
   return DLB_OK;
 }
