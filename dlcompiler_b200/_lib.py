@@ -59,14 +59,14 @@ SIGNATURES = {
     "dlb_moe_combine": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_int,
                                 c_int64, c_int64, c_void_p]),
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_float, c_int, c_int, c_void_p, c_void_p]),
-    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 20 + [c_int, c_int64, c_float, c_float, c_int, c_int,
+    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 21 + [c_int, c_int64, c_float, c_float, c_int, c_int,
                                                                       c_void_p, c_void_p]),
     "dlb_paged_decode_workspace_floats": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "dlb_paged_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                 c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_int,

@@ -27,6 +27,13 @@
 //              2^8 (lazy rescaling), and finally normalises and stores O
 // CTAs are ordered (sequence, kv head) group by group, heavy causal tiles first inside a group, so the
 // resident CTAs share K/V through L2 and the tail of each group is short.
+//
+// Built for tile widths D = 64 and 128.  Head sizes that are other multiples of 8 (and a v head size that
+// differs from the q/k one, as the reference's paged kernel allows, paged_attention.py:526-539) run on the
+// next width: the tensor maps carry the true sizes, so the copy engine zero-fills the missing columns of
+// every Q, K and V tile in shared memory and nothing is copied or padded in global memory.
+// V rows of the last key block that lie past the end of the keys are zeroed in shared memory before the
+// P.V MMA reads them: their probabilities are exactly zero, but 0 x (stale NaN bits of a cache page) is NaN.
 #include <math_constants.h>
 
 #include <algorithm>
@@ -145,6 +152,7 @@ struct PrefillParams {
   int table_is_int64;
   const int32_t* kv_seq_len;      // [batch]
   // Extras of the paged prefill branch (kernel instantiated with EXTRAS only when one is on):
+  int dv;                         // v / out head size (<= D, multiple of 8): output columns past it are not stored
   int window;                     // > 0: query at position pos sees keys pos - window .. pos (paged_attention.py:421-424,447)
   float softcap;                  // > 0: scores become softcap * tanh(score * sm_scale / softcap) (paged_attention.py:441-444)
   float sm_scale;
@@ -487,6 +495,20 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         unpack_f2(add_f2(sum2a, sum2b), a, b);
         l_sum = l_sum * alpha + (a + b);
       }
+      if (key0 + BN > kv_len) {
+        // rows of this V tile past the last key: zero them (generic-proxy stores), then make the stores
+        // visible to the tensor core's shared-memory reads before this block's P.V can be issued
+        ok = mbar_wait(&v_full[s], ph, abort_flag, p.status, 31, j);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int first_dead = max(kv_len - key0, 0);
+        uint8_t* vt = smem + OFF_V + s * KV_BYTES;
+        for (int i = threadIdx.x; i < (BN - first_dead) * BOXES * 8; i += 128) {
+          const int chunk = i & 7, bx = (i >> 3) % BOXES, r = first_dead + (i >> 3) / BOXES;
+          *reinterpret_cast<uint4*>(vt + bx * KV_BOX + r * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[s]);
@@ -517,7 +539,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
                                                          __uint_as_float(o[v * 8 + 2 * i + 1]) * inv_l);
               w[i] = *reinterpret_cast<uint32_t*>(&v2);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (c * 32 + v * 8 < p.dv)
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -560,7 +583,7 @@ static int launch_prefill(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
                                         const int32_t* b_start_loc, const int32_t* b_seq_len, int64_t batch,
                                         int64_t total_tokens, int64_t max_seq_len, int64_t hq, int64_t hkv,
-                                        int64_t head_dim, int64_t q_stride_t, int64_t q_stride_h,
+                                        int64_t head_dim, int64_t head_dim_v, int64_t q_stride_t, int64_t q_stride_h,
                                         int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
                                         int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h, float sm_scale,
                                         int causal, int dtype, int32_t* status, void* stream) {
@@ -568,9 +591,11 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "flash_prefill: dtype %d (need fp16 or bf16)", dtype);
-  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
-                "flash_prefill: head_dim %lld not supported (64 or 128)", (long long)head_dim);
-  const int D = (int)head_dim;
+  DLB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0 && head_dim_v >= 8 && head_dim_v <= 128 &&
+                    head_dim_v % 8 == 0,
+                DLB_ERR_UNSUPPORTED, "flash_prefill: head_dim %lld / %lld not supported (multiples of 8 up to 128)",
+                (long long)head_dim, (long long)head_dim_v);
+  const int D = (head_dim <= 64 && head_dim_v <= 64) ? 64 : 128;   // tile width; the tensor maps keep the true sizes
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "flash_prefill: bad head counts");
   DLB_CHECK_ARG(total_tokens >= 0 && max_seq_len >= 0, DLB_ERR_BAD_ARG, "flash_prefill: negative size");
   if (batch == 0 || total_tokens == 0 || max_seq_len == 0) return DLB_OK;
@@ -583,11 +608,11 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
 
   const int kv_box = BN;
   CUtensorMap tq, tk, tv;
-  int rc = make_tmap_tokens(&tq, q, D, hq, total_tokens, q_stride_h, q_stride_t, BM);
+  int rc = make_tmap_tokens(&tq, q, head_dim, hq, total_tokens, q_stride_h, q_stride_t, BM);
   if (rc != DLB_OK) return rc;
-  rc = make_tmap_tokens(&tk, k, D, hkv, total_tokens, k_stride_h, k_stride_t, kv_box);
+  rc = make_tmap_tokens(&tk, k, head_dim, hkv, total_tokens, k_stride_h, k_stride_t, kv_box);
   if (rc != DLB_OK) return rc;
-  rc = make_tmap_tokens(&tv, v, D, hkv, total_tokens, v_stride_h, v_stride_t, kv_box);
+  rc = make_tmap_tokens(&tv, v, head_dim_v, hkv, total_tokens, v_stride_h, v_stride_t, kv_box);
   if (rc != DLB_OK) return rc;
 
   const uint32_t fmt = dtype == DLB_DTYPE_BF16 ? 1u : 0u;
@@ -621,6 +646,7 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   p.bt_stride = 0;
   p.table_is_int64 = 0;
   p.kv_seq_len = nullptr;
+  p.dv = (int)head_dim_v;
   p.window = 0;
   p.softcap = 0.f;
   p.sm_scale = sm_scale;
@@ -643,7 +669,8 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
                                        const void* block_table, const int32_t* q_start_loc,
                                        const int32_t* q_seq_len, const int32_t* kv_seq_len, int64_t batch,
                                        int64_t total_q_tokens, int64_t max_q_len, int64_t hq, int64_t hkv,
-                                       int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages,
+                                       int64_t head_dim, int64_t head_dim_v, int64_t page_size, int64_t num_pages,
+                                       int64_t max_pages,
                                        int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_page,
                                        int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
                                        int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
@@ -654,9 +681,12 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "flash_prefill_paged: dtype %d (need fp16 or bf16)", dtype);
-  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
-                "flash_prefill_paged: head_dim %lld not supported (64 or 128)", (long long)head_dim);
-  const int D = (int)head_dim;
+  DLB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0 && head_dim_v >= 8 && head_dim_v <= 128 &&
+                    head_dim_v % 8 == 0,
+                DLB_ERR_UNSUPPORTED,
+                "flash_prefill_paged: head_dim %lld / %lld not supported (multiples of 8 up to 128)",
+                (long long)head_dim, (long long)head_dim_v);
+  const int D = (head_dim <= 64 && head_dim_v <= 64) ? 64 : 128;   // tile width; the tensor maps keep the true sizes
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG,
                 "flash_prefill_paged: bad head counts");
   DLB_CHECK_ARG(total_q_tokens >= 0 && max_q_len >= 0, DLB_ERR_BAD_ARG, "flash_prefill_paged: negative size");
@@ -674,14 +704,14 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
                 "flash_prefill_paged: grid too large");
 
   CUtensorMap tq, tk, tv;
-  int rc = make_tmap_tokens(&tq, q, D, hq, total_q_tokens, q_stride_h, q_stride_t, BM);
+  int rc = make_tmap_tokens(&tq, q, head_dim, hq, total_q_tokens, q_stride_h, q_stride_t, BM);
   if (rc != DLB_OK) return rc;
   const int box_slots = (int)(page_size < BN ? page_size : BN);
-  rc = make_tmap_cache(&tk, k_cache, D, hkv, page_size, num_pages, k_stride_page, k_stride_slot, k_stride_head,
-                       box_slots);
+  rc = make_tmap_cache(&tk, k_cache, head_dim, hkv, page_size, num_pages, k_stride_page, k_stride_slot,
+                       k_stride_head, box_slots);
   if (rc != DLB_OK) return rc;
-  rc = make_tmap_cache(&tv, v_cache, D, hkv, page_size, num_pages, v_stride_page, v_stride_slot, v_stride_head,
-                       box_slots);
+  rc = make_tmap_cache(&tv, v_cache, head_dim_v, hkv, page_size, num_pages, v_stride_page, v_stride_slot,
+                       v_stride_head, box_slots);
   if (rc != DLB_OK) return rc;
 
   const uint32_t fmt = dtype == DLB_DTYPE_BF16 ? 1u : 0u;
@@ -713,6 +743,7 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
   p.bt_stride = bt_stride;
   p.table_is_int64 = table_is_int64;
   p.kv_seq_len = kv_seq_len;
+  p.dv = (int)head_dim_v;
   p.window = window > 0 ? (int)std::min<int64_t>(window, 1 << 29) : 0;
   p.softcap = softcap;
   p.sm_scale = sm_scale;

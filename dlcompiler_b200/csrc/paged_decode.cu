@@ -17,6 +17,12 @@
 // own 16 of the 64 keys of a tile and run mma.sync m16n8k16 with the
 // sequence's q-heads of one kv-head as the (zero-padded) M=16 rows, fed by
 // swizzle-aware ldmatrix.  Each KV byte is read from HBM exactly once.
+//
+// The kernel is built for tile widths D = 64 and 128.  Any q/k head size and any v head size that are
+// multiples of 8 up to 128 run on the next width (the reference splits the head into a power of two plus a
+// remainder and lets V have its own size, paged_attention.py:526-539): the tensor maps carry the TRUE
+// sizes, so the copy engine fills the missing columns of every tile with zeros in shared memory (no copy of
+// the cache), zero columns add nothing to a score, and output columns past the v head size are not stored.
 #include <math_constants.h>
 
 #include <mutex>
@@ -84,6 +90,7 @@ struct DecodeParams {
   int64_t o_stride_b, o_stride_h;
   int64_t bt_stride;
   int batch, hq, hkv, group;
+  int dk, dv;                // true head sizes of q/k and of v/out (<= D, multiples of 8); columns beyond them are zero
   int page_size, max_pages, num_pages;
   int chunk;                 // tokens per split (multiple of 64 and of the page size when page_size > 64)
   int max_splits;
@@ -103,6 +110,14 @@ struct DecodeParams {
 // this thread's earlier cp.async copies have landed" (the arrival is one of the barrier's expected count).
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+// the same copy, or 16 bytes of zeros when `src_or_base` is not `gmem_src` (a chunk past the head size):
+// the zero fill stays inside the cp.async group, so the stage's barrier covers it like any other chunk
+template <typename P>
+__device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const P* gmem_src, const P* src_or_base) {
+  const int bytes = (src_or_base == gmem_src) ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src_or_base), "r"(bytes)
+               : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -155,7 +170,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       const int rows = min(16, p.group - hblk * 16);
       T* o = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b;
       for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x)
-        o[(int64_t)(kvh * p.group + hblk * 16 + idx / D) * p.o_stride_h + idx % D] = Elem<T>::from_f(0.f);
+        if (idx % D < p.dv)
+          o[(int64_t)(kvh * p.group + hblk * 16 + idx / D) * p.o_stride_h + idx % D] = Elem<T>::from_f(0.f);
     }
     return;   // whole CTA leaves
   }
@@ -206,6 +222,7 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       const int sub = lane / CHUNKS;                // row inside the pass
       const int hbox = c16 >> 3, cc = c16 & 7;      // 64-wide column box and chunk inside its 128-byte row
       const bool one_token_pages = p.page_size == 1;
+      const bool k_chunk_ok = c16 * 8 < p.dk, v_chunk_ok = c16 * 8 < p.dv;   // chunks past the head size: zeros
       const T* k_lane = kc + (int64_t)kvh * p.k_stride_head + c16 * 8;   // this lane's chunk of row (page 0, slot 0)
       const T* v_lane = vc + (int64_t)kvh * p.v_stride_head + c16 * 8;
       for (int t = 0; t < n_tiles; ++t) {
@@ -242,8 +259,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
               ko += (int64_t)slot * p.k_stride_slot;
               vo += (int64_t)slot * p.v_stride_slot;
             }
-            cp_async_16(kdst + off, k_lane + ko);
-            cp_async_16(vdst + off, v_lane + vo);
+            cp_async_16_or_zero(kdst + off, k_lane + ko, k_chunk_ok ? k_lane + ko : (const T*)kc);
+            cp_async_16_or_zero(vdst + off, v_lane + vo, v_chunk_ok ? v_lane + vo : (const T*)vc);
           }
         }
         cp_async_arrive(&full_bar[s]);
@@ -293,7 +310,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
           const int row = r0 + (j & 1) * 8;
           const int col = ks * 16 + cq + (j >> 1) * 8;
           uint32_t v = 0;
-          if (row < rows_valid) v = *reinterpret_cast<const uint32_t*>(qb + (int64_t)(head0 + row) * p.q_stride_h + col);
+          if (row < rows_valid && col < p.dk)
+            v = *reinterpret_cast<const uint32_t*>(qb + (int64_t)(head0 + row) * p.q_stride_h + col);
           qf[ks][j] = v;
         }
       }
@@ -468,7 +486,8 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
     }
     const int head = head0 + row;
     if (p.max_splits == 1) {
-      out[(int64_t)b * p.o_stride_b + (int64_t)head * p.o_stride_h + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
+      if (d < p.dv)
+        out[(int64_t)b * p.o_stride_b + (int64_t)head * p.o_stride_h + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
     } else {
       float* dst = p.partial + (((int64_t)b * p.hq + head) * p.max_splits + split) * (D + 2);
       dst[d] = acc;
@@ -490,7 +509,7 @@ __global__ void __launch_bounds__(D) paged_decode_merge_kernel(const DecodeParam
   T* out = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_stride_b + (int64_t)head * p.o_stride_h;
   int lo, hi, kv_lo;
   if (!split_range(ctx, p.window, p.chunk, 0, lo, hi, kv_lo)) {
-    out[d] = Elem<T>::from_f(0.f);
+    if (d < p.dv) out[d] = Elem<T>::from_f(0.f);
     return;
   }
   const int n_splits = min(p.max_splits, (ctx - lo + p.chunk - 1) / p.chunk);
@@ -504,7 +523,7 @@ __global__ void __launch_bounds__(D) paged_decode_merge_kernel(const DecodeParam
     acc += src[s * (D + 2) + d] * sc;
     l += src[s * (D + 2) + D + 1] * sc;
   }
-  out[d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
+  if (d < p.dv) out[d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
 }
 
 template <typename T, int D>
@@ -535,13 +554,15 @@ static int launch_decode(const CUtensorMap& tk, const CUtensorMap& tv, const Dec
 
 extern "C" int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t head_dim,
                                                      int64_t max_splits) {
-  return max_splits <= 1 ? 0 : batch * hq * max_splits * (head_dim + 2);
+  const int64_t width = head_dim <= 64 ? 64 : 128;   // the tile width the kernel runs at
+  return max_splits <= 1 ? 0 : batch * hq * max_splits * (width + 2);
 }
 
 extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                 const void* block_table, const void* kv_seqlens, float* partial, int64_t batch,
-                                int64_t hq, int64_t hkv, int64_t head_dim, int64_t page_size, int64_t num_pages,
-                                int64_t max_pages, int64_t q_stride_b, int64_t q_stride_h, int64_t o_stride_b,
+                                int64_t hq, int64_t hkv, int64_t head_dim, int64_t head_dim_v, int64_t page_size,
+                                int64_t num_pages, int64_t max_pages, int64_t q_stride_b, int64_t q_stride_h,
+                                int64_t o_stride_b,
                                 int64_t o_stride_h, int64_t k_stride_page, int64_t k_stride_slot,
                                 int64_t k_stride_head, int64_t v_stride_page, int64_t v_stride_slot,
                                 int64_t v_stride_head, int64_t bt_stride, int table_is_int64, int lens_is_int64,
@@ -550,8 +571,11 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   using namespace dlb;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "paged_decode: dtype %d (need fp16 or bf16)", dtype);
-  DLB_CHECK_ARG(head_dim == 64 || head_dim == 128, DLB_ERR_UNSUPPORTED,
-                "paged_decode: head_dim %lld not supported (64 or 128)", (long long)head_dim);
+  DLB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0 && head_dim_v >= 8 && head_dim_v <= 128 &&
+                    head_dim_v % 8 == 0,
+                DLB_ERR_UNSUPPORTED, "paged_decode: head_dim %lld / %lld not supported (multiples of 8 up to 128)",
+                (long long)head_dim, (long long)head_dim_v);
+  const int width = (head_dim <= 64 && head_dim_v <= 64) ? 64 : 128;
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && hkv >= 1 && hq % hkv == 0, DLB_ERR_BAD_ARG, "paged_decode: bad head counts");
   DLB_CHECK_ARG(page_size >= 1 && (page_size & (page_size - 1)) == 0, DLB_ERR_UNSUPPORTED,
                 "paged_decode: page size %lld must be a power of two", (long long)page_size);
@@ -572,7 +596,7 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   int rc = make_tmap_cache(&tk, k_cache, head_dim, hkv, page_size, num_pages, k_stride_page, k_stride_slot,
                            k_stride_head, box_slots);
   if (rc != DLB_OK) return rc;
-  rc = make_tmap_cache(&tv, v_cache, head_dim, hkv, page_size, num_pages, v_stride_page, v_stride_slot,
+  rc = make_tmap_cache(&tv, v_cache, head_dim_v, hkv, page_size, num_pages, v_stride_page, v_stride_slot,
                        v_stride_head, box_slots);
   if (rc != DLB_OK) return rc;
 
@@ -591,6 +615,8 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   p.hq = (int)hq;
   p.hkv = (int)hkv;
   p.group = (int)(hq / hkv);
+  p.dk = (int)head_dim;
+  p.dv = (int)head_dim_v;
   p.page_size = (int)page_size;
   p.max_pages = (int)max_pages;
   p.num_pages = (int)num_pages;
@@ -617,10 +643,10 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   p.v_stride_head = v_stride_head;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DLB_DTYPE_BF16) {
-    return head_dim == 128 ? launch_decode<__nv_bfloat16, 128>(tk, tv, p, s)
-                           : launch_decode<__nv_bfloat16, 64>(tk, tv, p, s);
+    return width == 128 ? launch_decode<__nv_bfloat16, 128>(tk, tv, p, s)
+                        : launch_decode<__nv_bfloat16, 64>(tk, tv, p, s);
   }
-  return head_dim == 128 ? launch_decode<__half, 128>(tk, tv, p, s) : launch_decode<__half, 64>(tk, tv, p, s);
+  return width == 128 ? launch_decode<__half, 128>(tk, tv, p, s) : launch_decode<__half, 64>(tk, tv, p, s);
 }
 
 // ----------------------------------------------------------------------------
@@ -701,7 +727,7 @@ extern "C" int dlb_paged_decode_static(const void* q, const void* k_cache, const
   const int rc = decode_scratch_address(&scratch);
   if (rc != DLB_OK) return rc;
   return dlb_paged_decode(q, k_cache, v_cache, out, block_table, kv_seqlens, scratch, batch, hq, hkv, head_dim,
-                          page_size, num_pages, max_pages, q_stride_b, q_stride_h, o_stride_b, o_stride_h,
+                          head_dim, page_size, num_pages, max_pages, q_stride_b, q_stride_h, o_stride_b, o_stride_h,
                           k_stride_page, k_stride_slot, k_stride_head, v_stride_page, v_stride_slot, v_stride_head,
                           bt_stride, table_is_int64, lens_is_int64, chunk, max_splits, window, sm_scale, softcap,
                           dtype, status, stream);

@@ -32,7 +32,9 @@ def decode_attention_fwd(
     dev = _lib.require_cuda(q, k_buffer, v_buffer, o, req_to_token, b_req_idx, b_seq_len)
     assert q.dim() == 3 and k_buffer.dim() == 3 and v_buffer.dim() == 3
     batch, head, D = q.shape
-    assert k_buffer.shape[-1] == D and v_buffer.shape[-1] == D, "K and V head sizes must equal the query's"
+    Dv = v_buffer.shape[-1]
+    assert k_buffer.shape[-1] == D and o.shape[-1] == Dv, "k must have the query's head size, o the value's"
+    assert D % 8 == 0 and Dv % 8 == 0 and D <= 128 and Dv <= 128, "head sizes: multiples of 8 up to 128"
     assert q.stride(-1) == 1 and o.stride(-1) == 1 and k_buffer.stride(-1) == 1 and v_buffer.stride(-1) == 1
     hkv = k_buffer.shape[1]
     table = req_to_token.index_select(0, b_req_idx.to(torch.int64))
@@ -45,13 +47,13 @@ def decode_attention_fwd(
     chunk = _pick_chunk(batch, hkv, table.size(1), 1)
     max_splits = (table.size(1) + chunk - 1) // chunk
     lib = _lib.load()
-    nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, D, max_splits)
+    nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, max(D, Dv), max_splits)
     partial = torch.empty(max(nfloats, 1), dtype=torch.float32, device=dev)
     status = _lib.status_word(dev)
     with torch.cuda.device(dev):
         rc = lib.dlb_paged_decode(
             q.data_ptr(), k_buffer.data_ptr(), v_buffer.data_ptr(), o.data_ptr(), table.data_ptr(), lens.data_ptr(),
-            partial.data_ptr(), batch, head, hkv, D, 1, k_buffer.size(0), table.size(1),
+            partial.data_ptr(), batch, head, hkv, D, Dv, 1, k_buffer.size(0), table.size(1),
             q.stride(0), q.stride(1), o.stride(0), o.stride(1),
             k_buffer.stride(0), k_buffer.stride(0), k_buffer.stride(1),
             v_buffer.stride(0), v_buffer.stride(0), v_buffer.stride(1),

@@ -45,7 +45,10 @@ def paged_attention_fwd(
     position `kv_seqlens - q_seqlens + i` and attends causally to the cache, which must already hold the
     new tokens' K/V (fill_kv_cache runs first, as in the reference's callers).
     Sliding window and tanh soft-cap as in the reference, in both branches.
-    Restrictions of this implementation: D == Dv in {64, 128}, fp16/bf16, page size a power of two >= 16.
+    The q/k head size and the v/out head size may differ (paged_attention.py:526-539); both must be
+    multiples of 8 up to 128 (the kernels run at tile widths 64 and 128 and let the copy engine zero-fill
+    the missing columns in shared memory; the cache is never copied or padded).  fp16/bf16, page size a
+    power of two >= 16.
     """
     dev = _lib.require_cuda(q, k, v, o, block_offsets, kv_seqlens)
     if window_size is None:
@@ -61,7 +64,7 @@ def paged_attention_fwd(
     BLOCK = k.size(1)
     assert BLOCK >= 16
     is_decoding = q.shape[-3] == q_seqlens.size(0)
-    assert Lk == Lv, "the kernels need equal K and V head sizes"
+    assert Lk % 8 == 0 and Lv % 8 == 0 and Lk <= 128 and Lv <= 128, "head sizes: multiples of 8 up to 128"
     if not is_decoding:
         return _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens, max_seqlen,
                               window_size, sm_scale, logit_softcapping, dev)
@@ -79,13 +82,13 @@ def paged_attention_fwd(
         # a window touches at most window + one tile of alignment slack
         max_splits = min(max_splits, (window_size + 64 + chunk - 1) // chunk + 1)
     lib = _lib.load()
-    nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, Lq, max_splits)
+    nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, max(Lq, Lv), max_splits)
     partial = torch.empty(max(nfloats, 1), dtype=torch.float32, device=dev)
     status = _lib.status_word(dev)
     with torch.cuda.device(dev):
         rc = lib.dlb_paged_decode(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), block_offsets.data_ptr(), kv_seqlens.data_ptr(),
-            partial.data_ptr(), batch, head, hkv, Lq, BLOCK, k.size(0), max_pages,
+            partial.data_ptr(), batch, head, hkv, Lq, Lv, BLOCK, k.size(0), max_pages,
             q.stride(-3), q.stride(-2), o.stride(-3), o.stride(-2),
             k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
             block_offsets.stride(0), int(block_offsets.dtype == torch.int64), int(kv_seqlens.dtype == torch.int64),
@@ -99,7 +102,7 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
                    logit_softcapping, dev):
     """Prefill branch of paged_attention_fwd (paged_attention.py:617-671): the tcgen05 prefill kernel with
     its K/V tiles fetched page by page."""
-    assert q.dim() == 3 and o.shape == q.shape and q.stride(-1) == 1 and o.stride(-1) == 1
+    assert q.dim() == 3 and o.shape[:-1] == q.shape[:-1] and q.stride(-1) == 1 and o.stride(-1) == 1
     assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
     assert block_offsets.dtype in (torch.int32, torch.int64)
@@ -113,7 +116,7 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
         rc = lib.dlb_flash_prefill_paged(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), None, block_offsets.data_ptr(),
             q_start.data_ptr(), q_len.data_ptr(), kv_len.data_ptr(), batch, q.shape[0], int(max_seqlen),
-            q.shape[1], k.shape[2], q.shape[2], k.size(1), k.size(0), block_offsets.size(1),
+            q.shape[1], k.shape[2], q.shape[2], v.shape[3], k.size(1), k.size(0), block_offsets.size(1),
             q.stride(0), q.stride(1), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
             o.stride(0), o.stride(1), block_offsets.stride(0), int(block_offsets.dtype == torch.int64),
             int(window_size), float(sm_scale), float(logit_softcapping), 1, _lib.dtype_code(q), status.data_ptr(),

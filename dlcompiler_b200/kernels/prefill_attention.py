@@ -16,12 +16,14 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     [Hq, total]) is given it receives m * sm_scale + log(sum), the natural-log convention of
     python/dlBLAS/dlblas/kernels/flash_attention.py:152-155.
 
-    The tensor-core kernel is built for head sizes 64 and 128.  Any other size up to 128 (the reference
-    rounds up to a power of two and masks, prefill_attention.py:179-180; its test runs 96, 80 and 13,
-    tests/kernels/test_attention_kernels.py:157) is run by zero-padding q, k and v to the next built size
-    on the device: padded feature columns add exact zeros to every score and produce output columns
-    that are dropped, and the softmax scale still comes from the true head size.  The padded copies cost
-    one extra pass over q, k, v and o.
+    The tensor-core kernel is built for tile widths 64 and 128.  Any other head size up to 128 (the
+    reference rounds up to a power of two and masks, prefill_attention.py:179-180; its test runs 96, 80 and
+    13, tests/kernels/test_attention_kernels.py:157) runs on the next width.  For multiples of 8 nothing is
+    copied: the tensor maps carry the true size and the copy engine zero-fills the missing columns of every
+    tile in shared memory.  Sizes that are not multiples of 8 (rows that are not 16-byte aligned cannot be
+    addressed by the copy engine) are zero-padded to the next multiple of 8 on the device first, one extra
+    pass over q, k, v and o.  Zero feature columns add exact zeros to every score; the softmax scale comes
+    from the true head size.
     """
     dev = _lib.require_cuda(q, k, v, o, b_start_loc, b_seq_len, lse)
     assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3 and o.shape == q.shape
@@ -31,9 +33,9 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and o.stride(-1) == 1
     if sm_scale is None:
         sm_scale = 1.0 / (Lq**0.5)
-    if Lq not in (64, 128):
-        assert 1 <= Lq <= 128, "head sizes above 128 are not built"
-        pad = (64 if Lq <= 64 else 128) - Lq
+    assert 1 <= Lq <= 128, "head sizes above 128 are not built"
+    if Lq % 8 != 0 or any(t.stride(0) % 8 or t.stride(1) % 8 for t in (q, k, v, o)):
+        pad = (Lq + 7) // 8 * 8 - Lq
         qp, kp, vp = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
         op = torch.empty_like(qp)
         context_attention_fwd(qp, kp, vp, op, b_start_loc, b_seq_len, max_input_len, lse=lse, causal=causal,
@@ -52,7 +54,7 @@ def context_attention_fwd(q, k, v, o, b_start_loc, b_seq_len, max_input_len, lse
     with torch.cuda.device(dev):
         rc = lib.dlb_flash_prefill_varlen(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), _lib.ptr(lse), b_start_loc.data_ptr(),
-            b_seq_len.data_ptr(), batch, q.shape[0], int(max_input_len), head, k.shape[1], Lq,
+            b_seq_len.data_ptr(), batch, q.shape[0], int(max_input_len), head, k.shape[1], Lq, Lv,
             q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), o.stride(0), o.stride(1),
             float(sm_scale), int(causal), _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "context_attention_fwd")

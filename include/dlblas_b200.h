@@ -199,14 +199,15 @@ int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, i
                     int64_t out_row_stride, int dtype, const void* topk_ids, int ids_are_int64, int64_t id_lo,
                     int64_t id_hi, void* stream);
 
-/* Varlen causal GQA flash-attention prefill.  q [total, hq, d], k/v [total, hkv, d], out like q,
+/* Varlen causal GQA flash-attention prefill.  q [total, hq, head_dim], k [total, hkv, head_dim],
+ * v [total, hkv, head_dim_v], out [total, hq, head_dim_v] (head sizes: multiples of 8 up to 128),
  * lse (optional, may be NULL) fp32 [hq, total] = m * sm_scale + log(sum) in natural log.
  * Replaces context_attention_fwd, python/dlBLAS/dlblas/kernels/prefill_attention.py:155-181
  * (kernel :28-152); LSE convention of python/dlBLAS/dlblas/kernels/flash_attention.py:152-155. */
 int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
                              const int32_t* b_start_loc, const int32_t* b_seq_len, int64_t batch,
                              int64_t total_tokens, int64_t max_seq_len, int64_t hq, int64_t hkv, int64_t head_dim,
-                             int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
+                             int64_t head_dim_v, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
                              int64_t v_stride_t, int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h,
                              float sm_scale, int causal, int dtype, int32_t* status, void* stream);
 
@@ -215,33 +216,37 @@ int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* 
  * [num_pages, page_size, hkv, d], block_table [batch, max_pages] (int32 or int64), kv_seq_len [batch] =
  * history + q_seq_len; query i of a sequence sees keys 0 .. history + i (with window > 0 only the last
  * window + 1 of them; with softcap > 0 scores become softcap * tanh(score * sm_scale / softcap)).  Same
- * kernel as dlb_flash_prefill_varlen with K/V tiles fetched page by page.  Replaces the prefill branch of
+ * kernel as dlb_flash_prefill_varlen with K/V tiles fetched page by page; head_dim / head_dim_v as there
+ * (the reference test runs 48 / 32 and 32 / 32 over 16-token pages).  Replaces the prefill branch of
  * paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:617-671 (kernel :311-489). */
 int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                             const void* block_table, const int32_t* q_start_loc, const int32_t* q_seq_len,
                             const int32_t* kv_seq_len, int64_t batch, int64_t total_q_tokens, int64_t max_q_len,
-                            int64_t hq, int64_t hkv, int64_t head_dim, int64_t page_size, int64_t num_pages,
-                            int64_t max_pages, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_page,
-                            int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
-                            int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t, int64_t o_stride_h,
-                            int64_t bt_stride, int table_is_int64, int64_t window, float sm_scale, float softcap,
-                            int causal, int dtype, int32_t* status, void* stream);
+                            int64_t hq, int64_t hkv, int64_t head_dim, int64_t head_dim_v, int64_t page_size,
+                            int64_t num_pages, int64_t max_pages, int64_t q_stride_t, int64_t q_stride_h,
+                            int64_t k_stride_page, int64_t k_stride_slot, int64_t k_stride_head,
+                            int64_t v_stride_page, int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
+                            int64_t o_stride_h, int64_t bt_stride, int table_is_int64, int64_t window, float sm_scale,
+                            float softcap, int causal, int dtype, int32_t* status, void* stream);
 
-/* Number of fp32 elements of the split-KV workspace dlb_paged_decode needs (0 when max_splits == 1). */
+/* Number of fp32 elements of the split-KV workspace dlb_paged_decode needs (0 when max_splits == 1);
+ * head_dim = the larger of the q/k and the v head size. */
 int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t head_dim, int64_t max_splits);
 
 /* Paged flash-decode (one query token per sequence), split over the KV length in `chunk`-token
  * pieces with a log-sum-exp merge.  Caches are [num_pages, page_size, hkv, d]; block_table is
- * [batch, max_pages] (int32 or int64).  Replaces the decode branch of paged_attention_fwd,
- * python/dlBLAS/dlblas/kernels/paged_attention.py:492-671 (kernels :40-285). */
+ * [batch, max_pages] (int32 or int64).  head_dim is the q / k head size, head_dim_v the v / out head
+ * size: multiples of 8 up to 128, not necessarily equal (the reference handles any head size by a power
+ * of two plus a remainder, and a v size of its own: paged_attention.py:526-539).  Replaces the decode
+ * branch of paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:492-671 (kernels :40-285). */
 int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* block_table,
                      const void* kv_seqlens, float* partial, int64_t batch, int64_t hq, int64_t hkv,
-                     int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages, int64_t q_stride_b,
-                     int64_t q_stride_h, int64_t o_stride_b, int64_t o_stride_h, int64_t k_stride_page,
-                     int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page, int64_t v_stride_slot,
-                     int64_t v_stride_head, int64_t bt_stride, int table_is_int64, int lens_is_int64, int64_t chunk,
-                     int64_t max_splits, int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
-                     void* stream);
+                     int64_t head_dim, int64_t head_dim_v, int64_t page_size, int64_t num_pages, int64_t max_pages,
+                     int64_t q_stride_b, int64_t q_stride_h, int64_t o_stride_b, int64_t o_stride_h,
+                     int64_t k_stride_page, int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
+                     int64_t v_stride_slot, int64_t v_stride_head, int64_t bt_stride, int table_is_int64,
+                     int lens_is_int64, int64_t chunk, int64_t max_splits, int64_t window, float sm_scale,
+                     float softcap, int dtype, int32_t* status, void* stream);
 
 /* rms_norm with optional residual add.  new_x = x + residual in the storage dtype (written to
  * out_residual when given); out = w * (new_x * rsqrt(mean(new_x^2) + eps)).  weight_after_cast = 0

@@ -145,16 +145,22 @@ def main():
     fns = load_functions(os.path.join(tests, "test_paged_attention.py"),
                          ["_conti_input", "_make_bias", "_make_blocked_cache", "_naive_attention"])
     cases = []
-    for i, (d, hq, hkv, page, hist, dtype) in enumerate([(64, 8, 2, 16, [50, 40, 30, 20], torch.float16),
-                                                         (128, 8, 2, 16, [150, 77, 200, 16], torch.bfloat16),
-                                                         (128, 4, 4, 64, [64, 65, 1, 200], torch.float16)]):
+    # first the reference test's own geometry (test_paged_attention.py:247-262: head sizes 48 and 32 with a
+    # v head size of 32, 8 / 2 and 2 / 2 heads, 16-token pages, fp16), then the sizes of the benchmark
+    ref_geometry = [(dk, 32, hq, hkv, 16, [50, 40, 30, 20], torch.float16)
+                    for dk in (48, 32) for hq, hkv in ((8, 2), (2, 2))]
+    for i, (d, dv, hq, hkv, page, hist, dtype) in enumerate(ref_geometry + [
+            (64, 64, 8, 2, 16, [50, 40, 30, 20], torch.float16),
+            (128, 128, 8, 2, 16, [150, 77, 200, 16], torch.bfloat16),
+            (128, 128, 4, 4, 64, [64, 65, 1, 200], torch.float16),
+            (96, 64, 4, 2, 32, [70, 3, 129, 64], torch.bfloat16)]):
         torch.manual_seed(123 + i)
         seq_lens = torch.tensor([1, 1, 1, 1])
         history = torch.tensor(hist)
         full = seq_lens + history
         bq = torch.rand(4, 1, hq, d).to(dtype)
         bk = torch.rand(4, int(full.max()), hkv, d).to(dtype)
-        bv = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        bv = torch.rand(4, int(full.max()), hkv, dv).to(dtype)
         nblk = (full + page - 1) // page
         offs = [torch.arange(int(n)) * 4 + idx for idx, n in enumerate(nblk)]
         table = torch.zeros(4, max(len(o) for o in offs), dtype=torch.int64)
@@ -162,24 +168,27 @@ def main():
             row[:len(o)] = o
         mask = fns["_make_bias"](seq_lens, history, -1e30)
         gt = fns["_naive_attention"](bq, (bk, bv), mask)
-        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, d)
+        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, dv)
         cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
                       "block_offsets": table, "kv_seqlens": full, "gt": fns["_conti_input"](gt, seq_lens)})
     torch.save(cases, os.path.join(HERE, "paged_decode.pt"))
     # ---------------------------------------------------------------- paged prefill with history (same test file:
     # the reference's test of the prefill branch, test_paged_attention.py:150-290, with its own mask builder)
     cases = []
-    for i, (d, hq, hkv, page, seqs, hist, dtype) in enumerate([
-            (64, 8, 2, 16, [30, 50, 70, 90], [50, 40, 30, 20], torch.float16),       # the reference test's own lengths
-            (128, 8, 2, 64, [5, 130, 1, 64], [100, 37, 200, 0], torch.bfloat16),
-            (128, 4, 4, 16, [17, 33, 2, 80], [0, 15, 64, 1], torch.float16)]):
+    ref_geometry = [(dk, 32, hq, hkv, 16, [30, 50, 70, 90], [50, 40, 30, 20], torch.float16)
+                    for dk in (48, 32) for hq, hkv in ((8, 2), (2, 2))]     # test_paged_attention.py:247-262
+    for i, (d, dv, hq, hkv, page, seqs, hist, dtype) in enumerate(ref_geometry + [
+            (64, 64, 8, 2, 16, [30, 50, 70, 90], [50, 40, 30, 20], torch.float16),
+            (128, 128, 8, 2, 64, [5, 130, 1, 64], [100, 37, 200, 0], torch.bfloat16),
+            (128, 128, 4, 4, 16, [17, 33, 2, 80], [0, 15, 64, 1], torch.float16),
+            (80, 128, 4, 2, 32, [40, 150, 3, 64], [9, 0, 70, 64], torch.bfloat16)]):
         torch.manual_seed(223 + i)
         seq_lens = torch.tensor(seqs)
         history = torch.tensor(hist)
         full = seq_lens + history
         bq = torch.rand(4, int(seq_lens.max()), hq, d).to(dtype)
         bk = torch.rand(4, int(full.max()), hkv, d).to(dtype)
-        bv = torch.rand(4, int(full.max()), hkv, d).to(dtype)
+        bv = torch.rand(4, int(full.max()), hkv, dv).to(dtype)
         nblk = (full + page - 1) // page
         offs = [torch.arange(int(n)) * 4 + idx for idx, n in enumerate(nblk)]
         table = torch.zeros(4, max(len(o) for o in offs), dtype=torch.int64)
@@ -187,7 +196,7 @@ def main():
             row[:len(o)] = o
         mask = fns["_make_bias"](seq_lens, history, -1e30)
         gt = fns["_naive_attention"](bq, (bk, bv), mask)
-        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, d)
+        blocked_k, blocked_v = fns["_make_blocked_cache"](bk, bv, seq_lens, history, table, page, hkv, d, dv)
         cases.append({"q": fns["_conti_input"](bq, seq_lens), "k_cache": blocked_k, "v_cache": blocked_v,
                       "block_offsets": table, "q_seqlens": seq_lens, "kv_seqlens": full,
                       "gt": fns["_conti_input"](gt, seq_lens)})

@@ -62,8 +62,8 @@ def test_argument_errors_are_reported_without_a_device():
     assert rc < 0 and b"experts" in lib.dlb_last_error()
     with pytest.raises(AssertionError):
         _lib.check(rc, "gating")
-    rc = lib.dlb_paged_decode(None, None, None, None, None, None, None, 1, 32, 8, 96, 64, 1, 1, 0, 0, 0, 0, 0, 0, 0,
-                              0, 0, 0, 0, 0, 0, 256, 1, -1, 1.0, -1.0, _lib.DTYPE_BF16, None, None)
+    rc = lib.dlb_paged_decode(None, None, None, None, None, None, None, 1, 32, 8, 100, 64, 64, 1, 1, 0, 0, 0, 0, 0, 0,
+                              0, 0, 0, 0, 0, 0, 0, 256, 1, -1, 1.0, -1.0, _lib.DTYPE_BF16, None, None)
     assert rc < 0 and b"head_dim" in lib.dlb_last_error()
     rc = lib.dlb_moe_grouped_gemm(1, 100, 64, 1, 4, 128, 64, 64, 1, 128, 128, 1, 1, None, 10, 0, _lib.DTYPE_BF16,
                                   None, None)

@@ -95,7 +95,7 @@ def test_prefill_config_full_groups_and_properties(cuda_device):
 
 def _run_decode(dev, d, **kw):
     q = d["q"].to(dev)
-    o = torch.full_like(q, float("nan"))
+    o = torch.full(q.shape[:-1] + (d["v_cache"].shape[-1],), float("nan"), dtype=q.dtype, device=dev)
     B = q.shape[0]
     paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["block_table"].to(dev),
                         torch.arange(B, device=dev), torch.ones(B, dtype=torch.int64, device=dev),
@@ -251,7 +251,7 @@ def test_decode_small_pages(cuda_device, page):
     chunk, splits = 256, (tb.size(1) * page + 255) // 256
     part = torch.empty(max(lib.dlb_paged_decode_workspace_floats(3, 8, 128, splits), 1), device=dev)
     rc = lib.dlb_paged_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), tb.data_ptr(), ln.data_ptr(),
-                              part.data_ptr(), 3, 8, 2, 128, page, kc.size(0), tb.size(1), q.stride(0), q.stride(1),
+                              part.data_ptr(), 3, 8, 2, 128, 128, page, kc.size(0), tb.size(1), q.stride(0), q.stride(1),
                               o.stride(0), o.stride(1), kc.stride(0), kc.stride(1), kc.stride(2), vc.stride(0),
                               vc.stride(1), vc.stride(2), tb.stride(0), 0, 0, chunk, splits, -1, 128 ** -0.5, -1.0,
                               _lib.DTYPE_BF16, _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
@@ -376,7 +376,7 @@ def test_paged_prefill_golden(cuda_device, golden_dir):
     for c in torch.load(os.path.join(golden_dir, "paged_prefill.pt"), weights_only=True):
         dev = cuda_device
         q = c["q"].to(dev)
-        o = torch.full_like(q, float("nan"))
+        o = torch.full(q.shape[:-1] + (c["v_cache"].shape[-1],), float("nan"), dtype=q.dtype, device=dev)
         q_lens = c["q_seqlens"]
         start = torch.cumsum(q_lens, 0) - q_lens
         paged_attention_fwd(q, c["k_cache"].to(dev), c["v_cache"].to(dev), o, c["block_offsets"].to(dev),
@@ -384,3 +384,47 @@ def test_paged_prefill_golden(cuda_device, golden_dir):
         # reference test: atol=1e-3, rtol=1e-5 for fp16 (test_paged_attention.py:286)
         tol = 1e-3 if q.dtype == torch.float16 else 8e-3
         torch.testing.assert_close(o.cpu(), c["gt"], atol=tol, rtol=1e-5)
+
+
+def test_paged_prefill_ignores_stale_cache_slots(cuda_device, golden_dir):
+    """Cache slots past a sequence's last key (the tail of its last page, and every page that no sequence
+    uses) may hold anything, NaN bit patterns included: the output must not change by a bit."""
+    for c in torch.load(os.path.join(golden_dir, "paged_prefill.pt"), weights_only=True)[:6]:
+        dev = cuda_device
+        q = c["q"].to(dev)
+        q_lens = c["q_seqlens"]
+        start = torch.cumsum(q_lens, 0) - q_lens
+        page = c["k_cache"].shape[1]
+
+        def run(kc, vc):
+            o = torch.full(q.shape[:-1] + (vc.shape[-1],), float("nan"), dtype=q.dtype, device=dev)
+            paged_attention_fwd(q, kc.to(dev), vc.to(dev), o, c["block_offsets"].to(dev), start.to(dev),
+                                q_lens.to(dev), c["kv_seqlens"].to(dev), int(q_lens.max()))
+            return o.cpu()
+
+        base = run(c["k_cache"], c["v_cache"])
+        kc, vc = c["k_cache"].clone(), c["v_cache"].clone()
+        live = torch.zeros(kc.shape[0], page, dtype=torch.bool)
+        for b, n in enumerate(c["kv_seqlens"].tolist()):
+            for t in range(n):
+                live[int(c["block_offsets"][b, t // page]), t % page] = True
+        kc[~live] = float("nan")
+        vc[~live] = float("nan")
+        out = run(kc, vc)
+        assert torch.isfinite(out.float()).all()
+        assert torch.equal(out, base)
+
+
+@pytest.mark.parametrize("q_lens,hist", [([30, 50, 70, 90], [50, 40, 30, 20]), ([1, 1, 1, 1], [50, 40, 30, 20])])
+def test_paged_window_at_the_reference_test_sizes(cuda_device, q_lens, hist):
+    """The reference's sliding-window test geometry (test_paged_attention.py:303-316): head size 16 for q, k
+    and v, 4 / 2 heads, window 32, 16-token pages, fp16; prefill with history and decode."""
+    d = _paged_prefill_case(31, q_lens, hist, 16, 4, 2, 16, torch.float16)
+    dev = cuda_device
+    q = d["q"].to(dev)
+    o = torch.full_like(q, float("nan"))
+    paged_attention_fwd(q, d["k_cache"].to(dev), d["v_cache"].to(dev), o, d["table"].to(dev), d["q_start"].to(dev),
+                        d["q_lens"].to(dev), d["kv_lens"].to(dev), max(q_lens), window_size=32)
+    ref = oracle.paged_prefill_attention(d["q"], d["k_cache"], d["v_cache"], d["table"], d["q_start"], d["q_lens"],
+                                         d["kv_lens"], window_size=32)
+    torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=1e-3, atol=1e-3)
