@@ -61,9 +61,9 @@ SIGNATURES = {
     "dlb_flash_prefill_varlen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                         c_float, c_int, c_int, c_void_p, c_void_p]),
-    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 21 + [c_int, c_int64, c_float, c_float, c_int, c_int,
-                                                                      c_void_p, c_void_p]),
+                                         c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "dlb_flash_prefill_paged": (c_int, [c_void_p] * 9 + [c_int64] * 21 + [c_int, c_int64, c_float, c_float, c_int, c_void_p,
+                                                                      c_void_p, c_int, c_void_p, c_void_p]),
     "dlb_paged_decode_workspace_floats": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "dlb_paged_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
@@ -76,7 +76,7 @@ SIGNATURES = {
     "dlb_apply_rotary": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int,
                                  c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
                                  c_void_p]),
-    "dlb_fill_kv_cache": (c_int, [c_void_p] * 8 + [c_int64] * 19 + [c_int] * 5 + [c_void_p]),
+    "dlb_fill_kv_cache": (c_int, [c_void_p] * 8 + [c_int64] * 19 + [c_int] * 5 + [c_void_p, c_void_p, c_int, c_void_p]),
     "dlb_paged_decode_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                         c_int64, c_int64, c_int64, c_int64,

@@ -108,6 +108,41 @@ template <> struct Elem<float> {
   static __device__ __forceinline__ float from_f(float v) { return v; }
 };
 
+// Rotate-half rotary embedding of one (lower, upper) element pair, arithmetic in the tensors' 16-bit type:
+// each product and the sum round to T, as separate operations in T would (the reference evaluates
+// x * cos + rotate_half(x) * sin in the tensor dtype, apply_rotary_pos_emb.py:50-54,70-71).
+template <typename T> __device__ __forceinline__ T rot_lo(T lo, T hi, T c, T s) {
+  const float a = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(lo) * Elem<T>::to_f(c)));
+  const float b = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(hi) * Elem<T>::to_f(s)));
+  return Elem<T>::from_f(a - b);
+}
+template <typename T> __device__ __forceinline__ T rot_hi(T lo, T hi, T c, T s) {
+  const float a = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(hi) * Elem<T>::to_f(c)));
+  const float b = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(lo) * Elem<T>::to_f(s)));
+  return Elem<T>::from_f(a + b);
+}
+// the same on 8 pairs held in two 16-byte vectors, with packed two-element arithmetic: a packed multiply,
+// add or subtract rounds each lane once to T, which is what the scalar form above does (the fp32
+// product of two 16-bit values is exact, and so is the fp32 sum whenever it could round differently)
+template <typename T>
+__device__ __forceinline__ void rot_vec8(const uint4& lo, const uint4& hi, const uint4& cl, const uint4& ch,
+                                         const uint4& sl, const uint4& sh, uint4& olo, uint4& ohi) {
+  using T2 = typename Elem<T>::T2;
+  const T2* l2 = reinterpret_cast<const T2*>(&lo);
+  const T2* h2 = reinterpret_cast<const T2*>(&hi);
+  const T2* cl2 = reinterpret_cast<const T2*>(&cl);
+  const T2* ch2 = reinterpret_cast<const T2*>(&ch);
+  const T2* sl2 = reinterpret_cast<const T2*>(&sl);
+  const T2* sh2 = reinterpret_cast<const T2*>(&sh);
+  T2* ol2 = reinterpret_cast<T2*>(&olo);
+  T2* oh2 = reinterpret_cast<T2*>(&ohi);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    ol2[j] = __hsub2_rn(__hmul2_rn(l2[j], cl2[j]), __hmul2_rn(h2[j], sl2[j]));
+    oh2[j] = __hadd2_rn(__hmul2_rn(h2[j], ch2[j]), __hmul2_rn(l2[j], sh2[j]));
+  }
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }

@@ -66,7 +66,7 @@ template <int D> struct Layout {
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
   static constexpr int OFF_CTRL = OFF_V + KV_STAGES * KV_BYTES;
-  static constexpr int SMEM_BYTES = OFF_CTRL + 128;   // D=128: two CTAs (plus 1 KiB system reserve each) fit one SM
+  static constexpr int SMEM_BYTES = OFF_CTRL + 160;   // D=128: two CTAs (plus 1 KiB system reserve each) fit one SM
 };
 }  // namespace fp
 
@@ -152,6 +152,13 @@ struct PrefillParams {
   int table_is_int64;
   const int32_t* kv_seq_len;      // [batch]
   // Extras of the paged prefill branch (kernel instantiated with EXTRAS only when one is on):
+  // Rotary embedding of Q inside the kernel (rotate-half convention, arithmetic in the 16-bit type): cos / sin
+  // are [total_tokens, rot_dim] rows indexed like q's tokens; null = q is used as it is.  The Q tile is loaded
+  // once per CTA, so its rotation is one pass of the softmax warps over the tile in shared memory; K is
+  // expected to be rotated already (fill_kv_cache does it while it writes the cache).
+  const void* rot_cos;
+  const void* rot_sin;
+  int rot_dim;
   int dv;                         // v / out head size (<= D, multiple of 8): output columns past it are not stored
   int window;                     // > 0: query at position pos sees keys pos - window .. pos (paged_attention.py:421-424,447)
   float softcap;                  // > 0: scores become softcap * tanh(score * sm_scale / softcap) (paged_attention.py:441-444)
@@ -212,7 +219,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   // block j, and its arrival must not count toward block j's phase
   uint64_t* p_full = bars + 11;    // [2]
   uint64_t* pv_done = bars + 13;   // [2] P.V of the block in S/P buffer s retired: V stage s reusable, O updated
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* q_ready = bars + 15;   // Q tile rotated in place by the softmax warps (only with rot_cos)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -220,6 +228,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_ready, 128);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
@@ -317,7 +326,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else if (warp == WARP_MMA) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 23, 0);
+      bool ok = mbar_wait(p.rot_cos != nullptr ? q_ready : q_full, 0, abort_flag, p.status, 23, 0);
+      if (p.rot_cos != nullptr) tc_fence_after_sync();
       // descriptors as (low, high) words: only the address field (bytes >> 4) in the low word moves
       const uint64_t q_d0 = make_smem_desc(smem_u32(smem + OFF_Q), 16, 1024, 2);
       const uint64_t k_d0 = make_smem_desc(smem_u32(smem + OFF_K), 16, 1024, 2);
@@ -377,7 +387,37 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     float m_ref = -CUDART_INF_F;                   // reference max used for exponentiation (scaled, log2 domain)
     float l_sum = 0.f;
     bool ok = true;
-    for (int j = 0; j < nb; ++j) {
+    if (p.rot_cos != nullptr) {
+      // rotate this thread's query row in place in the swizzled Q tile (16-byte chunk c of row r sits at chunk
+      // position c ^ (r & 7) of its 128-byte line), then hand the tile to the MMA thread
+      ok = mbar_wait(q_full, 0, abort_flag, p.status, 32, 0);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok && q_pos < seq_len) {
+        const int half = p.rot_dim >> 1, hv = half >> 3;
+        const T* cs = reinterpret_cast<const T*>(p.rot_cos) + (int64_t)(start + q_pos) * p.rot_dim;
+        const T* sn = reinterpret_cast<const T*>(p.rot_sin) + (int64_t)(start + q_pos) * p.rot_dim;
+        auto chunk_at = [&](int col) -> uint4* {
+          return reinterpret_cast<uint4*>(smem + OFF_Q + (col >> 6) * Q_BOX + row * 128 +
+                                          ((((col & 63) >> 3) ^ (row & 7)) << 4));
+        };
+#pragma unroll 2
+        for (int i = 0; i < hv; ++i) {
+          uint4* plo = chunk_at(i * 8);
+          uint4* phi = chunk_at(half + i * 8);
+          const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cs) + i);
+          const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cs + half) + i);
+          const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sn) + i);
+          const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sn + half) + i);
+          uint4 olo, ohi;
+          rot_vec8<T>(*plo, *phi, cl, ch, sl, sh, olo, ohi);
+          *plo = olo;
+          *phi = ohi;
+        }
+      }
+      fence_proxy_async_smem();     // generic-proxy stores before the tensor core's reads of the tile
+      mbar_arrive(q_ready);
+    }
+    for (int j = 0; ok && j < nb; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       ok = mbar_wait(&s_full[s], ph, abort_flag, p.status, 28, j);
@@ -586,7 +626,8 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
                                         int64_t head_dim, int64_t head_dim_v, int64_t q_stride_t, int64_t q_stride_h,
                                         int64_t k_stride_t, int64_t k_stride_h, int64_t v_stride_t,
                                         int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h, float sm_scale,
-                                        int causal, int dtype, int32_t* status, void* stream) {
+                                        int causal, const void* q_cos, const void* q_sin, int dtype, int32_t* status,
+                                        void* stream) {
   using namespace dlb;
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
@@ -646,6 +687,12 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
   p.bt_stride = 0;
   p.table_is_int64 = 0;
   p.kv_seq_len = nullptr;
+  DLB_CHECK_ARG((q_cos == nullptr) == (q_sin == nullptr), DLB_ERR_BAD_ARG, "flash_prefill: cos and sin go together");
+  DLB_CHECK_ARG(q_cos == nullptr || (head_dim % 16 == 0 && (((uintptr_t)q_cos | (uintptr_t)q_sin) & 15) == 0),
+                DLB_ERR_ALIGNMENT, "flash_prefill: rotary needs a head size that is a multiple of 16 and 16-byte aligned cos / sin");
+  p.rot_cos = q_cos;
+  p.rot_sin = q_sin;
+  p.rot_dim = (int)head_dim;
   p.dv = (int)head_dim_v;
   p.window = 0;
   p.softcap = 0.f;
@@ -675,8 +722,8 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
                                        int64_t k_stride_slot, int64_t k_stride_head, int64_t v_stride_page,
                                        int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
                                        int64_t o_stride_h, int64_t bt_stride, int table_is_int64, int64_t window,
-                                       float sm_scale, float softcap, int causal, int dtype, int32_t* status,
-                                       void* stream) {
+                                       float sm_scale, float softcap, int causal, const void* q_cos,
+                                       const void* q_sin, int dtype, int32_t* status, void* stream) {
   using namespace dlb;
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
@@ -743,6 +790,14 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
   p.bt_stride = bt_stride;
   p.table_is_int64 = table_is_int64;
   p.kv_seq_len = kv_seq_len;
+  DLB_CHECK_ARG((q_cos == nullptr) == (q_sin == nullptr), DLB_ERR_BAD_ARG,
+                "flash_prefill_paged: cos and sin go together");
+  DLB_CHECK_ARG(q_cos == nullptr || (head_dim % 16 == 0 && (((uintptr_t)q_cos | (uintptr_t)q_sin) & 15) == 0),
+                DLB_ERR_ALIGNMENT,
+                "flash_prefill_paged: rotary needs a head size that is a multiple of 16 and 16-byte aligned cos / sin");
+  p.rot_cos = q_cos;
+  p.rot_sin = q_sin;
+  p.rot_dim = (int)head_dim;
   p.dv = (int)head_dim_v;
   p.window = window > 0 ? (int)std::min<int64_t>(window, 1 << 29) : 0;
   p.softcap = softcap;

@@ -163,18 +163,6 @@ static int launch_rms(const void* x, const void* w, const void* res, void* out, 
 // ----------------------------------------------------------------------------
 // rotary position embedding (rotate-half convention)
 // ----------------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ T rot_lo(T lo, T hi, T c, T s) {
-  // each product and the difference round to T, as separate operations in T would
-  const float a = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(lo) * Elem<T>::to_f(c)));
-  const float b = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(hi) * Elem<T>::to_f(s)));
-  return Elem<T>::from_f(a - b);
-}
-template <typename T> __device__ __forceinline__ T rot_hi(T lo, T hi, T c, T s) {
-  const float a = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(hi) * Elem<T>::to_f(c)));
-  const float b = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(lo) * Elem<T>::to_f(s)));
-  return Elem<T>::from_f(a + b);
-}
-
 struct RotaryParams {
   const void *q, *k, *cos, *sin;
   void *qo, *ko;
@@ -213,19 +201,7 @@ template <typename T> __global__ void __launch_bounds__(256) rotary_vec_kernel(c
     const uint4 hi = *(reinterpret_cast<const uint4*>(src + half) + i);
     const uint4 cl = __ldg(cs + i), ch = __ldg(cs + hv + i), sl = __ldg(sn + i), sh = __ldg(sn + hv + i);
     uint4 olo, ohi;
-    const T* l8 = reinterpret_cast<const T*>(&lo);
-    const T* h8 = reinterpret_cast<const T*>(&hi);
-    const T* cl8 = reinterpret_cast<const T*>(&cl);
-    const T* ch8 = reinterpret_cast<const T*>(&ch);
-    const T* sl8 = reinterpret_cast<const T*>(&sl);
-    const T* sh8 = reinterpret_cast<const T*>(&sh);
-    T* ol8 = reinterpret_cast<T*>(&olo);
-    T* oh8 = reinterpret_cast<T*>(&ohi);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      ol8[j] = rot_lo<T>(l8[j], h8[j], cl8[j], sl8[j]);
-      oh8[j] = rot_hi<T>(l8[j], h8[j], ch8[j], sh8[j]);
-    }
+    rot_vec8<T>(lo, hi, cl, ch, sl, sh, olo, ohi);
     *(reinterpret_cast<uint4*>(dst) + i) = olo;
     *(reinterpret_cast<uint4*>(dst + half) + i) = ohi;
   }
@@ -269,6 +245,7 @@ struct FillParams {
   int page, heads, dim_k, dim_v, max_pages, num_pages;
   int idx64_start, idx64_len, idx64_kv, idx64_table;
   int elem_size;
+  const void *k_cos, *k_sin;     // optional [total tokens, dim_k] rows in the states' dtype: K is rotated on its way in
 };
 
 __device__ __forceinline__ int64_t load_idx(const void* p, int64_t i, int is64) {
@@ -330,6 +307,62 @@ __global__ void __launch_bounds__(256) fill_kv_cache_kernel(const FillParams p) 
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       if (idx + j * stride < total) *dst[j] = val[j];
+  }
+}
+
+// The same walk with the rotary embedding of K applied on the way (rotate-half convention, arithmetic in the
+// 16-bit type, bit-identical to apply_rotary followed by a plain fill): one work item is a (lower, upper) pair
+// of 16-byte chunks of a K row, or one 16-byte chunk of a V row.  The cache then holds rotated keys, so the
+// attention kernels need no pass over K before they read it.
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kv_cache_rot_kernel(const FillParams p) {
+  const int b = blockIdx.x;
+  const int blk = blockIdx.y;
+  const int64_t q_start = load_idx(p.q_start, b, p.idx64_start);
+  const int q_len = (int)load_idx(p.q_len, b, p.idx64_len);
+  const int kv_len = (int)load_idx(p.kv_len, b, p.idx64_kv);
+  const int history = kv_len - q_len;
+  if (q_len <= 0 || history < 0) return;
+  const int first_slot0 = history % p.page;
+  const int page_idx = history / p.page + blk;
+  if (page_idx >= p.max_pages) return;
+  const int slot_lo = blk == 0 ? first_slot0 : 0;
+  const int slot_hi = min(p.page, q_len + first_slot0 - blk * p.page);
+  if (slot_lo >= slot_hi) return;
+  const int64_t page = load_idx(p.table, (int64_t)b * p.table_stride + page_idx, p.idx64_table);
+  if (page < 0 || page >= p.num_pages) return;
+  const int64_t tok0 = q_start + max(blk * p.page - first_slot0, 0);
+  const int half = p.dim_k >> 1, hv = half >> 3, v_units = p.dim_v >> 3;
+  const int per_tok = p.heads * (hv + v_units);
+  const int total = (slot_hi - slot_lo) * per_tok;
+  const int stride = blockDim.x * gridDim.z;
+#pragma unroll 2
+  for (int idx = threadIdx.x + blockIdx.z * blockDim.x; idx < total; idx += stride) {
+    const int s = idx / per_tok;
+    int r = idx - s * per_tok;
+    const int slot = slot_lo + s;
+    const int64_t tok = tok0 + s;
+    if (r < p.heads * hv) {
+      const int h = r / hv, i = r - h * hv;
+      const T* src = reinterpret_cast<const T*>(p.ks) + tok * p.ks_st + (int64_t)h * p.ks_sh;
+      T* dst = reinterpret_cast<T*>(p.kc) + page * p.kc_sp + (int64_t)slot * p.kc_ss + (int64_t)h * p.kc_sh;
+      const T* cs = reinterpret_cast<const T*>(p.k_cos) + tok * p.dim_k;
+      const T* sn = reinterpret_cast<const T*>(p.k_sin) + tok * p.dim_k;
+      const uint4 lo = *(reinterpret_cast<const uint4*>(src) + i);
+      const uint4 hi = *(reinterpret_cast<const uint4*>(src + half) + i);
+      const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cs) + i), ch = __ldg(reinterpret_cast<const uint4*>(cs + half) + i);
+      const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sn) + i), sh = __ldg(reinterpret_cast<const uint4*>(sn + half) + i);
+      uint4 olo, ohi;
+      rot_vec8<T>(lo, hi, cl, ch, sl, sh, olo, ohi);
+      *(reinterpret_cast<uint4*>(dst) + i) = olo;
+      *(reinterpret_cast<uint4*>(dst + half) + i) = ohi;
+    } else {
+      r -= p.heads * hv;
+      const int h = r / v_units, u = r - h * v_units;
+      const T* src = reinterpret_cast<const T*>(p.vs) + tok * p.vs_st + (int64_t)h * p.vs_sh;
+      T* dst = reinterpret_cast<T*>(p.vc) + page * p.vc_sp + (int64_t)slot * p.vc_ss + (int64_t)h * p.vc_sh;
+      *(reinterpret_cast<uint4*>(dst) + u) = *(reinterpret_cast<const uint4*>(src) + u);
+    }
   }
 }
 
@@ -410,7 +443,8 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
                                  int64_t vs_stride_h, int64_t kc_stride_page, int64_t kc_stride_slot,
                                  int64_t kc_stride_head, int64_t vc_stride_page, int64_t vc_stride_slot,
                                  int64_t vc_stride_head, int64_t table_stride, int start_is_int64, int qlen_is_int64,
-                                 int kvlen_is_int64, int table_is_int64, int elem_size, void* stream) {
+                                 int kvlen_is_int64, int table_is_int64, int elem_size, const void* k_cos,
+                                 const void* k_sin, int dtype, void* stream) {
   using namespace dlb;
   DLB_CHECK_ARG(batch >= 0 && max_q_seq_length >= 0 && page_size >= 1 && heads >= 1 && dim_k >= 1 && dim_v >= 0,
                 DLB_ERR_BAD_ARG, "fill_kv_cache: bad sizes");
@@ -434,6 +468,9 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
   p.idx64_start = start_is_int64; p.idx64_len = qlen_is_int64; p.idx64_kv = kvlen_is_int64;
   p.idx64_table = table_is_int64;
   p.elem_size = elem_size;
+  p.k_cos = k_cos;
+  p.k_sin = k_sin;
+  DLB_CHECK_ARG((k_cos == nullptr) == (k_sin == nullptr), DLB_ERR_BAD_ARG, "fill_kv_cache: cos and sin go together");
   // widest copy unit that every row start and row length allows
   auto mult = [&](int64_t v, int unit) { return (v * elem_size) % unit == 0; };
   const uintptr_t ptrs = (uintptr_t)k_states | (uintptr_t)v_states | (uintptr_t)k_caches | (uintptr_t)v_caches;
@@ -443,6 +480,16 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
     ok16 = ok16 && mult(v, 16);
   dim3 grid((unsigned)batch, (unsigned)blocks, 4);
   cudaStream_t s = (cudaStream_t)stream;
+  if (k_cos != nullptr) {
+    DLB_CHECK_ARG(ok16 && elem_size == 2 && dim_k % 16 == 0 && (dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16) &&
+                      (((uintptr_t)k_cos | (uintptr_t)k_sin) & 15) == 0,
+                  DLB_ERR_UNSUPPORTED,
+                  "fill_kv_cache: rotating K needs fp16/bf16, a head size that is a multiple of 16 and 16-byte aligned rows");
+    if (dtype == DLB_DTYPE_BF16) fill_kv_cache_rot_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
+    else fill_kv_cache_rot_kernel<__half><<<grid, 256, 0, s>>>(p);
+    DLB_CUDA_LAUNCH_CHECK();
+    return DLB_OK;
+  }
   if (ok16) fill_kv_cache_kernel<16><<<grid, 256, 0, s>>>(p);
   else if (elem_size == 4) fill_kv_cache_kernel<4><<<grid, 256, 0, s>>>(p);
   else if (elem_size == 2) fill_kv_cache_kernel<2><<<grid, 256, 0, s>>>(p);

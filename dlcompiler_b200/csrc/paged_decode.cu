@@ -129,7 +129,9 @@ __device__ __forceinline__ int load_index(const void* p, int64_t i, int is64) {
 
 // Token range [lo, hi) of split `s`; returns false if the split is empty.
 __device__ __forceinline__ bool split_range(int ctx, int window, int chunk, int s, int& lo, int& hi, int& kv_lo) {
-  kv_lo = (window > 0 && ctx > window) ? ctx - window : 0;
+  // the query sits at position ctx - 1 and sees keys ctx - 1 - window .. ctx - 1, as in the reference
+  // (paged_attention.py:163-165,192-194 with history_len = ctx - 1)
+  kv_lo = (window > 0 && ctx - 1 > window) ? ctx - 1 - window : 0;
   const int base = (kv_lo / pd::TILE_KEYS) * pd::TILE_KEYS;
   lo = base + s * chunk;
   hi = min(ctx, lo + chunk);

@@ -48,9 +48,10 @@ def call(q, k, v, causal, sm_scale, dropout_p):
     return flash_attention_fwd(q, k, v, causal, sm_scale)[0]
 
 
-def flash_attention_v2(q, k, v, causal=False, softmax_scale=None, return_lse=False):
+def flash_attention_v2(q, k, v, causal=False, softmax_scale=None, return_lse=False, q_cos=None, q_sin=None):
     """q, k, v [b, s, h, d] (flash_attention_v2.py:215-224); the reference's public `call(q, k, v)` is
-    the non-causal case.  Accumulation is fp32 (the reference kernel accumulates in fp16)."""
+    the non-causal case.  Accumulation is fp32 (the reference kernel accumulates in fp16).  `q_cos` /
+    `q_sin` ([b, s, d]): rotate q inside the kernel (see `context_attention_fwd`)."""
     batch, seqlen_q, nheads, d = q.shape
     assert k.shape == (batch, seqlen_q, nheads, d) and v.shape == k.shape
     assert q.dtype == k.dtype == v.dtype and q.dtype in (torch.float16, torch.bfloat16)
@@ -60,7 +61,8 @@ def flash_attention_v2(q, k, v, causal=False, softmax_scale=None, return_lse=Fal
     start = torch.arange(batch, dtype=torch.int32, device=q.device) * seqlen_q
     length = torch.full((batch,), seqlen_q, dtype=torch.int32, device=q.device)
     lse = torch.empty((nheads, batch * seqlen_q), dtype=torch.float32, device=q.device) if return_lse else None
-    context_attention_fwd(q2, k2, v2, o, start, length, seqlen_q, lse=lse, causal=causal, sm_scale=softmax_scale)
+    context_attention_fwd(q2, k2, v2, o, start, length, seqlen_q, lse=lse, causal=causal, sm_scale=softmax_scale,
+                          q_cos=q_cos, q_sin=q_sin)
     o = o.view(batch, seqlen_q, nheads, d)
     if return_lse:
         return o, lse.view(nheads, batch, seqlen_q).permute(1, 0, 2)

@@ -5,19 +5,18 @@ Reference semantics (fused_rotary_and_fa.py:120-182): rotate-half rotary embeddi
 of every k tile, `x0' = x0*cos0 - x1*sin0`, `x1' = x0*sin1 + x1*cos1`, evaluated in the tensors'
 16-bit type, then dense non-causal softmax attention over the rotated q and k.
 
-Here the two steps are two launches on the caller's stream: the rotary kernel writes rotated copies
-of q and k, the tcgen05 attention kernel reads them.  The rotation is not folded into the attention
-kernel: its Q and K tiles go from global memory to swizzled shared memory by TMA and from there
-straight into the tensor cores, so a rotation in between would be an extra shared-memory read-modify-
-write pass with a proxy fence per tile, repeated for every query tile and query head that re-reads a
-K tile, whereas the stand-alone pass touches every element once at HBM speed (7 % of the attention
-time at 4 x 8192 tokens).
+Here q is rotated inside the attention kernel: its tile is loaded once per CTA, and the softmax warps
+rotate it in place in shared memory before the first MMA.  k is rotated once per token by the rotary
+kernel (keys only) instead of once per tile inside the loop: every k tile is re-read by all the query
+tiles and heads that attend to it, so a rotation inside the loop would repeat the same arithmetic up to
+seqlen / 128 times; in a serving stack `fill_kv_cache(..., cos=, sin=)` does that one pass while it writes
+the cache, and no stand-alone pass is left.
 """
 from __future__ import annotations
 
 import torch
 
-from .apply_rotary_pos_emb import apply_rotary_pos_emb
+from .. import _lib
 from .flash_attention import flash_attention_v2
 
 
@@ -27,9 +26,27 @@ def fused_rotary_and_fa(q, k, v, cos, sin, causal=False, softmax_scale=None):
     assert k.shape == (batch, seqlen, nheads, d) and v.shape == k.shape
     assert q.dtype in (torch.float16, torch.bfloat16), "Only support fp16 and bf16"
     assert cos.shape == (batch, seqlen, d) and sin.shape == cos.shape
-    q3 = q.reshape(batch * seqlen, nheads, d)
-    k3 = k.reshape(batch * seqlen, nheads, d)
-    q_rot, k_rot = apply_rotary_pos_emb(q3, k3, cos.reshape(batch * seqlen, d), sin.reshape(batch * seqlen, d))
+    dev = _lib.require_cuda(q, k, v, cos, sin)
+    tokens = batch * seqlen
+    k3 = k.reshape(tokens, nheads, d)
+    cos2 = cos.to(q.dtype).reshape(tokens, d).contiguous()
+    sin2 = sin.to(q.dtype).reshape(tokens, d).contiguous()
+    k_rot = torch.empty_like(k3)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        # keys only: no query heads in this launch
+        rc = lib.dlb_apply_rotary(None, k3.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), None, k_rot.data_ptr(),
+                                  tokens, 0, nheads, d, 0, 0, k3.stride(0), k3.stride(1), 0, 0, k_rot.stride(0),
+                                  k_rot.stride(1), _lib.dtype_code(q), _lib.stream_ptr(dev))
+    _lib.check(rc, "fused_rotary_and_fa(keys)")
+    if d % 16 == 0:
+        return flash_attention_v2(q, k_rot.view(batch, seqlen, nheads, d), v, causal=causal,
+                                  softmax_scale=softmax_scale, q_cos=cos2, q_sin=sin2)
+    # head sizes the in-kernel rotation does not cover: rotate q with the stand-alone kernel as well
+    from .apply_rotary_pos_emb import apply_rotary_pos_emb
+
+    q3 = q.reshape(tokens, nheads, d)
+    q_rot, _ = apply_rotary_pos_emb(q3, k3, cos2, sin2)
     return flash_attention_v2(q_rot.view(batch, seqlen, nheads, d), k_rot.view(batch, seqlen, nheads, d), v,
                               causal=causal, softmax_scale=softmax_scale)
 

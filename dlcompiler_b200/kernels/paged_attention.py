@@ -34,6 +34,8 @@ def paged_attention_fwd(
     window_size: int = None,
     sm_scale: float = None,
     logit_softcapping: float = None,
+    q_cos: Tensor = None,
+    q_sin: Tensor = None,
 ):
     """Paged attention forward.
 
@@ -49,6 +51,8 @@ def paged_attention_fwd(
     multiples of 8 up to 128 (the kernels run at tile widths 64 and 128 and let the copy engine zero-fill
     the missing columns in shared memory; the cache is never copied or padded).  fp16/bf16, page size a
     power of two >= 16.
+    Extension (prefill branch): `q_cos` / `q_sin` ([total_q, D]) rotate q inside the kernel, see
+    `context_attention_fwd`; the cache must hold rotated keys (`fill_kv_cache(..., cos=, sin=)`).
     """
     dev = _lib.require_cuda(q, k, v, o, block_offsets, kv_seqlens)
     if window_size is None:
@@ -67,7 +71,8 @@ def paged_attention_fwd(
     assert Lk % 8 == 0 and Lv % 8 == 0 and Lk <= 128 and Lv <= 128, "head sizes: multiples of 8 up to 128"
     if not is_decoding:
         return _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens, max_seqlen,
-                              window_size, sm_scale, logit_softcapping, dev)
+                              window_size, sm_scale, logit_softcapping, dev, q_cos, q_sin)
+    assert q_cos is None and q_sin is None, "the decode branch takes q already rotated"
     assert k.dim() == 4 and v.dim() == 4 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert q.stride(-1) == 1 and o.stride(-1) == 1
     assert block_offsets.dim() == 2 and block_offsets.stride(1) == 1
@@ -80,7 +85,7 @@ def paged_attention_fwd(
     max_splits = (max_ctx + chunk - 1) // chunk
     if window_size > 0:
         # a window touches at most window + one tile of alignment slack
-        max_splits = min(max_splits, (window_size + 64 + chunk - 1) // chunk + 1)
+        max_splits = min(max_splits, (window_size + 1 + 64 + chunk - 1) // chunk + 1)
     lib = _lib.load()
     nfloats = lib.dlb_paged_decode_workspace_floats(batch, head, max(Lq, Lv), max_splits)
     partial = torch.empty(max(nfloats, 1), dtype=torch.float32, device=dev)
@@ -99,7 +104,7 @@ def paged_attention_fwd(
 
 
 def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens, max_seqlen, window_size, sm_scale,
-                   logit_softcapping, dev):
+                   logit_softcapping, dev, q_cos=None, q_sin=None):
     """Prefill branch of paged_attention_fwd (paged_attention.py:617-671): the tcgen05 prefill kernel with
     its K/V tiles fetched page by page."""
     assert q.dim() == 3 and o.shape[:-1] == q.shape[:-1] and q.stride(-1) == 1 and o.stride(-1) == 1
@@ -110,6 +115,9 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
     q_start = q_start_loc.to(device=dev, dtype=torch.int32).contiguous()
     q_len = q_seqlens.to(device=dev, dtype=torch.int32).contiguous()
     kv_len = kv_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+    from .prefill_attention import _rotary_tables
+
+    cos, sin = _rotary_tables(q, q_cos, q_sin)
     lib = _lib.load()
     status = _lib.status_word(dev)
     with torch.cuda.device(dev):
@@ -119,7 +127,7 @@ def _paged_prefill(q, k, v, o, block_offsets, q_start_loc, q_seqlens, kv_seqlens
             q.shape[1], k.shape[2], q.shape[2], v.shape[3], k.size(1), k.size(0), block_offsets.size(1),
             q.stride(0), q.stride(1), k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2),
             o.stride(0), o.stride(1), block_offsets.stride(0), int(block_offsets.dtype == torch.int64),
-            int(window_size), float(sm_scale), float(logit_softcapping), 1, _lib.dtype_code(q), status.data_ptr(),
-            _lib.stream_ptr(dev))
+            int(window_size), float(sm_scale), float(logit_softcapping), 1, _lib.ptr(cos), _lib.ptr(sin),
+            _lib.dtype_code(q), status.data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "paged_attention_fwd(prefill)")
     return o

@@ -202,6 +202,11 @@ int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, i
 /* Varlen causal GQA flash-attention prefill.  q [total, hq, head_dim], k [total, hkv, head_dim],
  * v [total, hkv, head_dim_v], out [total, hq, head_dim_v] (head sizes: multiples of 8 up to 128),
  * lse (optional, may be NULL) fp32 [hq, total] = m * sm_scale + log(sum) in natural log.
+ * q_cos / q_sin (optional, both or neither; [total, head_dim] in q's dtype, head_dim a multiple of 16): the
+ * rotate-half rotary embedding is applied to every Q tile inside the kernel, in the 16-bit type, bit-identical
+ * to dlb_apply_rotary; K must arrive rotated.  This is the query half of the reference's fused rotary +
+ * attention kernel (python/dlBLAS/dlblas/kernels/fused_rotary_and_fa.py:132-133); the key half (:177-178,
+ * every K tile rotated inside the loop) is done once per token by dlb_fill_kv_cache or dlb_apply_rotary.
  * Replaces context_attention_fwd, python/dlBLAS/dlblas/kernels/prefill_attention.py:155-181
  * (kernel :28-152); LSE convention of python/dlBLAS/dlblas/kernels/flash_attention.py:152-155. */
 int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* out, float* lse,
@@ -209,7 +214,8 @@ int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* 
                              int64_t total_tokens, int64_t max_seq_len, int64_t hq, int64_t hkv, int64_t head_dim,
                              int64_t head_dim_v, int64_t q_stride_t, int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h,
                              int64_t v_stride_t, int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h,
-                             float sm_scale, int causal, int dtype, int32_t* status, void* stream);
+                             float sm_scale, int causal, const void* q_cos, const void* q_sin, int dtype,
+                             int32_t* status, void* stream);
 
 /* Prefill over a paged cache that already holds the earlier tokens of each sequence (chunked prefill,
  * prefix reuse): q [total_q, hq, d] packed by sequence (q_start_loc, q_seq_len), caches
@@ -217,7 +223,8 @@ int dlb_flash_prefill_varlen(const void* q, const void* k, const void* v, void* 
  * history + q_seq_len; query i of a sequence sees keys 0 .. history + i (with window > 0 only the last
  * window + 1 of them; with softcap > 0 scores become softcap * tanh(score * sm_scale / softcap)).  Same
  * kernel as dlb_flash_prefill_varlen with K/V tiles fetched page by page; head_dim / head_dim_v as there
- * (the reference test runs 48 / 32 and 32 / 32 over 16-token pages).  Replaces the prefill branch of
+ * (the reference test runs 48 / 32 and 32 / 32 over 16-token pages); q_cos / q_sin as there, indexed by
+ * the rows of q.  Replaces the prefill branch of
  * paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:617-671 (kernel :311-489). */
 int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse,
                             const void* block_table, const int32_t* q_start_loc, const int32_t* q_seq_len,
@@ -227,7 +234,8 @@ int dlb_flash_prefill_paged(const void* q, const void* k_cache, const void* v_ca
                             int64_t k_stride_page, int64_t k_stride_slot, int64_t k_stride_head,
                             int64_t v_stride_page, int64_t v_stride_slot, int64_t v_stride_head, int64_t o_stride_t,
                             int64_t o_stride_h, int64_t bt_stride, int table_is_int64, int64_t window, float sm_scale,
-                            float softcap, int causal, int dtype, int32_t* status, void* stream);
+                            float softcap, int causal, const void* q_cos, const void* q_sin, int dtype,
+                            int32_t* status, void* stream);
 
 /* Number of fp32 elements of the split-KV workspace dlb_paged_decode needs (0 when max_splits == 1);
  * head_dim = the larger of the q/k and the v head size. */
@@ -268,7 +276,12 @@ int dlb_apply_rotary(const void* q, const void* k, const void* cos, const void* 
 /* Scatter the new tokens' key/value states into the paged caches [pages, page_size, heads, d]:
  * token i of sequence b lands in slot (history + i) % page_size of page
  * block_offsets[b, (history + i) / page_size], history = kv_seq_length[b] - q_seq_length[b].
- * Bit-exact copy.  Replaces python/dlBLAS/dlblas/kernels/fill_kv_cache.py:24-185. */
+ * Bit-exact copy.  Replaces python/dlBLAS/dlblas/kernels/fill_kv_cache.py:24-185.
+ * k_cos / k_sin (optional, both or neither; [total new tokens, dim_k] in the states' dtype, fp16/bf16, dim_k a
+ * multiple of 16, `dtype` = DLB_DTYPE_*): K is rotated (rotate-half rotary embedding, bit-identical to
+ * dlb_apply_rotary) while it is written, so the cache holds rotated keys and no pass over K precedes the
+ * attention; this takes the place of the per-tile K rotation of
+ * python/dlBLAS/dlblas/kernels/fused_rotary_and_fa.py:177-178.  `dtype` is ignored without them. */
 int dlb_fill_kv_cache(const void* k_states, const void* v_states, void* k_caches, void* v_caches,
                       const void* q_start_loc, const void* q_seq_length, const void* kv_seq_length,
                       const void* block_offsets, int64_t batch, int64_t max_q_seq_length, int64_t page_size,
@@ -276,7 +289,8 @@ int dlb_fill_kv_cache(const void* k_states, const void* v_states, void* k_caches
                       int64_t ks_stride_t, int64_t ks_stride_h, int64_t vs_stride_t, int64_t vs_stride_h,
                       int64_t kc_stride_page, int64_t kc_stride_slot, int64_t kc_stride_head, int64_t vc_stride_page,
                       int64_t vc_stride_slot, int64_t vc_stride_head, int64_t table_stride, int start_is_int64,
-                      int qlen_is_int64, int kvlen_is_int64, int table_is_int64, int elem_size, void* stream);
+                      int qlen_is_int64, int kvlen_is_int64, int table_is_int64, int elem_size, const void* k_cos,
+                      const void* k_sin, int dtype, void* stream);
 
 /* Capacity, in fp32 elements (32 MiB), of the fixed device array used by dlb_paged_decode_static. */
 #define DLB_DECODE_STATIC_FLOATS (8ll * 1024 * 1024)

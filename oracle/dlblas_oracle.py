@@ -369,7 +369,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_sc
     """Decode ground truth: `_naive_attention` of test_paged_attention.py:61-84 specialised to one
     query token per sequence, reading K/V through the block table.  q [B, Hq, D]; scores in
     fp32, softmax in fp32, P cast to the value dtype before P.V; optional sliding window
-    (keys in [ctx - window, ctx)) and tanh soft-cap as in paged_attention.py:175-200."""
+    (the query at position ctx - 1 sees keys ctx - 1 - window .. ctx - 1, paged_attention.py:163-165,192-194
+    with history_len = ctx - 1) and tanh soft-cap as in paged_attention.py:175-200."""
     B, hq, d = q.shape
     page = k_cache.shape[1]
     hkv = k_cache.shape[2]
@@ -385,7 +386,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_offsets, kv_seqlens, sm_sc
         pages = block_offsets[b, :npg].to(torch.int64)
         ks = k_cache[pages].reshape(npg * page, hkv, -1)[:n]
         vs = v_cache[pages].reshape(npg * page, hkv, -1)[:n]
-        lo = max(0, n - window_size) if (window_size is not None and window_size > 0) else 0
+        lo = max(0, n - 1 - window_size) if (window_size is not None and window_size > 0) else 0
         ks, vs = ks[lo:], vs[lo:]
         kf = ks.transpose(0, 1).repeat_interleave(group, 0).float()      # [hq, n, d]
         vf = vs.transpose(0, 1).repeat_interleave(group, 0)

@@ -200,3 +200,60 @@ def test_fused_rotary_and_fa(cuda_device, dtype):
     ref = oracle.context_attention(qr, kr, v.reshape(b * s, h, d), torch.arange(b) * s, torch.full((b,), s),
                                    causal=False)
     torch.testing.assert_close(out.reshape(b * s, h, d).float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("D,dtype", [(128, torch.bfloat16), (64, torch.float16), (96, torch.bfloat16), (32, torch.float16)])
+def test_rotary_inside_prefill_and_fill_equal_the_separate_kernels(cuda_device, D, dtype):
+    """Rotary folded into the neighbouring kernels: q rotated on its tile inside the attention kernel, k rotated
+    while fill_kv_cache writes it.  Both must give the bits of the stand-alone rotary kernel followed by the plain
+    kernels: the rotated cache is compared directly, the attention output through both routes."""
+    from dlcompiler_b200 import context_attention_fwd
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(D)
+    q_lens, hist = torch.tensor([70, 1, 200, 129]), torch.tensor([0, 35, 16, 100])
+    kv_lens = q_lens + hist
+    hq, hkv, page = 8, 2, 16
+    total = int(q_lens.sum())
+    q = torch.randn(total, hq, D, generator=g).to(dtype).to(dev)
+    k_new = torch.randn(total, hkv, D, generator=g).to(dtype).to(dev)
+    v_new = torch.randn(total, hkv, D, generator=g).to(dtype).to(dev)
+    cos = torch.rand(total, D, generator=g).to(dtype).to(dev)
+    sin = torch.rand(total, D, generator=g).to(dtype).to(dev)
+    pages_per_seq = (kv_lens + page - 1) // page
+    n_pages = int(pages_per_seq.sum())
+    table = torch.zeros(4, int(pages_per_seq.max()), dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g)
+    at = 0
+    for b, n in enumerate(pages_per_seq.tolist()):
+        table[b, :n] = perm[at:at + n].to(torch.int32)
+        at += n
+    base_k = torch.randn(n_pages, page, hkv, D, generator=g).to(dtype).to(dev)     # history keys (already rotated)
+    base_v = torch.randn(n_pages, page, hkv, D, generator=g).to(dtype).to(dev)
+    start = (torch.cumsum(q_lens, 0) - q_lens).to(dev)
+    ql, kl, tb = q_lens.to(dev), kv_lens.to(dev), table.to(dev)
+
+    # route A: stand-alone rotary, plain fill, plain paged prefill
+    q_rot, k_rot = apply_rotary_pos_emb(q, k_new, cos, sin)
+    kc_a, vc_a = base_k.clone(), base_v.clone()
+    fill_kv_cache(k_rot, v_new, kc_a, vc_a, start, ql, kl, int(q_lens.max()), tb)
+    o_a = torch.full_like(q, float("nan"))
+    paged_attention_fwd(q_rot, kc_a, vc_a, o_a, tb, start, ql, kl, int(q_lens.max()))
+    # route B: k rotated by the fill, q rotated inside the attention kernel
+    kc_b, vc_b = base_k.clone(), base_v.clone()
+    fill_kv_cache(k_new, v_new, kc_b, vc_b, start, ql, kl, int(q_lens.max()), tb, cos=cos, sin=sin)
+    assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)
+    o_b = torch.full_like(q, float("nan"))
+    paged_attention_fwd(q, kc_b, vc_b, o_b, tb, start, ql, kl, int(q_lens.max()), q_cos=cos, q_sin=sin)
+    assert torch.isfinite(o_a.float()).all()
+    assert torch.equal(o_a, o_b)
+    # the contiguous entry point, same comparison (no history)
+    o_c = torch.empty_like(q)
+    context_attention_fwd(q_rot, k_rot, v_new, o_c, start.int(), ql.int(), int(q_lens.max()))
+    o_d = torch.empty_like(q)
+    context_attention_fwd(q, k_rot, v_new, o_d, start.int(), ql.int(), int(q_lens.max()), q_cos=cos, q_sin=sin)
+    assert torch.equal(o_c, o_d)
+    # and against the oracle, end to end
+    rq, rk = oracle.apply_rotary_pos_emb(q.cpu(), k_new.cpu(), cos.cpu(), sin.cpu())
+    ref = oracle.context_attention(rq, rk, v_new.cpu(), start.cpu(), q_lens)
+    torch.testing.assert_close(o_d.cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
