@@ -78,6 +78,62 @@ __device__ __forceinline__ float sigmoid_spec(float x) {
   return y;
 }
 
+// The same sequence on two scores at once with the packed fp32 instructions of sm_100 (fma.rn.f32x2,
+// add.rn.f32x2): every lane of a packed operation rounds exactly like its scalar form, so the scores are
+// bit-identical to sigmoid_spec, and the 16 FMAs / adds of the sequence cost half the issue slots.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void sigmoid_spec2(float x0, float x1, float& y0, float& y1) {
+  constexpr float kMagic = 12582912.0f;
+  constexpr float kNegLog2eHi = -1.44269502162933349609e+00f;
+  constexpr float kNegLog2eLo = -1.92596303350001107901e-08f;
+  const float c0 = fminf(fmaxf(x0, -87.0f), 86.0f), c1 = fminf(fmaxf(x1, -87.0f), 86.0f);
+  const uint64_t xc = f2_pack(c0, c1);
+  const uint64_t hi2 = f2_pack(kNegLog2eHi, kNegLog2eHi);
+  const uint64_t z = f2_fma(xc, hi2, f2_pack(kMagic, kMagic));
+  const uint64_t n = f2_add(z, f2_pack(-kMagic, -kMagic));                      // z - M, exact
+  float n0, n1;
+  f2_unpack(n, n0, n1);
+  uint64_t r = f2_fma(xc, hi2, f2_pack(-n0, -n1));
+  r = f2_fma(xc, f2_pack(kNegLog2eLo, kNegLog2eLo), r);
+  uint64_t p = f2_pack(1.32874317932873964310e-03f, 1.32874317932873964310e-03f);
+  p = f2_fma(p, r, f2_pack(9.67150740325450897217e-03f, 9.67150740325450897217e-03f));
+  p = f2_fma(p, r, f2_pack(5.55065572261810302734e-02f, 5.55065572261810302734e-02f));
+  p = f2_fma(p, r, f2_pack(2.40222424268722534180e-01f, 2.40222424268722534180e-01f));
+  p = f2_fma(p, r, f2_pack(6.93147063255310058594e-01f, 6.93147063255310058594e-01f));
+  p = f2_fma(p, r, f2_pack(1.0f, 1.0f));
+  float p0, p1, z0, z1;
+  f2_unpack(p, p0, p1);
+  f2_unpack(z, z0, z1);
+  const float e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(z0) << 23));
+  const float e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(z1) << 23));
+  const uint64_t one = f2_pack(1.0f, 1.0f);
+  const uint64_t d = f2_add(one, f2_pack(e0, e1));
+  float d0, d1;
+  f2_unpack(d, d0, d1);
+  uint64_t y = f2_pack(__int_as_float(0x7EF311C7 - __float_as_int(d0)), __int_as_float(0x7EF311C7 - __float_as_int(d1)));
+  const uint64_t nd = f2_pack(-d0, -d1);
+#pragma unroll
+  for (int it = 0; it < 3; ++it) y = f2_fma(y, f2_fma(nd, y, one), y);
+  f2_unpack(y, y0, y1);
+}
+
 // Order-preserving map from fp32 to unsigned: a > b  <=>  key(a) > key(b); -inf maps to
 // 0x007fffff, which leaves 0 free as "slot retired".
 __device__ __forceinline__ uint32_t score_key(float v) {
@@ -187,8 +243,18 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
 
   // ---- scoring ----
   if (p.scoring == DLB_SCORE_SIGMOID) {
+    if constexpr (VPL >= 2) {
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) s[v] = valid(v) ? sigmoid_spec(s[v]) : -CUDART_INF_F;
+      for (int v = 0; v < VPL; v += 2) {
+        float y0, y1;
+        sigmoid_spec2(s[v], s[v + 1], y0, y1);
+        s[v] = valid(v) ? y0 : -CUDART_INF_F;
+        s[v + 1] = valid(v + 1) ? y1 : -CUDART_INF_F;
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) s[v] = valid(v) ? sigmoid_spec(s[v]) : -CUDART_INF_F;
+    }
   } else {
     // softmax is monotone in the logit: without a bias the selection runs on the raw logits,
     // which keeps the chosen ids independent of how exp() rounds
