@@ -294,6 +294,41 @@ __global__ void __launch_bounds__(256) fill_kv_cache_kernel(const FillParams p) 
     }
   };
   const int stride = blockDim.x * gridDim.z;
+  if (stride % per_tok == 0) {
+    // A thread keeps its (head, unit) column and walks the slots, four copies in flight: the index
+    // arithmetic (two divisions per unit in the general walk below) is done once per thread.
+    const int idx0 = threadIdx.x + blockIdx.z * blockDim.x;
+    const int s0 = idx0 / per_tok, ds = stride / per_tok;
+    int r = idx0 - s0 * per_tok;
+    const uint8_t* sbase;
+    uint8_t* dbase;
+    int64_t s_tok, d_slot;     // bytes per token of the states / per slot of the cache
+    if (r < p.heads * k_units) {
+      const int h = r / k_units, u = r - h * k_units;
+      sbase = reinterpret_cast<const uint8_t*>(p.ks) + ((int64_t)h * p.ks_sh) * es + (int64_t)u * UNIT;
+      dbase = reinterpret_cast<uint8_t*>(p.kc) + (page * p.kc_sp + (int64_t)h * p.kc_sh) * es + (int64_t)u * UNIT;
+      s_tok = p.ks_st * es;
+      d_slot = p.kc_ss * es;
+    } else {
+      r -= p.heads * k_units;
+      const int h = r / v_units, u = r - h * v_units;
+      sbase = reinterpret_cast<const uint8_t*>(p.vs) + ((int64_t)h * p.vs_sh) * es + (int64_t)u * UNIT;
+      dbase = reinterpret_cast<uint8_t*>(p.vc) + (page * p.vc_sp + (int64_t)h * p.vc_sh) * es + (int64_t)u * UNIT;
+      s_tok = p.vs_st * es;
+      d_slot = p.vc_ss * es;
+    }
+    const int nslots = slot_hi - slot_lo;
+    for (int sidx = s0; sidx < nslots; sidx += 4 * ds) {
+      U val[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (sidx + j * ds < nslots) val[j] = *reinterpret_cast<const U*>(sbase + (tok0 + sidx + j * ds) * s_tok);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (sidx + j * ds < nslots) *reinterpret_cast<U*>(dbase + (int64_t)(slot_lo + sidx + j * ds) * d_slot) = val[j];
+    }
+    return;
+  }
   for (int idx = threadIdx.x + blockIdx.z * blockDim.x; idx < total; idx += 4 * stride) {
     const U* src[4];
     U* dst[4];

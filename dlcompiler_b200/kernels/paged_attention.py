@@ -10,7 +10,11 @@ from .. import _lib
 
 logger = logging.getLogger("dlblas")
 
-_TARGET_CTAS = 148 * 2 * 16  # split work items aimed at per launch (16 waves of 2 CTAs per SM)
+# Split work items aimed at per launch: 4 waves of 2 CTAs per SM.  A split pays a fixed price (barrier set-up,
+# Q fragments, the cross-warp merge and the partial's round trip through the merge kernel), so splits should be
+# as long as load balance allows: at 16 sequences of 1k-32k tokens, 512-token splits (16 waves) reach 4.95 TB/s,
+# 2048-token splits (4 waves) 5.92 TB/s and 4096-token splits 6.04 TB/s.
+_TARGET_CTAS = 148 * 2 * 4
 
 
 def _pick_chunk(batch: int, kv_heads: int, max_ctx: int, page_size: int) -> int:
