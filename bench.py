@@ -1,7 +1,7 @@
 """Benchmark of the dlBLAS hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ops all|none]
-    python bench.py --profile-case {silu,gating,moe,prefill,decode,rotary} [--steps N]
+    python bench.py --profile-case {silu,gating,moe,prefill,prefill_c4,decode,rotary,rotary_c4} [--steps N]
 
 Headline (one JSON line on stdout): fused_moe on the Mixtral-like configuration
 (T=4096, H=4096, I=14336, E=8, top_k=2, bf16) in TFLOP/s, whole job.  N > 1 runs the
@@ -42,10 +42,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC = {
     "grouped_gemm": {"gate_up_silu": 2968.7e6, "down_scatter": 1468.0e6, "per_step": 4436.7e6},
     "silu_and_mul": 229.0e6,
-    "flash_prefill": None,
+    "flash_prefill": 635.1e6,
     "paged_decode": 4430.5e6,
     "rms_norm": 480.8e6,
-    "apply_rotary_pos_emb": None,
+    "apply_rotary_pos_emb": 630.4e6,
     "fill_kv_cache": 221.9e6,
 }
 
@@ -536,6 +536,30 @@ MOE_WORKLOAD = ("C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16 (moe_align 
                 "down GEMM x weight -> combine)")
 
 
+def bind_to_gpu_cpus(device_index):
+    """Runs this rank on the CPU cores next to its GPU (the affinity NVML reports for the device), so that the
+    pinned host buffers of the end-to-end leg are first touched, and therefore placed, on the GPU's own NUMA
+    node.  Host-side placement only; nothing on the GPU is changed.  Silently skipped where NVML or the
+    affinity call is unavailable."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:  # noqa: BLE001 - older bindings want bytes
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception as exc:  # noqa: BLE001 - placement is an optimisation, never a requirement
+        print(f"[bench] CPU affinity not set ({exc!r})", file=sys.stderr)
+
+
 # --------------------------------------------------------------------------- headline: fused_moe
 def run_ours(args):
     import dlcompiler_b200 as dl
@@ -556,6 +580,8 @@ def run_ours(args):
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
+
+        bind_to_gpu_cpus(local_rank)
 
         os.environ.setdefault("NCCL_DEBUG", "WARN")     # stdout is redirected anyway; a caller's setting stands
         dist = dist_mod
@@ -759,16 +785,18 @@ def run_profile_case(args):
         hs, w1, w2 = d["hidden_states"].to(dev), d["w1"].to(dev), d["w2"].to(dev)
         fn = lambda: dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k)
         what = "fused_moe T=2048 H=4096 I=7168 E=4 top_k=2 bf16"
-    elif op == "prefill":
-        wl = W.PrefillWorkload(batch=2, seq_len=4096)                  # q/k/v/o 168 MB > L2
+    elif op in ("prefill", "prefill_c4"):
+        # q/k/v/o 168 MB > L2; prefill_c4 is the benchmark shape itself (670 MB), for one-pass DRAM counters
+        wl = W.PrefillWorkload(batch=2, seq_len=4096) if op == "prefill" else W.PrefillWorkload()
         d = wl.make()
         q, k, v = d["q"].to(dev), d["k"].to(dev), d["v"].to(dev)
         o = torch.empty_like(q)
         st, ln = d["b_start_loc"].to(dev), d["b_seq_len"].to(dev)
         fn = lambda: dl.context_attention_fwd(q, k, v, o, st, ln, d["max_input_len"])
-        what = "prefill B=2 S=4096 Hq=32 Hkv=8 D=128 bf16"
-    elif op == "rotary":
-        tok, hq, hk, dd = 8192, 32, 8, 128                             # q + k 84 MB in, 84 MB out, cos/sin 4 MB
+        what = f"prefill B={wl.batch} S={wl.seq_len} Hq=32 Hkv=8 D=128 bf16"
+    elif op in ("rotary", "rotary_c4"):
+        # q + k 84 MB in, 84 MB out, cos/sin 4 MB; rotary_c4: the benchmark's 32768 tokens (688 MB per pass)
+        tok, hq, hk, dd = (8192 if op == "rotary" else 32768), 32, 8, 128
         g = torch.Generator(device=dev)
         g.manual_seed(7)
         q = torch.randn(tok, hq, dd, generator=g, device=dev).to(torch.bfloat16)
@@ -776,7 +804,7 @@ def run_profile_case(args):
         cos = torch.rand(tok, dd, generator=g, device=dev).to(torch.bfloat16)
         sin = torch.rand(tok, dd, generator=g, device=dev).to(torch.bfloat16)
         fn = lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k)
-        what = "rotary in place q [8192, 32, 128] k [8192, 8, 128] bf16"
+        what = f"rotary in place q [{tok}, 32, 128] k [{tok}, 8, 128] bf16"
     else:
         wl = W.DecodeWorkload(batch=16)                                # ~1.1 GB of KV cache
         d = wl.make(device=dev)
@@ -823,7 +851,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=4096)
     ap.add_argument("--warm-seconds", type=float, default=1.0,
                     help="N = 1: keep warming up until this much wall time has passed (device under load)")
-    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "decode", "rotary"],
+    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "prefill_c4", "decode", "rotary", "rotary_c4"],
                     help="run one op --steps times (at most 8) on a profiler-sized case and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -140,12 +140,14 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < top_k; ++k) {
+      // the row is fetched whether or not its slot counts (every slot has a row in the buffer), so that the
+      // row's load does not wait for the id's; a slot that does not count is dropped after the fact
+      uint4 x = __ldcs(reinterpret_cast<const uint4*>(partial + (t * top_k + k) * (int64_t)hidden) + v);
       if (topk_ids != nullptr) {
-        const int64_t id = ids_are_int64 ? reinterpret_cast<const int64_t*>(topk_ids)[t * top_k + k]
-                                         : (int64_t)reinterpret_cast<const int32_t*>(topk_ids)[t * top_k + k];
-        if (id < id_lo || id >= id_hi) continue;
+        const int64_t id = ids_are_int64 ? __ldg(reinterpret_cast<const int64_t*>(topk_ids) + t * top_k + k)
+                                         : (int64_t)__ldg(reinterpret_cast<const int32_t*>(topk_ids) + t * top_k + k);
+        if (id < id_lo || id >= id_hi) x = make_uint4(0u, 0u, 0u, 0u);
       }
-      const uint4 x = __ldcs(reinterpret_cast<const uint4*>(partial + (t * top_k + k) * (int64_t)hidden) + v);
       const T2* x2 = reinterpret_cast<const T2*>(&x);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
