@@ -86,7 +86,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             print(log, file=sys.stderr)
     newest = max(os.path.getmtime(o) for o in objs)
     if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < newest:
-        cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fPIC"]
+        cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fPIC", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

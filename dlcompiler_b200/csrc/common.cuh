@@ -12,6 +12,20 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <nvtx3/nvToolsExt.h>
+
+// NVTX range around the host side of an entry point (argument checks, tensor-map encoding, launches): a
+// timeline tool shows each library call under its own name; without a tool attached the calls cost a
+// pointer test each.
+namespace dlb {
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+}  // namespace dlb
+#define DLB_NVTX(name) ::dlb::NvtxRange dlb_nvtx_range_(name)
 
 // ----------------------------------------------------------------------------
 // Status codes returned by every extern "C" entry point.

@@ -410,6 +410,7 @@ static int fill_ptrs(PeerPtrs* out, void* const* in, int world, const char* what
 
 extern "C" int dlb_ep_barrier(void* const* flags_sym, int slot, int rank, int world, int epoch, int32_t* status,
                               void* stream) {
+  DLB_NVTX("dlb_ep_barrier");
   using namespace dlb;
   DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
                 "ep_barrier: rank %d of %d", rank, world);
@@ -426,6 +427,7 @@ extern "C" int dlb_ep_route(const void* topk_ids, int ids_are_int64, int64_t num
                             void* const* flags_sym, int32_t* dest_pos, int32_t* block_start,
                             int32_t* num_post_padded, int32_t* row_map, int rank, int world, int experts,
                             int64_t cap, int epoch, int32_t* status, void* stream) {
+  DLB_NVTX("dlb_ep_route");
   using namespace dlb;
   DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
                 "ep_route: rank %d of %d", rank, world);
@@ -471,6 +473,7 @@ extern "C" int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_
                            const int32_t* dest_pos, void* const* rows_sym, void* const* w_sym,
                            void* const* meta_sym, void* const* flags_sym, int32_t* done_counter, int64_t numel,
                            int top_k, int rank, int world, int experts, int64_t cap, int epoch, void* stream) {
+  DLB_NVTX("dlb_ep_send");
   using namespace dlb;
   DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && rank >= 0 && rank < world, DLB_ERR_BAD_ARG,
                 "ep_send: rank %d of %d", rank, world);
@@ -517,6 +520,7 @@ extern "C" int dlb_ep_send(const void* hidden, int64_t hidden_row_stride, int64_
 extern "C" int dlb_ep_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
                               int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world, int epoch,
                               const int32_t* dest_pos, int32_t* status, void* stream) {
+  DLB_NVTX("dlb_ep_combine");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0, DLB_ERR_BAD_ARG, "ep_combine: bad sizes");
   DLB_CHECK_ARG(world >= 1 && world <= ep::MAX_RANKS && wait_flags != nullptr, DLB_ERR_BAD_ARG,
@@ -550,6 +554,7 @@ extern "C" int dlb_ep_combine_pull(void* const* y_sym, int64_t y_row_stride, con
                                    const int32_t* dest_pos, void* out, int64_t tokens, int top_k, int64_t hidden,
                                    int64_t out_row_stride, int dtype, const int32_t* wait_flags, int world,
                                    int experts, int64_t cap, int epoch, int32_t* status, void* stream) {
+  DLB_NVTX("dlb_ep_combine_pull");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0 && tokens * top_k < (1LL << 24), DLB_ERR_BAD_ARG,
                 "ep_combine_pull: bad sizes");

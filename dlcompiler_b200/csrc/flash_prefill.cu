@@ -628,6 +628,7 @@ extern "C" int dlb_flash_prefill_varlen(const void* q, const void* k, const void
                                         int64_t v_stride_h, int64_t o_stride_t, int64_t o_stride_h, float sm_scale,
                                         int causal, const void* q_cos, const void* q_sin, int dtype, int32_t* status,
                                         void* stream) {
+  DLB_NVTX("dlb_flash_prefill_varlen");
   using namespace dlb;
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
@@ -724,6 +725,7 @@ extern "C" int dlb_flash_prefill_paged(const void* q, const void* k_cache, const
                                        int64_t o_stride_h, int64_t bt_stride, int table_is_int64, int64_t window,
                                        float sm_scale, float softcap, int causal, const void* q_cos,
                                        const void* q_sin, int dtype, int32_t* status, void* stream) {
+  DLB_NVTX("dlb_flash_prefill_paged");
   using namespace dlb;
   using namespace dlb::fp;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,

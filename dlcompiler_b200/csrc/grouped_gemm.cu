@@ -517,6 +517,7 @@ extern "C" int dlb_moe_grouped_gemm(const void* a, int64_t a_rows, int64_t a_row
                                     const int32_t* sorted_token_ids, const int32_t* block_start,
                                     const float* topk_weights, int64_t numel, int flags, int dtype,
                                     int32_t* status, void* stream) {
+  DLB_NVTX("dlb_moe_grouped_gemm");
   DLB_CHECK_ARG((flags & dlb::gg::FLAG_PEER) == 0, DLB_ERR_BAD_ARG,
                 "grouped_gemm: peer scatter is only available through dlb_moe_grouped_gemm_sync");
   return dlb::grouped_gemm_impl(a, a_rows, a_row_stride, b, num_experts, rows_per_expert, k, b_row_stride, out,
@@ -536,6 +537,7 @@ extern "C" int dlb_moe_grouped_gemm_sync(const void* a, int64_t a_rows, int64_t 
                                          const int32_t* wait_flags, void* const* signal_flags,
                                          int32_t* done_counter, int sync_world, int sync_epoch, int32_t* status,
                                          void* stream) {
+  DLB_NVTX("dlb_moe_grouped_gemm_sync");
   using namespace dlb::gg;
   void* o = out;
   if ((flags & FLAG_PEER) && o == nullptr && peer_out != nullptr && num_peers > 0) o = peer_out[0];

@@ -199,6 +199,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS) moe_start_end_kernel(const IdT*
 
 extern "C" int dlb_moe_start_end(const void* topk_ids, int ids_are_int64, int64_t numel, int num_experts,
                                  void* exp_start, void* exp_end, int out_is_int64, void* stream) {
+  DLB_NVTX("dlb_moe_start_end");
   using namespace dlb;
   DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 30), DLB_ERR_TOO_LARGE, "moe_start_end: numel=%lld out of range",
                 (long long)numel);
@@ -228,6 +229,7 @@ extern "C" int dlb_moe_align_block_size(const void* topk_ids, int ids_are_int64,
                                         int block, int32_t* sorted_token_ids, int64_t sorted_capacity,
                                         int32_t* expert_ids, int64_t expert_ids_capacity,
                                         int32_t* num_tokens_post_padded, int32_t* block_start, void* stream) {
+  DLB_NVTX("dlb_moe_align_block_size");
   using namespace dlb;
   DLB_CHECK_ARG(numel >= 0 && numel < (1LL << 30), DLB_ERR_TOO_LARGE, "moe_align: numel=%lld out of range",
                 (long long)numel);
@@ -268,6 +270,7 @@ extern "C" int dlb_moe_permute_rows(const void* src, void* dst, const int32_t* s
                                     const int32_t* num_tokens_post_padded, int64_t numel, int top_k,
                                     int64_t hidden, int64_t src_row_stride, int64_t sorted_capacity,
                                     int elem_size, void* stream) {
+  DLB_NVTX("dlb_moe_permute_rows");
   using namespace dlb;
   DLB_CHECK_ARG(elem_size == 2 || elem_size == 4, DLB_ERR_UNSUPPORTED, "moe_permute: element size %d", elem_size);
   DLB_CHECK_ARG(top_k >= 1 && numel >= 0 && hidden >= 0, DLB_ERR_BAD_ARG, "moe_permute: bad sizes");
@@ -290,6 +293,7 @@ extern "C" int dlb_moe_permute_rows(const void* src, void* dst, const int32_t* s
 extern "C" int dlb_moe_combine(const void* partial, void* out, int64_t tokens, int top_k, int64_t hidden,
                                int64_t out_row_stride, int dtype, const void* topk_ids, int ids_are_int64,
                                int64_t id_lo, int64_t id_hi, void* stream) {
+  DLB_NVTX("dlb_moe_combine");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && top_k >= 1 && hidden >= 0, DLB_ERR_BAD_ARG, "moe_combine: bad sizes");
   if (tokens == 0 || hidden == 0) return DLB_OK;

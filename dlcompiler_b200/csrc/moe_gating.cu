@@ -637,6 +637,7 @@ extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, i
                                        int64_t tokens, int experts, int64_t logits_row_stride, int n_group,
                                        int topk_group, int top_k, int scoring, int renormalize, float scale,
                                        void* stream) {
+  DLB_NVTX("dlb_grouped_topk_gating");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0, DLB_ERR_BAD_ARG, "gating: negative token count");
   DLB_CHECK_ARG(experts >= 1 && experts <= 512, DLB_ERR_UNSUPPORTED, "gating: experts=%d not in [1, 512]", experts);
@@ -675,6 +676,7 @@ extern "C" int dlb_grouped_topk_gating(const float* logits, const float* bias, i
 
 extern "C" int dlb_gshard_gate(const float* logits, int64_t tokens, int experts, int top_k, float* gates,
                                int32_t* ids /* [tokens, top_k] */, float* scratch_weights, void* stream) {
+  DLB_NVTX("dlb_gshard_gate");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && experts >= 1 && experts <= 512 && top_k >= 1 && top_k <= 32 && top_k <= experts,
                 DLB_ERR_BAD_ARG, "gshard_gate: bad sizes");
@@ -695,6 +697,7 @@ extern "C" int dlb_gshard_assign(const float* gates, const int32_t* ids_choice_m
                                  int64_t capacity, float* colsum_scratch, int64_t colsum_blocks, int32_t* loc,
                                  float* me, float* ce, float* l_aux, int32_t* ec_idx, float* weights,
                                  int64_t* expert_select_token_idx, void* stream) {
+  DLB_NVTX("dlb_gshard_assign");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 1 && experts >= 1 && experts <= 1024 && top_k >= 1 && capacity >= 1 && colsum_blocks >= 1,
                 DLB_ERR_BAD_ARG, "gshard_assign: bad sizes");
@@ -735,6 +738,7 @@ extern "C" int dlb_gshard_assign(const float* gates, const int32_t* ids_choice_m
 
 extern "C" int dlb_gshard_gate_bwd(const float* gates, const float* ce, const float* grad_l_aux, float* grad_logits,
                                    int64_t tokens, int experts, void* stream) {
+  DLB_NVTX("dlb_gshard_gate_bwd");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && experts >= 1, DLB_ERR_BAD_ARG, "gshard_gate_bwd: bad sizes");
   if (tokens == 0) return DLB_OK;
@@ -751,6 +755,7 @@ extern "C" int dlb_gshard_gate_bwd_weights(const float* gates, const float* ce, 
                                            const int32_t* ids_choice_major, const int32_t* loc,
                                            const float* grad_weights, float* grad_logits, int64_t tokens, int experts,
                                            int top_k, int64_t capacity, void* stream) {
+  DLB_NVTX("dlb_gshard_gate_bwd_weights");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && experts >= 1 && top_k >= 1 && top_k <= 32 && capacity >= 1, DLB_ERR_BAD_ARG,
                 "gshard_gate_bwd_weights: bad sizes");

@@ -406,6 +406,7 @@ __global__ void __launch_bounds__(256) fill_kv_cache_rot_kernel(const FillParams
 extern "C" int dlb_rms_norm(const void* x, const void* weight, const void* residual, void* out, void* out_residual,
                             int64_t rows, int64_t n, int64_t x_row_stride, int64_t residual_row_stride,
                             int64_t out_row_stride, float eps, int weight_after_cast, int dtype, void* stream) {
+  DLB_NVTX("dlb_rms_norm");
   using namespace dlb;
   DLB_CHECK_ARG(rows >= 0 && n >= 1 && n < (1LL << 30), DLB_ERR_BAD_ARG, "rms_norm: bad sizes");
   if (rows == 0) return DLB_OK;
@@ -435,6 +436,7 @@ extern "C" int dlb_apply_rotary(const void* q, const void* k, const void* cos, c
                                 int64_t q_stride_h, int64_t k_stride_t, int64_t k_stride_h, int64_t qo_stride_t,
                                 int64_t qo_stride_h, int64_t ko_stride_t, int64_t ko_stride_h, int dtype,
                                 void* stream) {
+  DLB_NVTX("dlb_apply_rotary");
   using namespace dlb;
   DLB_CHECK_ARG(tokens >= 0 && hq >= 0 && hk >= 0 && dim >= 2 && dim % 2 == 0, DLB_ERR_BAD_ARG, "rotary: bad sizes");
   if (tokens == 0 || hq + hk == 0) return DLB_OK;
@@ -480,6 +482,7 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
                                  int64_t vc_stride_head, int64_t table_stride, int start_is_int64, int qlen_is_int64,
                                  int kvlen_is_int64, int table_is_int64, int elem_size, const void* k_cos,
                                  const void* k_sin, int dtype, void* stream) {
+  DLB_NVTX("dlb_fill_kv_cache");
   using namespace dlb;
   DLB_CHECK_ARG(batch >= 0 && max_q_seq_length >= 0 && page_size >= 1 && heads >= 1 && dim_k >= 1 && dim_v >= 0,
                 DLB_ERR_BAD_ARG, "fill_kv_cache: bad sizes");

@@ -570,6 +570,7 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
                                 int64_t v_stride_head, int64_t bt_stride, int table_is_int64, int lens_is_int64,
                                 int64_t chunk, int64_t max_splits, int64_t window, float sm_scale, float softcap,
                                 int dtype, int32_t* status, void* stream) {
+  DLB_NVTX("dlb_paged_decode");
   using namespace dlb;
   DLB_CHECK_ARG(dtype == DLB_DTYPE_BF16 || dtype == DLB_DTYPE_F16, DLB_ERR_UNSUPPORTED,
                 "paged_decode: dtype %d (need fp16 or bf16)", dtype);
@@ -717,6 +718,7 @@ extern "C" int dlb_paged_decode_static(const void* q, const void* k_cache, const
                                        int table_is_int64, int lens_is_int64, int64_t chunk, int64_t max_splits,
                                        int64_t window, float sm_scale, float softcap, int dtype, int32_t* status,
                                        void* stream) {
+  DLB_NVTX("dlb_paged_decode_static");
   using namespace dlb;
   DLB_CHECK_ARG(batch >= 0 && hq >= 1 && head_dim >= 1 && max_splits >= 1, DLB_ERR_BAD_ARG,
                 "paged_decode_static: bad sizes");

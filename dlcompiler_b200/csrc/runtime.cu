@@ -3,6 +3,7 @@
 // The library never allocates or frees device memory.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <atomic>
 #include <mutex>
@@ -20,7 +21,17 @@ void set_last_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static std::atomic<uint64_t> g_wait_budget_ns{DLB_WAIT_BUDGET_NS};
+// DLBLAS_B200_WAIT_BUDGET_MS in the environment sets the limit at load time (1..60000 ms); dlb_set_wait_budget_ms
+// changes it later
+static uint64_t initial_wait_budget_ns() {
+  const char* v = getenv("DLBLAS_B200_WAIT_BUDGET_MS");
+  if (v != nullptr) {
+    const long ms = strtol(v, nullptr, 10);
+    if (ms >= 1 && ms <= 60000) return (uint64_t)ms * 1000000ull;
+  }
+  return DLB_WAIT_BUDGET_NS;
+}
+static std::atomic<uint64_t> g_wait_budget_ns{initial_wait_budget_ns()};
 
 uint64_t wait_budget_ns() { return g_wait_budget_ns.load(std::memory_order_relaxed); }
 

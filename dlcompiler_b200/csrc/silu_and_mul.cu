@@ -119,6 +119,7 @@ static int launch_silu(const void* x, void* out, int64_t rows, int n, int64_t xs
 extern "C" int dlb_silu_and_mul(const void* gate_up, void* out, int64_t rows, int64_t n,
                                 int64_t gate_up_row_stride, int64_t out_row_stride, int dtype,
                                 void* stream) {
+  DLB_NVTX("dlb_silu_and_mul");
   using namespace dlb;
   DLB_CHECK_ARG(rows >= 0 && n >= 0, DLB_ERR_BAD_ARG, "silu_and_mul: negative size");
   DLB_CHECK_ARG(n <= 0x3fffffff, DLB_ERR_TOO_LARGE, "silu_and_mul: N=%lld too large", (long long)n);

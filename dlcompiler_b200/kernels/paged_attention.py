@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import logging
+import os
 
 import torch
 from torch import Tensor
@@ -18,7 +19,12 @@ _TARGET_CTAS = 148 * 2 * 4
 
 
 def _pick_chunk(batch: int, kv_heads: int, max_ctx: int, page_size: int) -> int:
-    """Tokens per KV split: a power of two, at least one 64-key tile and one page."""
+    """Tokens per KV split: a power of two, at least one 64-key tile and one page.
+    DLBLAS_B200_DECODE_CHUNK in the environment forces the value (rounded up to a legal one)."""
+    forced = os.environ.get("DLBLAS_B200_DECODE_CHUNK")
+    if forced:
+        chunk = 1 << max(int(forced) - 1, 1).bit_length()
+        return max(64, page_size, chunk)
     want = max(1, batch * kv_heads * max_ctx // _TARGET_CTAS)
     chunk = 1 << (want.bit_length() - 1)
     lo = max(256, page_size)
