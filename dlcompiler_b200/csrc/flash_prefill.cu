@@ -389,29 +389,39 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     bool ok = true;
     if (p.rot_cos != nullptr) {
       // rotate this thread's query row in place in the swizzled Q tile (16-byte chunk c of row r sits at chunk
-      // position c ^ (r & 7) of its 128-byte line), then hand the tile to the MMA thread
+      // position c ^ (r & 7) of its 128-byte line), then hand the tile to the MMA thread.  The row's cos / sin
+      // values are fetched BEFORE the wait for the Q tile, so the two latencies overlap.
+      const bool row_live = q_pos < seq_len;
+      const int half = p.rot_dim >> 1, hv = half >> 3;          // hv <= 8 (head size <= 128)
+      const T* cs = reinterpret_cast<const T*>(p.rot_cos) + (int64_t)(start + (row_live ? q_pos : 0)) * p.rot_dim;
+      const T* sn = reinterpret_cast<const T*>(p.rot_sin) + (int64_t)(start + (row_live ? q_pos : 0)) * p.rot_dim;
+      uint4 cl[8], ch[8], sl[8], sh[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i < hv && row_live) {
+          cl[i] = __ldg(reinterpret_cast<const uint4*>(cs) + i);
+          ch[i] = __ldg(reinterpret_cast<const uint4*>(cs + half) + i);
+          sl[i] = __ldg(reinterpret_cast<const uint4*>(sn) + i);
+          sh[i] = __ldg(reinterpret_cast<const uint4*>(sn + half) + i);
+        }
+      }
       ok = mbar_wait(q_full, 0, abort_flag, p.status, 32, 0);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok && q_pos < seq_len) {
-        const int half = p.rot_dim >> 1, hv = half >> 3;
-        const T* cs = reinterpret_cast<const T*>(p.rot_cos) + (int64_t)(start + q_pos) * p.rot_dim;
-        const T* sn = reinterpret_cast<const T*>(p.rot_sin) + (int64_t)(start + q_pos) * p.rot_dim;
+      if (ok && row_live) {
         auto chunk_at = [&](int col) -> uint4* {
           return reinterpret_cast<uint4*>(smem + OFF_Q + (col >> 6) * Q_BOX + row * 128 +
                                           ((((col & 63) >> 3) ^ (row & 7)) << 4));
         };
-#pragma unroll 2
-        for (int i = 0; i < hv; ++i) {
-          uint4* plo = chunk_at(i * 8);
-          uint4* phi = chunk_at(half + i * 8);
-          const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cs) + i);
-          const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cs + half) + i);
-          const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sn) + i);
-          const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sn + half) + i);
-          uint4 olo, ohi;
-          rot_vec8<T>(*plo, *phi, cl, ch, sl, sh, olo, ohi);
-          *plo = olo;
-          *phi = ohi;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (i < hv) {
+            uint4* plo = chunk_at(i * 8);
+            uint4* phi = chunk_at(half + i * 8);
+            uint4 olo, ohi;
+            rot_vec8<T>(*plo, *phi, cl[i], ch[i], sl[i], sh[i], olo, ohi);
+            *plo = olo;
+            *phi = ohi;
+          }
         }
       }
       fence_proxy_async_smem();     // generic-proxy stores before the tensor core's reads of the tile

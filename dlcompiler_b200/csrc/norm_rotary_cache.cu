@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(256) fill_kv_cache_kernel(const FillParams p) 
 // of 16-byte chunks of a K row, or one 16-byte chunk of a V row.  The cache then holds rotated keys, so the
 // attention kernels need no pass over K before they read it.
 template <typename T>
-__global__ void __launch_bounds__(256) fill_kv_cache_rot_kernel(const FillParams p) {
+__global__ void __launch_bounds__(512, 3) fill_kv_cache_rot_kernel(const FillParams p) {
   const int b = blockIdx.x;
   const int blk = blockIdx.y;
   const int64_t q_start = load_idx(p.q_start, b, p.idx64_start);
@@ -369,18 +369,21 @@ __global__ void __launch_bounds__(256) fill_kv_cache_rot_kernel(const FillParams
   const int64_t tok0 = q_start + max(blk * p.page - first_slot0, 0);
   const int half = p.dim_k >> 1, hv = half >> 3, v_units = p.dim_v >> 3;
   const int per_tok = p.heads * (hv + v_units);
-  const int total = (slot_hi - slot_lo) * per_tok;
-  const int stride = blockDim.x * gridDim.z;
-#pragma unroll 2
-  for (int idx = threadIdx.x + blockIdx.z * blockDim.x; idx < total; idx += stride) {
-    const int s = idx / per_tok;
-    int r = idx - s * per_tok;
-    const int slot = slot_lo + s;
-    const int64_t tok = tok0 + s;
-    if (r < p.heads * hv) {
-      const int h = r / hv, i = r - h * hv;
-      const T* src = reinterpret_cast<const T*>(p.ks) + tok * p.ks_st + (int64_t)h * p.ks_sh;
-      T* dst = reinterpret_cast<T*>(p.kc) + page * p.kc_sp + (int64_t)slot * p.kc_ss + (int64_t)h * p.kc_sh;
+  // The block size is a multiple of per_tok (the launcher sees to it), so a thread keeps its item of the
+  // token row (a K chunk pair of one head, or a V chunk) and walks the slots: no division inside the loop.
+  const int idx0 = threadIdx.x + blockIdx.z * blockDim.x;
+  const int s0 = idx0 / per_tok, ds = (blockDim.x * gridDim.z) / per_tok;
+  int r = idx0 - s0 * per_tok;
+  const int nslots = slot_hi - slot_lo;
+  if (r < p.heads * hv) {
+    const int h = r / hv, i = r - h * hv;
+    const T* sbase = reinterpret_cast<const T*>(p.ks) + (int64_t)h * p.ks_sh;
+    T* dbase = reinterpret_cast<T*>(p.kc) + page * p.kc_sp + (int64_t)h * p.kc_sh;
+#pragma unroll 1
+    for (int sidx = s0; sidx < nslots; sidx += ds) {
+      const int64_t tok = tok0 + sidx;
+      const T* src = sbase + tok * p.ks_st;
+      T* dst = dbase + (int64_t)(slot_lo + sidx) * p.kc_ss;
       const T* cs = reinterpret_cast<const T*>(p.k_cos) + tok * p.dim_k;
       const T* sn = reinterpret_cast<const T*>(p.k_sin) + tok * p.dim_k;
       const uint4 lo = *(reinterpret_cast<const uint4*>(src) + i);
@@ -391,12 +394,20 @@ __global__ void __launch_bounds__(256) fill_kv_cache_rot_kernel(const FillParams
       rot_vec8<T>(lo, hi, cl, ch, sl, sh, olo, ohi);
       *(reinterpret_cast<uint4*>(dst) + i) = olo;
       *(reinterpret_cast<uint4*>(dst + half) + i) = ohi;
-    } else {
-      r -= p.heads * hv;
-      const int h = r / v_units, u = r - h * v_units;
-      const T* src = reinterpret_cast<const T*>(p.vs) + tok * p.vs_st + (int64_t)h * p.vs_sh;
-      T* dst = reinterpret_cast<T*>(p.vc) + page * p.vc_sp + (int64_t)slot * p.vc_ss + (int64_t)h * p.vc_sh;
-      *(reinterpret_cast<uint4*>(dst) + u) = *(reinterpret_cast<const uint4*>(src) + u);
+    }
+  } else {
+    r -= p.heads * hv;
+    const int h = r / v_units, u = r - h * v_units;
+    const T* sbase = reinterpret_cast<const T*>(p.vs) + (int64_t)h * p.vs_sh;
+    T* dbase = reinterpret_cast<T*>(p.vc) + page * p.vc_sp + (int64_t)h * p.vc_sh;
+    for (int sidx = s0; sidx < nslots; sidx += 4 * ds) {
+      uint4 val[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (sidx + j * ds < nslots) val[j] = *(reinterpret_cast<const uint4*>(sbase + (tok0 + sidx + j * ds) * p.vs_st) + u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (sidx + j * ds < nslots) *(reinterpret_cast<uint4*>(dbase + (int64_t)(slot_lo + sidx + j * ds) * p.vc_ss) + u) = val[j];
     }
   }
 }
@@ -523,8 +534,11 @@ extern "C" int dlb_fill_kv_cache(const void* k_states, const void* v_states, voi
                       (((uintptr_t)k_cos | (uintptr_t)k_sin) & 15) == 0,
                   DLB_ERR_UNSUPPORTED,
                   "fill_kv_cache: rotating K needs fp16/bf16, a head size that is a multiple of 16 and 16-byte aligned rows");
-    if (dtype == DLB_DTYPE_BF16) fill_kv_cache_rot_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(p);
-    else fill_kv_cache_rot_kernel<__half><<<grid, 256, 0, s>>>(p);
+    const int per_tok = (int)(heads * (dim_k / 16 + dim_v / 8));
+    DLB_CHECK_ARG(per_tok <= 512, DLB_ERR_UNSUPPORTED, "fill_kv_cache: heads x head size too large for the rotating form");
+    const int threads = (512 / per_tok) * per_tok;      // a multiple of per_tok: every thread keeps its item
+    if (dtype == DLB_DTYPE_BF16) fill_kv_cache_rot_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(p);
+    else fill_kv_cache_rot_kernel<__half><<<grid, threads, 0, s>>>(p);
     DLB_CUDA_LAUNCH_CHECK();
     return DLB_OK;
   }
