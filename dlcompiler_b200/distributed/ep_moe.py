@@ -281,6 +281,14 @@ def ep_fused_moe_peer(ctx: EpPeerContext, hidden_states, w1_local, w2_local, top
     With `ctx.pull` off the down GEMM's epilogue instead stores each row into the SENDER's result buffer
     and the combine reads locally.  `EpPeerContext` picks the form from the number of tiles the down GEMM
     is expected to have (one wave or less: pull).
+
+    Every rank of the group must call this once per step, in the same order.  The kernels wait for each
+    other on flags in peer memory; a wait gives up after the wait budget (2 s unless changed with
+    `_lib.set_wait_budget_ms` or DLBLAS_B200_WAIT_BUDGET_MS), which is therefore the largest skew between
+    ranks a step tolerates.  A wait that gave up does not stop the step: the kernels go on with whatever had
+    arrived and record the fact in the device status word, so a caller has to call `check_device_status()`
+    (it synchronises) before it trusts the output; it raises `DlblasError` if any wait of the step timed out.
+    Ids outside [0, num_experts) are sent nowhere and add nothing to their token's output.
     """
     from .. import _lib
 
