@@ -304,12 +304,13 @@ int dlb_fill_kv_cache(const void* k_states, const void* v_states, void* k_caches
  * loads the library holds its 32 MiB until the process exits.  The call allocates nothing.
  *   - needs dlb_paged_decode_workspace_floats(batch, hq, head_dim, max_splits) <=
  *     DLB_DECODE_STATIC_FLOATS, otherwise it returns an error (status -5) and launches nothing;
+ *     `status` may be NULL (a caller that must not allocate may not have a status word yet);
  *   - the first call on a device looks up the array's device address; make that call before any
  *     stream capture on that device;
  *   - all calls on a device share the array (it keeps the last call's contents; no part of it
  *     needs clearing between calls), so calls whose kernels may overlap on the GPU must be
  *     serialised by the caller.
- * All other arguments are those of dlb_paged_decode. */
+ * All other arguments are those of dlb_paged_decode, with one head size for q/k and v (head_dim). */
 int dlb_paged_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
                             const void* block_table, const void* kv_seqlens, int64_t batch, int64_t hq, int64_t hkv,
                             int64_t head_dim, int64_t page_size, int64_t num_pages, int64_t max_pages,
