@@ -16,9 +16,16 @@ Parity status
            The sliding-window and soft-cap forms of the paged prefill and the
            topk_gating gradients have no reference fixture; they are tied to the
            pinned functions by tests/test_oracle_props.py and by autograd.
-  UNPINNED grouped_topk_gating (group-limited sigmoid routing) and
-           moe_align_block_size: the reference contains neither, so these two
-           restate the definitions written in this file; "parity unpinned".
+  THIRD-PARTY PINNED  grouped_topk_gating (group-limited sigmoid routing) and
+           moe_align_block_size: the reference project contains neither.  They restate
+           the published algorithms and are checked against other implementations of
+           them: the routing against the output of transformers 5.5.0
+           DeepseekV3MoE.route_tokens_to_experts executed on seeded inputs
+           (tests/golden/grouped_gating_hf.pt), the block-padded sort against the worked
+           example in the docstring of vLLM 0.22's moe_align_block_size
+           (tests/golden/moe_align_vllm_doc.pt); both fixtures are produced by
+           tests/golden/make_golden_third_party.py.  Against the REFERENCE these two
+           stay "parity unpinned": it has nothing to compare with.
            The LSE output of prefill is pinned only through its formula
            (python/dlBLAS/dlblas/kernels/flash_attention.py:152-155).
 """
@@ -121,7 +128,7 @@ def sigmoid_spec(x: torch.Tensor) -> torch.Tensor:
 def grouped_topk_gating(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, n_group: int = 1,
                         topk_group: int = 1, routed_scaling_factor: float = 1.0, renormalize: bool = True,
                         scoring_func: str = "sigmoid"):
-    """Group-limited top-k routing (UNPINNED: no reference implementation exists).
+    """Group-limited top-k routing (absent from the reference; pinned to the transformers DeepSeek-V3 router).
 
     Definition: scores = sigmoid_spec(logits) or softmax(logits) in fp32; choice = scores + bias
     (for softmax without bias the selection runs on the logits, which order identically);
@@ -196,7 +203,7 @@ def softmax_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = Fa
 # moe_align_block_size
 # --------------------------------------------------------------------------------------
 def moe_align_block_size(topk_ids: torch.Tensor, block: int, num_experts: int):
-    """Block-padded counting sort of the slots by expert (UNPINNED: absent from the reference).
+    """Block-padded counting sort of the slots by expert (absent from the reference; pinned to vLLM's documented example).
 
     Conventions fixed here: sorted_token_ids has numel + num_experts*(block-1) entries rounded
     up to a multiple of `block`, filled with the sentinel `numel`; within an expert the slots

@@ -152,3 +152,26 @@ def test_moe_align_config_and_foreign_ids(cuda_device):
     s, e, n = moe_align_block_size(local.to(cuda_device), 128, 4)
     rs, re_, rn, _ = oracle.moe_align_block_size(local, 128, 4)
     assert torch.equal(s.cpu(), rs) and torch.equal(e.cpu(), re_) and torch.equal(n.cpu(), rn)
+
+
+def test_grouped_gating_matches_transformers_fixture(cuda_device, golden_dir):
+    """The CUDA router against the output of transformers' DeepseekV3MoE.route_tokens_to_experts (fixture made by
+    tests/golden/make_golden_third_party.py): same expert set per token, weights within fp32 rounding."""
+    for case in torch.load(os.path.join(golden_dir, "grouped_gating_hf.pt"), weights_only=True):
+        ids, w = grouped_topk_gating(case["logits"].to(cuda_device), case["bias"].to(cuda_device), case["top_k"],
+                                     case["n_group"], case["topk_group"], case["scale"], case["renormalize"], "sigmoid")
+        keep = oracle.gating_margins(case["logits"], case["bias"], case["top_k"], case["n_group"],
+                                     case["topk_group"]) > 1e-6
+        a, ai = torch.sort(ids.cpu().long()[keep], dim=-1)
+        b, bi = torch.sort(case["ids"].long()[keep], dim=-1)
+        assert torch.equal(a, b)
+        torch.testing.assert_close(w.cpu()[keep].gather(1, ai), case["weights"][keep].gather(1, bi), rtol=2e-6, atol=2e-6)
+
+
+def test_moe_align_matches_vllm_documented_example(cuda_device, golden_dir):
+    d = torch.load(os.path.join(golden_dir, "moe_align_vllm_doc.pt"), weights_only=True)
+    ids, block, want = d["topk_ids"], d["block_size"], d["token_ids"]
+    s, e, n = moe_align_block_size(ids.to(cuda_device), block, int(ids.max()) + 1)
+    assert int(n.item()) == want.numel()
+    assert torch.equal(s.cpu()[:want.numel()], want)
+    assert e.cpu()[:want.numel() // block].tolist() == [1, 2, 3, 4]

@@ -127,3 +127,40 @@ def test_gshard_topk_gating_ground_truth(golden_dir):
         assert sel.shape == c["select"].shape
         # torch.topk leaves the order among equal priorities open: compare what was selected, not where
         assert torch.equal(_selection_priorities(sel, prio, E), _selection_priorities(c["select"], prio, E))
+
+
+# ---- third-party pins for the two operators that the reference project does not contain ------------------
+def _same_routing(ids, w, case, tol=2e-6):
+    """ids as sets per token (the third-party router returns them unsorted), weights matched by id."""
+    ref_ids, ref_w = case["ids"].long(), case["weights"]
+    a, ai = torch.sort(ids.long(), dim=-1)
+    b, bi = torch.sort(ref_ids, dim=-1)
+    assert torch.equal(a, b)
+    torch.testing.assert_close(w.gather(1, ai), ref_w.gather(1, bi), rtol=tol, atol=tol)
+
+
+def test_grouped_gating_matches_transformers_deepseek_v3_router(golden_dir):
+    """Group-limited sigmoid routing against the output of transformers' DeepseekV3MoE.route_tokens_to_experts
+    (executed by tests/golden/make_golden_third_party.py).  That router fills masked groups with 0 instead of
+    -inf, which selects differently only when a biased score is <= 0; the fixtures' biases keep them positive.
+    Tokens whose float64 decision margin is below fp32 noise are excluded (two sigmoid implementations may
+    order them differently); the fixtures have none or a handful."""
+    for case in _load(golden_dir, "grouped_gating_hf.pt"):
+        ids, w = oracle.grouped_topk_gating(case["logits"], case["bias"], case["top_k"], case["n_group"],
+                                            case["topk_group"], case["scale"], case["renormalize"], "sigmoid")
+        keep = oracle.gating_margins(case["logits"], case["bias"], case["top_k"], case["n_group"],
+                                     case["topk_group"]) > 1e-6
+        assert keep.float().mean() > 0.98
+        sub = {"ids": case["ids"][keep], "weights": case["weights"][keep]}
+        _same_routing(ids[keep], w[keep], sub)
+
+
+def test_moe_align_matches_vllm_documented_example(golden_dir):
+    """The worked example in the docstring of vLLM's moe_align_block_size (experts numbered 1..4): same slot
+    order inside an expert, same sentinel (numel), same per-expert padding to a block."""
+    d = _load(golden_dir, "moe_align_vllm_doc.pt")
+    ids, block, want = d["topk_ids"], d["block_size"], d["token_ids"]
+    s, e, n, _ = oracle.moe_align_block_size(ids, block, int(ids.max()) + 1)
+    assert int(n) == want.numel()
+    assert torch.equal(s[:want.numel()], want)
+    assert e[:want.numel() // block].tolist() == [1, 2, 3, 4]
