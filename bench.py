@@ -1,7 +1,7 @@
 """Benchmark of the dlBLAS hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ops all|none]
-    python bench.py --profile-case {silu,gating,moe,prefill,prefill_c4,decode,rotary,rotary_c4} [--steps N]
+    python bench.py --profile-case {silu,gating,moe,prefill,prefill_c4,decode,decode_p1,rotary,rotary_c4} [--steps N]
 
 Headline (one JSON line on stdout): fused_moe on the Mixtral-like configuration
 (T=4096, H=4096, I=14336, E=8, top_k=2, bf16) in TFLOP/s, whole job.  N > 1 runs the
@@ -809,6 +809,16 @@ def run_profile_case(args):
         sin = torch.rand(tok, dd, generator=g, device=dev).to(torch.bfloat16)
         fn = lambda: dl.apply_rotary_pos_emb(q, k, cos, sin, q, k)
         what = f"rotary in place q [{tok}, 32, 128] k [{tok}, 8, 128] bf16"
+    elif op == "decode_p1":
+        wl = W.DecodeWorkload(batch=16, page=1)                        # token-granular cache, ~1.1 GB
+        d = wl.make(device=dev)
+        q = d["q"].to(dev)
+        o = torch.empty_like(q)
+        tb, ln = d["block_table"].to(dev), d["kv_seqlens"].to(dev)
+        kb, vb = d["k_cache"].squeeze(1), d["v_cache"].squeeze(1)
+        req = torch.arange(wl.batch, device=dev)
+        fn = lambda: dl.decode_attention_fwd(q, kb, vb, o, tb, req, None, ln, None, tb.size(1), q.size(-1) ** -0.5)
+        what = f"decode_attention_fwd B=16 ctx_sum={int(d['kv_seqlens'].sum())} page 1 bf16"
     else:
         wl = W.DecodeWorkload(batch=16)                                # ~1.1 GB of KV cache
         d = wl.make(device=dev)
@@ -855,7 +865,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=4096)
     ap.add_argument("--warm-seconds", type=float, default=1.0,
                     help="N = 1: keep warming up until this much wall time has passed (device under load)")
-    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "prefill_c4", "decode", "rotary", "rotary_c4"],
+    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "prefill_c4", "decode", "decode_p1", "rotary", "rotary_c4"],
                     help="run one op --steps times (at most 8) on a profiler-sized case and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -3,8 +3,8 @@
 // One warp per token.  Lane l owns the VPL consecutive experts
 // [l*VPL, (l+1)*VPL), loaded as 128-bit vectors; every reduction (softmax
 // max/sum, per-group top-2 sums, group ranking, k rounds of arg-max) is a
-// warp-shuffle tree, so no shared memory and no atomics are used and the
-// result is deterministic.
+// warp-shuffle tree or a hardware warp reduction; shared memory only holds
+// per-warp lists (no atomics), so the result is deterministic.
 //
 // Algorithm (scoring = sigmoid, grouped):
 //   s[e]   = sigmoid(logits[e])                       (weights come from s)
@@ -106,29 +106,32 @@ __device__ __forceinline__ void sigmoid_spec2(float x0, float x1, float& y0, flo
   const float c0 = fminf(fmaxf(x0, -87.0f), 86.0f), c1 = fminf(fmaxf(x1, -87.0f), 86.0f);
   const uint64_t xc = f2_pack(c0, c1);
   const uint64_t hi2 = f2_pack(kNegLog2eHi, kNegLog2eHi);
-  const uint64_t z = f2_fma(xc, hi2, f2_pack(kMagic, kMagic));
-  const uint64_t n = f2_add(z, f2_pack(-kMagic, -kMagic));                      // z - M, exact
-  float n0, n1;
-  f2_unpack(n, n0, n1);
-  uint64_t r = f2_fma(xc, hi2, f2_pack(-n0, -n1));
+  const uint64_t magic2 = f2_pack(kMagic, kMagic);
+  const uint64_t neg1 = f2_pack(-1.0f, -1.0f);
+  const uint64_t one = f2_pack(1.0f, 1.0f);
+  const uint64_t z = f2_fma(xc, hi2, magic2);
+  const uint64_t negn = f2_fma(z, neg1, magic2);                                 // M - z = -n, exact
+  uint64_t r = f2_fma(xc, hi2, negn);
   r = f2_fma(xc, f2_pack(kNegLog2eLo, kNegLog2eLo), r);
   uint64_t p = f2_pack(1.32874317932873964310e-03f, 1.32874317932873964310e-03f);
   p = f2_fma(p, r, f2_pack(9.67150740325450897217e-03f, 9.67150740325450897217e-03f));
   p = f2_fma(p, r, f2_pack(5.55065572261810302734e-02f, 5.55065572261810302734e-02f));
   p = f2_fma(p, r, f2_pack(2.40222424268722534180e-01f, 2.40222424268722534180e-01f));
   p = f2_fma(p, r, f2_pack(6.93147063255310058594e-01f, 6.93147063255310058594e-01f));
-  p = f2_fma(p, r, f2_pack(1.0f, 1.0f));
+  p = f2_fma(p, r, one);
   float p0, p1, z0, z1;
   f2_unpack(p, p0, p1);
   f2_unpack(z, z0, z1);
-  const float e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(z0) << 23));
-  const float e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(z1) << 23));
-  const uint64_t one = f2_pack(1.0f, 1.0f);
-  const uint64_t d = f2_add(one, f2_pack(e0, e1));
-  float d0, d1;
-  f2_unpack(d, d0, d1);
-  uint64_t y = f2_pack(__int_as_float(0x7EF311C7 - __float_as_int(d0)), __int_as_float(0x7EF311C7 - __float_as_int(d1)));
-  const uint64_t nd = f2_pack(-d0, -d1);
+  // e = p * 2^n: n sits in the low bits of z; one integer multiply-add moves it into p's exponent field
+  const uint32_t e0 = __float_as_uint(z0) * 0x00800000u + __float_as_uint(p0);
+  const uint32_t e1 = __float_as_uint(z1) * 0x00800000u + __float_as_uint(p1);
+  // -d = -(1 + e) rounds exactly like d (round-to-nearest is symmetric); bits(d) = bits(-d) - 2^31, so the
+  // first guess 0x7EF311C7 - bits(d) is 0xFEF311C7 - bits(-d) and d itself is never needed
+  const uint64_t nd = f2_fma(f2_pack(__uint_as_float(e0), __uint_as_float(e1)), neg1, neg1);
+  float nd0, nd1;
+  f2_unpack(nd, nd0, nd1);
+  uint64_t y = f2_pack(__uint_as_float(0xFEF311C7u - __float_as_uint(nd0)),
+                       __uint_as_float(0xFEF311C7u - __float_as_uint(nd1)));
 #pragma unroll
   for (int it = 0; it < 3; ++it) y = f2_fma(y, f2_fma(nd, y, one), y);
   f2_unpack(y, y0, y1);
@@ -176,45 +179,63 @@ __device__ __forceinline__ void merge_top2(float& a1, float& a2, float b1, float
   a2 = lo;
 }
 
-// k rounds over the heads of the sorted per-lane lists.  One hardware warp reduction (redux.sync) finds
-// the maximum head; a ballot picks the lowest lane among equals (lanes hold ascending expert ranges);
-// the winning lane pops its head (predicated moves, no branch).  Lane k remembers round k's winner as
-// (lane, key) and, when TRACK_DUP, how many equal keys of that lane left before it: equal keys inside
-// one lane leave in index order, and such rounds are consecutive.
-template <int VPL, bool TRACK_DUP>
-__device__ __forceinline__ void topk_rounds(uint32_t (&key)[VPL], int top_k, int lane, int& my_owner,
-                                            uint32_t& my_key, int& my_dup) {
-  int prev_owner = -1, dup = 0;
-  uint32_t prev_key = 0;
-#pragma unroll 2
+// Shared-memory shape of the router for VPL experts per lane: a lane's sorted list has VPL entries plus a
+// zero terminator, padded so that 128-bit stores stay aligned and (for VPL = 8: 12 words per lane) free of
+// bank conflicts; 16 experts per lane run 4 warps per CTA to stay inside the 48 KiB static limit.
+template <int VPL> struct GateShape {
+  static constexpr int WARPS = VPL >= 16 ? 4 : 8;
+  static constexpr int LIST = VPL + (VPL >= 4 ? 4 : 1);
+};
+
+// k rounds over the heads of the sorted per-lane lists.  Only the head lives in a register; the rest of a
+// lane's list is in shared memory behind it.  One hardware warp reduction (redux.sync) finds the maximum
+// head; a ballot picks the lowest lane among equals (lanes hold ascending expert ranges); that lane alone
+// records the round's winner as (key, lane, run) in win[k], steps its list pointer and reloads its head
+// (the list ends in 0 = retired).  `run` counts how many equal keys of that lane left directly before:
+// equal keys inside one lane leave in consecutive rounds and stand for ascending expert indices.
+template <bool TRACK_DUP, int TOPK>
+__device__ __forceinline__ void topk_rounds(uint32_t head, const uint32_t* __restrict__ my_list, uint2* __restrict__ win,
+                                            int top_k_rt, int lane) {
+  const int top_k = TOPK > 0 ? TOPK : top_k_rt;
+  uint32_t lt;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(lt));
+  int ptr = 0, run = 0;
+  uint32_t last = 0;
+#pragma unroll(TOPK > 0 ? TOPK : 4)
   for (int k = 0; k < top_k; ++k) {
-    const uint32_t wmax = __reduce_max_sync(0xffffffffu, key[0]);
-    const int owner = __ffs(__ballot_sync(0xffffffffu, key[0] == wmax)) - 1;
-    const bool rec = lane == k;
-    my_owner = rec ? owner : my_owner;
-    my_key = rec ? wmax : my_key;
-    if constexpr (TRACK_DUP) {
-      dup = (owner == prev_owner && wmax == prev_key) ? dup + 1 : 0;
-      prev_owner = owner;
-      prev_key = wmax;
-      my_dup = rec ? dup : my_dup;
+    const uint32_t wmax = __reduce_max_sync(0xffffffffu, head);
+    const bool mine = head == wmax;
+    const uint32_t eq = __ballot_sync(0xffffffffu, mine);
+    if (mine && (eq & lt) == 0) {
+      if constexpr (TRACK_DUP) {
+        run = (wmax == last) ? run + 1 : 0;
+        last = wmax;
+      }
+      win[k] = make_uint2(wmax, (uint32_t)lane | ((uint32_t)run << 8));
+      ++ptr;
+      head = my_list[ptr];
     }
-    const bool pop = lane == owner;
-#pragma unroll
-    for (int v = 0; v + 1 < VPL; ++v) key[v] = pop ? key[v + 1] : key[v];
-    key[VPL - 1] = pop ? 0u : key[VPL - 1];
   }
 }
 
 // One warp per token, VPL experts per lane (lane l holds experts l*VPL ..).  FULL: experts == 32 * VPL
-// and 16-byte aligned rows and bias, so no bounds checks and only vector loads.
-template <int VPL, bool FULL>
-__global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
+// and 16-byte aligned rows and bias, so no bounds checks and only vector loads.  LG >= 0 fixes the lanes per
+// group at 2^LG with all 32 lanes in groups, and TOPK > 0 fixes top_k, so that the shuffle trees, the group
+// ranking and the rounds unroll (the DeepSeek-V3 shape: 256 experts, 8 groups, top-8); LG = -1 / TOPK = 0
+// read them from the parameters.
+#ifndef DLB_GATE_MIN_BLOCKS
+#define DLB_GATE_MIN_BLOCKS 6
+#endif
+template <int VPL, bool FULL, int LG = -1, int TOPK = 0>
+__global__ void __launch_bounds__(GateShape<VPL>::WARPS * 32, LG >= 0 ? DLB_GATE_MIN_BLOCKS : 1)
+grouped_topk_kernel(GatingParams p) {
+  constexpr int WARPS = GateShape<VPL>::WARPS, LIST = GateShape<VPL>::LIST;
   const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
-  const int64_t token = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  __shared__ __align__(16) uint32_t sm_key[8][32 * VPL];   // per warp: every expert's selection key, by expert index
-  __shared__ __align__(16) float sm_s[8][32 * VPL];        // per warp: every expert's un-biased score
+  const int64_t token = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  __shared__ __align__(16) uint32_t sm_key[WARPS][32 * VPL];     // per warp: every expert's selection key, by expert index
+  __shared__ __align__(16) float sm_s[WARPS][32 * VPL];          // per warp: every expert's un-biased score
+  __shared__ __align__(16) uint32_t sm_list[WARPS][32 * LIST];   // per warp: each lane's keys sorted descending, then 0
+  __shared__ __align__(8) uint2 sm_win[WARPS][32];               // per warp: round k's winner (key, lane | run << 8)
   if (token >= p.tokens) return;  // whole warp leaves together
 
   const int E = p.experts;
@@ -242,7 +263,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
   }
 
   // ---- scoring ----
-  if (p.scoring == DLB_SCORE_SIGMOID) {
+  if (LG >= 0 || p.scoring == DLB_SCORE_SIGMOID) {   // the fixed-shape form is only launched for sigmoid scoring
     if constexpr (VPL >= 2) {
 #pragma unroll
       for (int v = 0; v < VPL; v += 2) {
@@ -283,7 +304,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     for (int v = 0; v < VPL; ++v)
       if (valid(v)) p.probs[token * E + e0 + v] = s[v];
   }
-  if (p.scoring == DLB_SCORE_SIGMOID || p.bias != nullptr) {
+  if (LG >= 0 || p.scoring == DLB_SCORE_SIGMOID || p.bias != nullptr) {
     if (p.bias == nullptr) {
 #pragma unroll
       for (int v = 0; v < VPL; ++v) c[v] = s[v];
@@ -322,46 +343,66 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
   }
   sort_desc<VPL>(key);
+  uint32_t* my_list = sm_list[threadIdx.x >> 5] + lane * LIST;
+  if constexpr (VPL >= 4) {
+#pragma unroll
+    for (int v = 0; v < VPL; v += 4)
+      *reinterpret_cast<uint4*>(my_list + v) = make_uint4(key[v], key[v + 1], key[v + 2], key[v + 3]);
+  } else {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) my_list[v] = key[v];
+  }
+  my_list[VPL] = 0u;
+  // equal keys inside one lane need the run bookkeeping (with a ragged last lane the -inf fillers do not count)
+  bool lane_dup = false;
+#pragma unroll
+  for (int v = 0; v + 1 < VPL; ++v) lane_dup |= (key[v] == key[v + 1]) && (FULL || key[v] > KEY_NEG_INF);
+  const bool any_dup = __any_sync(0xffffffffu, lane_dup);
+  uint32_t head = key[0];
 
   // ---- group selection: a group's score is the sum of its two best choices ----
-  if (p.n_group > 1) {
-    const int lpg = p.lanes_per_group, lg = p.lanes_per_group_log2;   // a group spans 2^lg lanes
+  if (LG >= 0 || p.n_group > 1) {
+    const int lg = LG >= 0 ? LG : p.lanes_per_group_log2;   // a group spans 2^lg lanes
+    const int lpg = 1 << lg;
+    const int n_group = LG >= 0 ? (32 >> LG) : p.n_group;
     float t1 = key_score(key[0]);
     float t2 = -CUDART_INF_F;
     if constexpr (VPL >= 2) t2 = key_score(key[1]);
+#pragma unroll
     for (int o = 1; o < lpg; o <<= 1) {
       const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
       const float o2 = __shfl_xor_sync(0xffffffffu, t2, o);
       merge_top2(t1, t2, o1, o2);
     }
     const int my_group = lane >> lg;
-    const float my_score = (my_group < p.n_group) ? __fadd_rn(t1, t2) : -CUDART_INF_F;
+    const float my_score = (LG >= 0 || my_group < n_group) ? __fadd_rn(t1, t2) : -CUDART_INF_F;
     // rank = groups that beat mine (ties: lower index).  The lanes of a group share the comparisons:
     // each takes a slice of the groups, then the partial counts are summed inside the group.
-    const int per = (p.n_group + lpg - 1) >> lg;
+    const int per = (n_group + lpg - 1) >> lg;
     const int g0 = (lane & (lpg - 1)) * per;
     int rank = 0;
+#pragma unroll
     for (int i = 0; i < per; ++i) {
       const int g = g0 + i;
       const float gs = __shfl_sync(0xffffffffu, my_score, (g << lg) & 31);
-      rank += (g < p.n_group) && ((gs > my_score) || (gs == my_score && g < my_group));
+      rank += (g < n_group) && ((gs > my_score) || (gs == my_score && g < my_group));
     }
-    for (int o = 1; o < lpg; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-    const bool keep = (my_group < p.n_group) && (rank < p.topk_group);
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) key[v] = keep ? key[v] : KEY_NEG_INF;
+    for (int o = 1; o < lpg; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+    // a lane of a dropped group retires: top_k never exceeds the experts of the kept groups (checked by the
+    // entry point), so its list is never needed
+    head = ((LG >= 0 || my_group < n_group) && (rank < p.topk_group)) ? head : 0u;
   }
 
-  // ---- top-k (ties -> lower expert index); equal finite keys inside one lane need the slower bookkeeping ----
-  bool lane_dup = false;
-#pragma unroll
-  for (int v = 0; v + 1 < VPL; ++v) lane_dup |= (key[v] == key[v + 1]) && (key[v] > KEY_NEG_INF);
-  const bool any_dup = __any_sync(0xffffffffu, lane_dup);
-  int my_owner = 0, my_dup = 0;
-  uint32_t my_key = 0;
-  if (!any_dup) topk_rounds<VPL, false>(key, p.top_k, lane, my_owner, my_key, my_dup);
-  else topk_rounds<VPL, true>(key, p.top_k, lane, my_owner, my_key, my_dup);
+  // ---- top-k (ties -> lower expert index) ----
+  uint2* win = sm_win[threadIdx.x >> 5];
+  const int top_k = TOPK > 0 ? TOPK : p.top_k;
+  if (!any_dup) topk_rounds<false, TOPK>(head, my_list, win, top_k, lane);
+  else topk_rounds<true, TOPK>(head, my_list, win, top_k, lane);
   __syncwarp();
+  const uint2 mine = win[lane < top_k ? lane : 0];
+  const uint32_t my_key = mine.x;
+  const int my_owner = mine.y & 0xff, my_dup = mine.y >> 8;
   int my_v = 0;
   {
     const uint32_t* ok = wkeys + my_owner * VPL;
@@ -378,7 +419,7 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
 #pragma unroll
     for (int v = VPL - 1; v >= 0; --v) my_v = (orig[v] == my_key) ? v : my_v;
-    if (any_dup) {     // take the (dup+1)-th match
+    if (any_dup) {     // take the (run+1)-th match
       int seen = 0, pick = my_v;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
@@ -390,16 +431,17 @@ __global__ void __launch_bounds__(256) grouped_topk_kernel(GatingParams p) {
     }
   }
   const int my_id = my_owner * VPL + my_v;
-  const float my_w = (lane < p.top_k) ? wscores[my_id] : 0.f;
+  const float my_w = (lane < top_k) ? wscores[my_id] : 0.f;
   float wsum = my_w;
+  // lanes >= top_k hold 0, so with top_k <= 8 the first two levels of the tree add exact zeros and are skipped
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-  if (lane < p.top_k) {
+  for (int o = (TOPK > 0 && TOPK <= 8) ? 4 : 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+  if (lane < top_k) {
     float w = my_w;
     if (p.renormalize) w = __fdividef(w, wsum + 1e-20f);
     w *= p.scale;
-    p.ids[token * p.top_k + lane] = my_id;
-    p.weights[token * p.top_k + lane] = w;
+    p.ids[token * top_k + lane] = my_id;
+    p.weights[token * top_k + lane] = w;
   }
 }
 
@@ -416,7 +458,7 @@ static int launch_gating(const GatingParams& p_in, void* stream) {
   }
   const bool full = p.experts == 32 * vpl && ((uintptr_t)p.logits & 15) == 0 && (p.ld % 4) == 0 &&
                     ((uintptr_t)p.bias & 15) == 0;
-  const int warps = 8;
+  const int warps = vpl >= 16 ? 4 : 8;                     // GateShape<VPL>::WARPS
   const int64_t blocks = (p.tokens + warps - 1) / warps;
   DLB_CHECK_ARG(blocks <= 0x7fffffffLL, DLB_ERR_TOO_LARGE, "gating: too many tokens");
   cudaStream_t s = (cudaStream_t)stream;
@@ -429,7 +471,9 @@ static int launch_gating(const GatingParams& p_in, void* stream) {
       else grouped_topk_kernel<4, false><<<g, t, 0, s>>>(p);
       break;
     case 8:
-      if (full) grouped_topk_kernel<8, true><<<g, t, 0, s>>>(p);
+      if (full && p.n_group == 8 && p.top_k == 8 && p.scoring == DLB_SCORE_SIGMOID)
+        grouped_topk_kernel<8, true, 2, 8><<<g, t, 0, s>>>(p);
+      else if (full) grouped_topk_kernel<8, true><<<g, t, 0, s>>>(p);
       else grouped_topk_kernel<8, false><<<g, t, 0, s>>>(p);
       break;
     default:

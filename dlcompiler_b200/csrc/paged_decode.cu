@@ -102,21 +102,20 @@ struct DecodeParams {
   int gather;
   const void* k_cache;
   const void* v_cache;
-  int64_t k_stride_page, k_stride_slot, k_stride_head;
-  int64_t v_stride_page, v_stride_slot, v_stride_head;
+  int64_t k_stride_head, v_stride_head;                   // elements
+  uint32_t k_page_bytes, k_slot_bytes, v_page_bytes, v_slot_bytes;
+  int page_shift;                                         // log2(page_size) in the gather path (1, 2 or 4 tokens)
 };
 
-// 16-byte asynchronous copy global -> shared (bypassing L1), and "arrive on this mbarrier once all of
-// this thread's earlier cp.async copies have landed" (the arrival is one of the barrier's expected count).
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-// the same copy, or 16 bytes of zeros when `src_or_base` is not `gmem_src` (a chunk past the head size):
-// the zero fill stays inside the cp.async group, so the stage's barrier covers it like any other chunk
-template <typename P>
-__device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const P* gmem_src, const P* src_or_base) {
-  const int bytes = (src_or_base == gmem_src) ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src_or_base), "r"(bytes)
+// 16-byte asynchronous copy global -> shared (bypassing L1), or 16 bytes of zeros when src_bytes == 0 (a
+// chunk past the head size: the zero fill stays inside the cp.async group, so the stage's barrier covers
+// it like any other chunk), to `smem_dst + DST_OFFSET`: the offset is an immediate of the instruction, so
+// one address register serves the K and the V half of a stage.  cp_async_arrive: "arrive on this mbarrier
+// once all of this thread's earlier cp.async copies have landed" (one of the barrier's expected count).
+template <int DST_OFFSET>
+__device__ __forceinline__ void cp_async_16_sized(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0 + %3], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes),
+               "n"(DST_OFFSET)
                : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
@@ -216,56 +215,70 @@ paged_decode_split_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gr
       // cp.async straight into the same 128-byte-swizzled tile layout: 16 lanes per token row, two rows
       // per pass.  The launch has GATHER_WARPS producer warps in this mode, each taking its share of a
       // tile's 64 rows (a producer warp's instruction rate, not bandwidth, is what limits the gather).
-      const T* kc = reinterpret_cast<const T*>(p.k_cache);
-      const T* vc = reinterpret_cast<const T*>(p.v_cache);
+      // Everything a lane needs per row is fixed before the tile loop: its 16-byte column of the row (or a
+      // zero-length copy past the head size), and the swizzled shared-memory offset of each of its rows.
+      // Per row that leaves one shuffle (the row's page), one multiply-add per cache and the two copies.
       constexpr int CHUNKS = D / 8;                 // 16-byte chunks per token row
       constexpr int ROWS_PER_PASS = 32 / CHUNKS;    // 2 (D = 128) or 4 (D = 64)
+      constexpr int PASSES = GATHER_ROWS / ROWS_PER_PASS;
       const int c16 = lane % CHUNKS;                // chunk inside the row
       const int sub = lane / CHUNKS;                // row inside the pass
       const int hbox = c16 >> 3, cc = c16 & 7;      // 64-wide column box and chunk inside its 128-byte row
+      const int q = warp - CONSUMER_WARPS;
       const bool one_token_pages = p.page_size == 1;
       const bool k_chunk_ok = c16 * 8 < p.dk, v_chunk_ok = c16 * 8 < p.dv;   // chunks past the head size: zeros
-      const T* k_lane = kc + (int64_t)kvh * p.k_stride_head + c16 * 8;   // this lane's chunk of row (page 0, slot 0)
-      const T* v_lane = vc + (int64_t)kvh * p.v_stride_head + c16 * 8;
+      const uint32_t k_bytes = k_chunk_ok ? 16u : 0u, v_bytes = v_chunk_ok ? 16u : 0u;
+      const char* k_lane = reinterpret_cast<const char*>(p.k_cache) +
+                           ((int64_t)kvh * p.k_stride_head + (k_chunk_ok ? c16 * 8 : 0)) * (int64_t)sizeof(T);
+      const char* v_lane = reinterpret_cast<const char*>(p.v_cache) +
+                           ((int64_t)kvh * p.v_stride_head + (v_chunk_ok ? c16 * 8 : 0)) * (int64_t)sizeof(T);
+      uint32_t row_off[PASSES];
+#pragma unroll
+      for (int i = 0; i < PASSES; ++i) {
+        const int r = q * GATHER_ROWS + sub + i * ROWS_PER_PASS;
+        row_off[i] = (uint32_t)(hbox * HALF_BYTES + r * 128 + ((cc ^ (r & 7)) << 4));
+      }
+      const uint32_t smem_base = smem_u32(smem);
+      // (page, slot) of this warp's rows, one row per lane, looked up one tile ahead of the copies
+      auto lookup = [&](int t, int& pg, int& sl) {
+        const int tok = lo + t * TILE_KEYS + q * GATHER_ROWS + (lane % GATHER_ROWS);
+        int page_slot = one_token_pages ? tok : (tok >> p.page_shift);
+        if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // rows past the table: any valid page
+        int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
+        if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
+        pg = page;
+        sl = tok & (p.page_size - 1);
+      };
+      int pg, sl;
+      lookup(0, pg, sl);
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % STAGES;
         const uint32_t ph = (t / STAGES) & 1;
+        int pg_next = 0, sl_next = 0;
+        if (t + 1 < n_tiles) lookup(t + 1, pg_next, sl_next);
         int ok = 1;
         if (lane == 0) ok = mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, 11, t) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        uint8_t* kdst = smem + s * STAGE_BYTES + hbox * HALF_BYTES;
-        uint8_t* vdst = kdst + KV_BYTES;
-        const int tok0 = lo + t * TILE_KEYS;
-        // this warp's rows' (page, slot) are looked up once, one row per lane, and handed out by shuffles
-        const int q = warp - CONSUMER_WARPS;
-        int pg, sl;
-        {
-          const int tok = tok0 + q * GATHER_ROWS + (lane % GATHER_ROWS);
-          int page_slot = tok / p.page_size;
-          if (page_slot >= p.max_pages) page_slot = p.max_pages - 1;   // rows past the table: any valid page
-          int page = load_index(p.block_table, (int64_t)b * p.bt_stride + page_slot, p.table_is_int64);
-          if (tok >= ctx || page < 0 || page >= p.num_pages) page = 0;  // masked later; keep the address legal
-          pg = page;
-          sl = tok % p.page_size;
-        }
-        {
-#pragma unroll 4
-          for (int rr = sub; rr < GATHER_ROWS; rr += ROWS_PER_PASS) {
-            const int r = q * GATHER_ROWS + rr;
-            const int page = __shfl_sync(0xffffffffu, pg, rr);
-            const uint32_t off = (uint32_t)(r * 128 + ((cc ^ (r & 7)) << 4));
-            int64_t ko = (int64_t)page * p.k_stride_page, vo = (int64_t)page * p.v_stride_page;
-            if (!one_token_pages) {   // uniform
-              const int slot = __shfl_sync(0xffffffffu, sl, rr);
-              ko += (int64_t)slot * p.k_stride_slot;
-              vo += (int64_t)slot * p.v_stride_slot;
-            }
-            cp_async_16_or_zero(kdst + off, k_lane + ko, k_chunk_ok ? k_lane + ko : (const T*)kc);
-            cp_async_16_or_zero(vdst + off, v_lane + vo, v_chunk_ok ? v_lane + vo : (const T*)vc);
+        const uint32_t stage = smem_base + s * STAGE_BYTES;
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+          const int rr = sub + i * ROWS_PER_PASS;
+          const uint32_t page = (uint32_t)__shfl_sync(0xffffffffu, pg, rr);
+          const char* ks = k_lane + (uint64_t)page * p.k_page_bytes;
+          const char* vs = v_lane + (uint64_t)page * p.v_page_bytes;
+          if (!one_token_pages) {   // uniform
+            const uint32_t slot = (uint32_t)__shfl_sync(0xffffffffu, sl, rr);
+            ks += (uint64_t)slot * p.k_slot_bytes;
+            vs += (uint64_t)slot * p.v_slot_bytes;
           }
+          const uint32_t dst = stage + row_off[i];
+          cp_async_16_sized<0>(dst, ks, k_bytes);
+          cp_async_16_sized<KV_BYTES>(dst, vs, v_bytes);
         }
         cp_async_arrive(&full_bar[s]);
+        pg = pg_next;
+        sl = sl_next;
       }
     }
     const int keys_per_box = min(p.page_size, TILE_KEYS);
@@ -635,15 +648,21 @@ extern "C" int dlb_paged_decode(const void* q, const void* k_cache, const void* 
   const bool aligned16 = ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && k_stride_page % 8 == 0 &&
                          k_stride_slot % 8 == 0 && k_stride_head % 8 == 0 && v_stride_page % 8 == 0 &&
                          v_stride_slot % 8 == 0 && v_stride_head % 8 == 0;
-  p.gather = (page_size < 8 && aligned16) ? 1 : 0;
+  // (the lanes address rows as page * page_bytes + slot * slot_bytes with 32-bit byte strides and a shift
+  // for the page index, so the page size must be 1, 2 or 4 and the strides below 4 GiB)
+  const int64_t esz = 2;
+  const bool small_strides = k_stride_page * esz < (1LL << 32) && k_stride_slot * esz < (1LL << 32) &&
+                             v_stride_page * esz < (1LL << 32) && v_stride_slot * esz < (1LL << 32);
+  p.gather = (page_size < 8 && aligned16 && small_strides) ? 1 : 0;   // page sizes are powers of two: 1, 2, 4
   p.k_cache = k_cache;
   p.v_cache = v_cache;
-  p.k_stride_page = k_stride_page;
-  p.k_stride_slot = k_stride_slot;
   p.k_stride_head = k_stride_head;
-  p.v_stride_page = v_stride_page;
-  p.v_stride_slot = v_stride_slot;
   p.v_stride_head = v_stride_head;
+  p.k_page_bytes = (uint32_t)(k_stride_page * esz);
+  p.k_slot_bytes = (uint32_t)(k_stride_slot * esz);
+  p.v_page_bytes = (uint32_t)(v_stride_page * esz);
+  p.v_slot_bytes = (uint32_t)(v_stride_slot * esz);
+  p.page_shift = page_size == 4 ? 2 : (page_size == 2 ? 1 : 0);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == DLB_DTYPE_BF16) {
     return width == 128 ? launch_decode<__nv_bfloat16, 128>(tk, tv, p, s)
