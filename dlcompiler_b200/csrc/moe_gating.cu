@@ -99,25 +99,30 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-__device__ __forceinline__ void sigmoid_spec2(float x0, float x1, float& y0, float& y1) {
-  constexpr float kMagic = 12582912.0f;
-  constexpr float kNegLog2eHi = -1.44269502162933349609e+00f;
-  constexpr float kNegLog2eLo = -1.92596303350001107901e-08f;
+// The packed constants of the sequence, as 64-bit pairs in constant memory: the compiler keeps them in
+// uniform registers, where immediates would be rebuilt pair by pair with moves.
+enum { SC_HI = 0, SC_LO, SC_MAGIC, SC_NEG1, SC_ONE, SC_P5, SC_P4, SC_P3, SC_P2, SC_P1, SC_COUNT };
+__constant__ float2 g_sig_pairs[SC_COUNT] = {
+    {-1.44269502162933349609e+00f, -1.44269502162933349609e+00f}, {-1.92596303350001107901e-08f, -1.92596303350001107901e-08f},
+    {12582912.0f, 12582912.0f}, {-1.0f, -1.0f}, {1.0f, 1.0f},
+    {1.32874317932873964310e-03f, 1.32874317932873964310e-03f}, {9.67150740325450897217e-03f, 9.67150740325450897217e-03f},
+    {5.55065572261810302734e-02f, 5.55065572261810302734e-02f}, {2.40222424268722534180e-01f, 2.40222424268722534180e-01f},
+    {6.93147063255310058594e-01f, 6.93147063255310058594e-01f}};
+__device__ __forceinline__ uint64_t sig_pair(int i) { return *reinterpret_cast<const uint64_t*>(&g_sig_pairs[i]); }
+// Packed sigmoid_spec of two logits; the result stays packed (lo = sigmoid(x0), hi = sigmoid(x1)).
+__device__ __forceinline__ uint64_t sigmoid_spec2(float x0, float x1) {
   const float c0 = fminf(fmaxf(x0, -87.0f), 86.0f), c1 = fminf(fmaxf(x1, -87.0f), 86.0f);
   const uint64_t xc = f2_pack(c0, c1);
-  const uint64_t hi2 = f2_pack(kNegLog2eHi, kNegLog2eHi);
-  const uint64_t magic2 = f2_pack(kMagic, kMagic);
-  const uint64_t neg1 = f2_pack(-1.0f, -1.0f);
-  const uint64_t one = f2_pack(1.0f, 1.0f);
+  const uint64_t hi2 = sig_pair(SC_HI), magic2 = sig_pair(SC_MAGIC), neg1 = sig_pair(SC_NEG1), one = sig_pair(SC_ONE);
   const uint64_t z = f2_fma(xc, hi2, magic2);
   const uint64_t negn = f2_fma(z, neg1, magic2);                                 // M - z = -n, exact
   uint64_t r = f2_fma(xc, hi2, negn);
-  r = f2_fma(xc, f2_pack(kNegLog2eLo, kNegLog2eLo), r);
-  uint64_t p = f2_pack(1.32874317932873964310e-03f, 1.32874317932873964310e-03f);
-  p = f2_fma(p, r, f2_pack(9.67150740325450897217e-03f, 9.67150740325450897217e-03f));
-  p = f2_fma(p, r, f2_pack(5.55065572261810302734e-02f, 5.55065572261810302734e-02f));
-  p = f2_fma(p, r, f2_pack(2.40222424268722534180e-01f, 2.40222424268722534180e-01f));
-  p = f2_fma(p, r, f2_pack(6.93147063255310058594e-01f, 6.93147063255310058594e-01f));
+  r = f2_fma(xc, sig_pair(SC_LO), r);
+  uint64_t p = sig_pair(SC_P5);
+  p = f2_fma(p, r, sig_pair(SC_P4));
+  p = f2_fma(p, r, sig_pair(SC_P3));
+  p = f2_fma(p, r, sig_pair(SC_P2));
+  p = f2_fma(p, r, sig_pair(SC_P1));
   p = f2_fma(p, r, one);
   float p0, p1, z0, z1;
   f2_unpack(p, p0, p1);
@@ -134,7 +139,7 @@ __device__ __forceinline__ void sigmoid_spec2(float x0, float x1, float& y0, flo
                        __uint_as_float(0xFEF311C7u - __float_as_uint(nd1)));
 #pragma unroll
   for (int it = 0; it < 3; ++it) y = f2_fma(y, f2_fma(nd, y, one), y);
-  f2_unpack(y, y0, y1);
+  return y;
 }
 
 // Order-preserving map from fp32 to unsigned: a > b  <=>  key(a) > key(b); -inf maps to
@@ -143,14 +148,11 @@ __device__ __forceinline__ uint32_t score_key(float v) {
   const uint32_t b = __float_as_uint(v);
   return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);     // negative: all bits flip; else only the sign bit
 }
-__device__ __forceinline__ float key_score(uint32_t k) {
-  return __uint_as_float(k ^ ((uint32_t)((int32_t)~k >> 31) | 0x80000000u));
-}
 constexpr uint32_t KEY_NEG_INF = 0x007fffffu;
 
-// Sorts N keys in registers, descending, with Batcher's odd-even merge network
+// Sorts N keys (unsigned or float) in registers, descending, with Batcher's odd-even merge network
 // (19 compare-exchanges for N = 8); every index below is a compile-time constant once unrolled.
-template <int N> __device__ __forceinline__ void sort_desc(uint32_t (&k)[N]) {
+template <int N, typename K> __device__ __forceinline__ void sort_desc(K (&k)[N]) {
 #pragma unroll
   for (int p = 1; p < N; p <<= 1) {
 #pragma unroll
@@ -161,7 +163,7 @@ template <int N> __device__ __forceinline__ void sort_desc(uint32_t (&k)[N]) {
         for (int i = 0; i < q; ++i) {
           const int lo = i + j, hi = i + j + q;
           if (hi < N && (lo / (2 * p)) == (hi / (2 * p))) {
-            const uint32_t a = k[lo], b = k[hi];
+            const K a = k[lo], b = k[hi];
             k[lo] = max(a, b);
             k[hi] = min(a, b);
           }
@@ -199,8 +201,10 @@ __device__ __forceinline__ void topk_rounds(uint32_t head, const uint32_t* __res
   const int top_k = TOPK > 0 ? TOPK : top_k_rt;
   uint32_t lt;
   asm("mov.u32 %0, %%lanemask_lt;" : "=r"(lt));
-  int ptr = 0, run = 0;
+  int run = 0;
   uint32_t last = 0;
+  uint32_t tag = (uint32_t)lane;     // with `head` the pair that a winner stores: both stay in vector registers
+  const uint32_t* next = my_list;    // the lane's list entry behind `head`
 #pragma unroll(TOPK > 0 ? TOPK : 4)
   for (int k = 0; k < top_k; ++k) {
     const uint32_t wmax = __reduce_max_sync(0xffffffffu, head);
@@ -208,12 +212,13 @@ __device__ __forceinline__ void topk_rounds(uint32_t head, const uint32_t* __res
     const uint32_t eq = __ballot_sync(0xffffffffu, mine);
     if (mine && (eq & lt) == 0) {
       if constexpr (TRACK_DUP) {
-        run = (wmax == last) ? run + 1 : 0;
-        last = wmax;
+        run = (head == last) ? run + 1 : 0;
+        last = head;
+        tag = (uint32_t)lane | ((uint32_t)run << 8);
       }
-      win[k] = make_uint2(wmax, (uint32_t)lane | ((uint32_t)run << 8));
-      ++ptr;
-      head = my_list[ptr];
+      win[k] = make_uint2(head, tag);
+      ++next;
+      head = *next;
     }
   }
 }
@@ -268,7 +273,7 @@ grouped_topk_kernel(GatingParams p) {
 #pragma unroll
       for (int v = 0; v < VPL; v += 2) {
         float y0, y1;
-        sigmoid_spec2(s[v], s[v + 1], y0, y1);
+        f2_unpack(sigmoid_spec2(s[v], s[v + 1]), y0, y1);
         s[v] = valid(v) ? y0 : -CUDART_INF_F;
         s[v + 1] = valid(v + 1) ? y1 : -CUDART_INF_F;
       }
@@ -312,10 +317,8 @@ grouped_topk_kernel(GatingParams p) {
 #pragma unroll
       for (int v = 0; v < VPL; v += 4) {
         const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + e0 + v));
-        c[v] = __fadd_rn(s[v], bv.x);
-        c[v + 1] = __fadd_rn(s[v + 1], bv.y);
-        c[v + 2] = __fadd_rn(s[v + 2], bv.z);
-        c[v + 3] = __fadd_rn(s[v + 3], bv.w);
+        f2_unpack(f2_add(f2_pack(s[v], s[v + 1]), f2_pack(bv.x, bv.y)), c[v], c[v + 1]);          // rounds like __fadd_rn
+        f2_unpack(f2_add(f2_pack(s[v + 2], s[v + 3]), f2_pack(bv.z, bv.w)), c[v + 2], c[v + 3]);
       }
     } else {
 #pragma unroll
@@ -323,26 +326,43 @@ grouped_topk_kernel(GatingParams p) {
     }
   }
 
-  // ---- keys: the originals go to shared memory for the final index look-up, a sorted copy stays in registers
-  uint32_t key[VPL];
+  // ---- keys: the originals go to shared memory for the final index look-up, a sorted copy feeds the rounds.
+  // The scores are sorted as floats.  Positive floats order like their bit patterns, so when every selection
+  // score of the token is > 0 (sigmoid scores with the usual small bias) the bits serve as integer keys as
+  // they are; only a token with a score <= 0 (or -inf fillers of a ragged last lane) pays for the mapping.
+  float f[VPL];
 #pragma unroll
-  for (int v = 0; v < VPL; ++v) key[v] = score_key(c[v]);
+  for (int v = 0; v < VPL; ++v) f[v] = c[v];
+  sort_desc<VPL>(f);
+  const bool any_nonpos = __any_sync(0xffffffffu, !(f[VPL - 1] > 0.f));
+  uint32_t key[VPL], okey[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    key[v] = __float_as_uint(f[v]);
+    okey[v] = __float_as_uint(c[v]);
+  }
+  if (any_nonpos) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      key[v] = score_key(f[v]);
+      okey[v] = score_key(c[v]);
+    }
+  }
   uint32_t* wkeys = sm_key[threadIdx.x >> 5];
   float* wscores = sm_s[threadIdx.x >> 5];
   if constexpr (VPL >= 4) {
 #pragma unroll
     for (int v = 0; v < VPL; v += 4) {
-      *reinterpret_cast<uint4*>(wkeys + e0 + v) = make_uint4(key[v], key[v + 1], key[v + 2], key[v + 3]);
+      *reinterpret_cast<uint4*>(wkeys + e0 + v) = make_uint4(okey[v], okey[v + 1], okey[v + 2], okey[v + 3]);
       *reinterpret_cast<float4*>(wscores + e0 + v) = make_float4(s[v], s[v + 1], s[v + 2], s[v + 3]);
     }
   } else {
 #pragma unroll
     for (int v = 0; v < VPL; ++v) {
-      wkeys[e0 + v] = key[v];
+      wkeys[e0 + v] = okey[v];
       wscores[e0 + v] = s[v];
     }
   }
-  sort_desc<VPL>(key);
   uint32_t* my_list = sm_list[threadIdx.x >> 5] + lane * LIST;
   if constexpr (VPL >= 4) {
 #pragma unroll
@@ -365,9 +385,9 @@ grouped_topk_kernel(GatingParams p) {
     const int lg = LG >= 0 ? LG : p.lanes_per_group_log2;   // a group spans 2^lg lanes
     const int lpg = 1 << lg;
     const int n_group = LG >= 0 ? (32 >> LG) : p.n_group;
-    float t1 = key_score(key[0]);
+    float t1 = f[0];
     float t2 = -CUDART_INF_F;
-    if constexpr (VPL >= 2) t2 = key_score(key[1]);
+    if constexpr (VPL >= 2) t2 = f[1];
 #pragma unroll
     for (int o = 1; o < lpg; o <<= 1) {
       const float o1 = __shfl_xor_sync(0xffffffffu, t1, o);
