@@ -17,13 +17,14 @@ __device__ __forceinline__ float silu_mul_f32(float g, float u) {
 }
 
 template <typename T, int UNROLL>
-__global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out,
+__global__ void __launch_bounds__(512) silu_and_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out,
                                                                int nvec /* N / 8 */, int64_t x_row_stride,
                                                                int64_t out_row_stride, int n) {
   using T2 = typename Elem<T>::T2;
   // blockIdx.x = row, blockIdx.y = segment of the row: no integer division anywhere
   const int64_t r = blockIdx.x;
-  const int c0 = blockIdx.y * (256 * UNROLL) + threadIdx.x;
+  const int bd = blockDim.x;
+  const int c0 = blockIdx.y * (bd * UNROLL) + threadIdx.x;
   const uint4* gp = reinterpret_cast<const uint4*>(x + r * x_row_stride);
   const uint4* up = reinterpret_cast<const uint4*>(x + r * x_row_stride + n);
   uint4* op = reinterpret_cast<uint4*>(out + r * out_row_stride);
@@ -31,7 +32,7 @@ __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restri
   uint4 g[UNROLL], u[UNROLL];
 #pragma unroll
   for (int i = 0; i < UNROLL; ++i) {
-    const int c = c0 + i * 256;
+    const int c = c0 + i * bd;
     if (c < nvec) {
       g[i] = __ldcs(gp + c);
       u[i] = __ldcs(up + c);
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(256) silu_and_mul_vec_kernel(const T* __restri
   }
 #pragma unroll
   for (int i = 0; i < UNROLL; ++i) {
-    const int c = c0 + i * 256;
+    const int c = c0 + i * bd;
     if (c >= nvec) continue;
     uint4 o;
     const T2* g2 = reinterpret_cast<const T2*>(&g[i]);
@@ -80,27 +81,35 @@ static int launch_silu(const void* x, void* out, int64_t rows, int n, int64_t xs
   if (vec_ok) {
     if constexpr (sizeof(T) == 2) {
       const int nvec = n / VEC;
-      // vectors per thread: the choice that wastes the fewest idle threads in a row's last block
-      int best_u = 1;
-      int64_t best_waste = -1;
-      for (int u : {1, 2, 4, 8}) {
-        const int per_block = 256 * u;
-        const int64_t waste = (int64_t)((nvec + per_block - 1) / per_block) * per_block - nvec;
-        if (best_waste < 0 || waste < best_waste || (waste == best_waste && u <= 4)) {
-          best_waste = waste;
-          best_u = u;
+      // block size (whole warps) and vectors per thread: the pair that leaves the fewest idle vector slots in
+      // a row's last block.  N = 11008 has 1376 vectors per row: 352 threads x 4 cover a row with 32 idle
+      // slots, where 256 threads x 2 leave 160 of 1536 idle.
+      constexpr int kPreferredUnroll = 4;   // measured at N = 11008: 4 and 2 are equal (0.955 / 0.95 of HBM), 8 is 0.91
+      int best_u = 1, best_bd = 256;
+      int64_t best_cost = -1;
+      for (int bd = 128; bd <= 512; bd += 32) {
+        for (int u : {1, 2, 4, 8}) {
+          const int per_block = bd * u;
+          const int64_t waste = (int64_t)((nvec + per_block - 1) / per_block) * per_block - nvec;
+          // ties: the preferred unroll, then the block size nearest 256
+          const int64_t cost = waste * 4096 + (u == kPreferredUnroll ? 0 : 1024) + (bd > 256 ? bd - 256 : 256 - bd);
+          if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_u = u;
+            best_bd = bd;
+          }
         }
       }
-      const int segs = (nvec + 256 * best_u - 1) / (256 * best_u);
+      const int segs = (nvec + best_bd * best_u - 1) / (best_bd * best_u);
       DLB_CHECK_ARG(rows <= 0x7fffffffLL && segs <= 65535, DLB_ERR_TOO_LARGE, "silu_and_mul: grid too large");
       const dim3 grid((unsigned)rows, (unsigned)segs);
       const T* xp = (const T*)x;
       T* op = (T*)out;
       switch (best_u) {
-        case 1: silu_and_mul_vec_kernel<T, 1><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
-        case 2: silu_and_mul_vec_kernel<T, 2><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
-        case 4: silu_and_mul_vec_kernel<T, 4><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
-        default: silu_and_mul_vec_kernel<T, 8><<<grid, 256, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        case 1: silu_and_mul_vec_kernel<T, 1><<<grid, best_bd, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        case 2: silu_and_mul_vec_kernel<T, 2><<<grid, best_bd, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        case 4: silu_and_mul_vec_kernel<T, 4><<<grid, best_bd, 0, stream>>>(xp, op, nvec, xs, os, n); break;
+        default: silu_and_mul_vec_kernel<T, 8><<<grid, best_bd, 0, stream>>>(xp, op, nvec, xs, os, n); break;
       }
     }
   } else {
