@@ -289,6 +289,35 @@ def test_decode_attention_fwd_token_granular(cuda_device, hq, hkv, cap):
     torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("dk,dv,dtype", [(64, 64, torch.bfloat16), (48, 32, torch.float16), (96, 64, torch.bfloat16),
+                                         (128, 80, torch.float16)])
+def test_decode_attention_fwd_token_granular_head_sizes(cuda_device, dk, dv, dtype):
+    """The one-token-page gather at the 64-wide tile, at head sizes below the tile width (chunks past the head
+    size are zero-length copies) and with a v head size that differs from the q / k one."""
+    from dlcompiler_b200 import decode_attention_fwd
+
+    g = torch.Generator().manual_seed(dk * 1000 + dv)
+    B, hq, hkv, max_ctx, pool = 4, 8, 2, 300, 1500
+    lens = torch.randint(1, max_ctx + 1, (B,), generator=g)
+    req_to_token = torch.zeros(B, max_ctx, dtype=torch.int32)
+    perm = torch.randperm(pool, generator=g)
+    off = 0
+    for i in range(B):
+        n = int(lens[i])
+        req_to_token[i, :n] = perm[off:off + n].to(torch.int32)
+        off += n
+    kb = torch.randn(pool, hkv, dk, generator=g).to(dtype)
+    vb = torch.randn(pool, hkv, dv, generator=g).to(dtype)
+    q = torch.randn(B, hq, dk, generator=g).to(dtype)
+    dev = cuda_device
+    o = torch.full((B, hq, dv), float("nan"), dtype=dtype, device=dev)
+    start = torch.cat([lens.new_zeros(1), lens.cumsum(0)[:-1]])
+    decode_attention_fwd(q.to(dev), kb.to(dev), vb.to(dev), o, req_to_token.to(dev), torch.arange(B, device=dev),
+                         start.to(dev), lens.to(dev), None, max_ctx, dk ** -0.5)
+    ref = oracle.paged_decode_attention(q, kb.unsqueeze(1), vb.unsqueeze(1), req_to_token, lens, sm_scale=dk ** -0.5)
+    torch.testing.assert_close(o.cpu().float(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
 # ------------------------------------------------------------------ prefill over a paged cache with history
 def _paged_prefill_case(seed, q_lens, hist_lens, page, hq, hkv, D, dtype, table_dtype=torch.int32):
     g = torch.Generator().manual_seed(seed)
