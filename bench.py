@@ -1,7 +1,7 @@
 """Benchmark of the dlBLAS hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--ops all|none]
-    python bench.py --profile-case {silu,gating,moe,prefill,prefill_c4,decode,decode_p1,rotary,rotary_c4} [--steps N]
+    python bench.py --profile-case {silu,gating,moe,moe_c3,moe_c3_unit,prefill,prefill_c4,decode,decode_p1,rotary,rotary_c4} [--steps N]
 
 Headline (one JSON line on stdout): fused_moe on the Mixtral-like configuration
 (T=4096, H=4096, I=14336, E=8, top_k=2, bf16) in TFLOP/s, whole job.  N > 1 runs the
@@ -789,6 +789,21 @@ def run_profile_case(args):
         hs, w1, w2 = d["hidden_states"].to(dev), d["w1"].to(dev), d["w2"].to(dev)
         fn = lambda: dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k)
         what = "fused_moe T=2048 H=4096 I=7168 E=4 top_k=2 bf16"
+    elif op in ("moe_c3", "moe_c3_unit"):
+        # the benchmark shape itself, for one-pass DRAM counters: weights drawn on the device with the benchmark's
+        # standard deviation (0.02) or with unit variance (the grouped GEMM's clock under the power cap, and
+        # with it its DRAM re-reads, depend on the operand values)
+        wl = W.MoeWorkload()
+        d = wl.make(weights=False)
+        std = 0.02 if op == "moe_c3" else 1.0
+        g = torch.Generator(device=dev)
+        g.manual_seed(11)
+        w1 = (torch.randn(wl.experts, 2 * wl.inter, wl.hidden, generator=g, device=dev) * std).to(torch.bfloat16)
+        w2 = (torch.randn(wl.experts, wl.hidden, wl.inter, generator=g, device=dev) * std).to(torch.bfloat16)
+        tw, ti = dl.softmax_topk(d["router_logits"].to(dev), wl.top_k)
+        hs = d["hidden_states"].to(dev)
+        fn = lambda: dl.fused_moe(hs, w1, w2, tw, ti, wl.top_k)
+        what = f"fused_moe C3 shape, weights N(0, {std}^2) bf16"
     elif op in ("prefill", "prefill_c4"):
         # q/k/v/o 168 MB > L2; prefill_c4 is the benchmark shape itself (670 MB), for one-pass DRAM counters
         wl = W.PrefillWorkload(batch=2, seq_len=4096) if op == "prefill" else W.PrefillWorkload()
@@ -865,7 +880,7 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=4096)
     ap.add_argument("--warm-seconds", type=float, default=1.0,
                     help="N = 1: keep warming up until this much wall time has passed (device under load)")
-    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "prefill", "prefill_c4", "decode", "decode_p1", "rotary", "rotary_c4"],
+    ap.add_argument("--profile-case", default=None, choices=["silu", "gating", "moe", "moe_c3", "moe_c3_unit", "prefill", "prefill_c4", "decode", "decode_p1", "rotary", "rotary_c4"],
                     help="run one op --steps times (at most 8) on a profiler-sized case and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
