@@ -540,6 +540,18 @@ MOE_WORKLOAD = ("C3 fused_moe T=4096 H=4096 I=14336 E=8 top_k=2 bf16 (moe_align 
                 "down GEMM x weight -> combine)")
 
 
+_ORIGINAL_AFFINITY = None
+
+
+def restore_cpu_affinity():
+    """Gives the process back every core it started with (the CPU baseline leg uses all of them)."""
+    if _ORIGINAL_AFFINITY is not None:
+        try:
+            os.sched_setaffinity(0, _ORIGINAL_AFFINITY)
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] CPU affinity not restored ({exc!r})", file=sys.stderr)
+
+
 def bind_to_gpu_cpus(device_index):
     """Runs this rank on the CPU cores next to its GPU (the affinity NVML reports for the device), so that the
     pinned host buffers of the end-to-end leg are first touched, and therefore placed, on the GPU's own NUMA
@@ -557,8 +569,11 @@ def bind_to_gpu_cpus(device_index):
             handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
         words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
         cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
-        cpus &= os.sched_getaffinity(0)
+        global _ORIGINAL_AFFINITY
+        start = os.sched_getaffinity(0)
+        cpus &= start
         if cpus:
+            _ORIGINAL_AFFINITY = start
             os.sched_setaffinity(0, cpus)
     except Exception as exc:  # noqa: BLE001 - placement is an optimisation, never a requirement
         print(f"[bench] CPU affinity not set ({exc!r})", file=sys.stderr)
@@ -581,11 +596,11 @@ def run_ours(args):
     peaks = load_peaks()
     wl = W.MoeWorkload()
 
+    # at every N: the pinned buffers of the end-to-end leg belong on the GPU's own NUMA node
+    bind_to_gpu_cpus(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
-
-        bind_to_gpu_cpus(local_rank)
 
         os.environ.setdefault("NCCL_DEBUG", "WARN")     # stdout is redirected anyway; a caller's setting stands
         dist = dist_mod
@@ -750,6 +765,7 @@ def run_ours(args):
         if args.cpu_baseline:
             del w1, w2
             torch.cuda.empty_cache()
+            restore_cpu_affinity()
             tf, secs, cores, passes = cpu_fused_moe(args.cpu_sample)
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": f"first {args.cpu_sample} of 4096 tokens, best of {passes} passes "
