@@ -245,8 +245,11 @@ int64_t dlb_paged_decode_workspace_floats(int64_t batch, int64_t hq, int64_t hea
  * pieces with a log-sum-exp merge.  Caches are [num_pages, page_size, hkv, d]; block_table is
  * [batch, max_pages] (int32 or int64).  head_dim is the q / k head size, head_dim_v the v / out head
  * size: multiples of 8 up to 128, not necessarily equal (the reference handles any head size by a power
- * of two plus a remainder, and a v size of its own: paged_attention.py:526-539).  Replaces the decode
- * branch of paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:492-671 (kernels :40-285). */
+ * of two plus a remainder, and a v size of its own: paged_attention.py:526-539).  page_size is a power of
+ * two; pages of 1, 2 or 4 tokens (page size 1 = the token-granular cache of decode_attention_fwd,
+ * decode_attention.py:559-620) are gathered row by row when the caches are 16-byte aligned with page and slot
+ * strides below 4 GiB, and fall back to one tensor-map box per page otherwise (slower, same result).
+ * Replaces the decode branch of paged_attention_fwd, python/dlBLAS/dlblas/kernels/paged_attention.py:492-671 (kernels :40-285). */
 int dlb_paged_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const void* block_table,
                      const void* kv_seqlens, float* partial, int64_t batch, int64_t hq, int64_t hkv,
                      int64_t head_dim, int64_t head_dim_v, int64_t page_size, int64_t num_pages, int64_t max_pages,
