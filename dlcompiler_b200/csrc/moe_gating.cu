@@ -228,11 +228,9 @@ __device__ __forceinline__ void topk_rounds(uint32_t head, const uint32_t* __res
 // group at 2^LG with all 32 lanes in groups, and TOPK > 0 fixes top_k, so that the shuffle trees, the group
 // ranking and the rounds unroll (the DeepSeek-V3 shape: 256 experts, 8 groups, top-8); LG = -1 / TOPK = 0
 // read them from the parameters.
-#ifndef DLB_GATE_MIN_BLOCKS
-#define DLB_GATE_MIN_BLOCKS 6
-#endif
+constexpr int kGateMinBlocks = 6;   // 40 registers per thread, six CTAs per SM (1 % faster than 48 registers / five)
 template <int VPL, bool FULL, int LG = -1, int TOPK = 0>
-__global__ void __launch_bounds__(GateShape<VPL>::WARPS * 32, LG >= 0 ? DLB_GATE_MIN_BLOCKS : 1)
+__global__ void __launch_bounds__(GateShape<VPL>::WARPS * 32, LG >= 0 ? kGateMinBlocks : 1)
 grouped_topk_kernel(GatingParams p) {
   constexpr int WARPS = GateShape<VPL>::WARPS, LIST = GateShape<VPL>::LIST;
   const int lane = threadIdx.x & 31;
